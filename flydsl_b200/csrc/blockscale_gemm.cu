@@ -1,0 +1,780 @@
+// FP8 (e4m3) block-scale GEMM core for sm_100a: one persistent, warp-specialised kernel template
+// that serves the dense GEMM and both MoE stages.
+//
+//   C[m,n] = sum_kb ( sum_{k in kb} A[m,k] * B[n,k] ) * sa[kb,m] * sb[n/128,kb]
+//
+// Roles inside a 384-thread CTA (one CTA per SM):
+//   warp 0      producer: TMA tensor load of the A tile (dense) and bulk copies of the repacked,
+//               pre-swizzled weight tile into a multistage shared-memory ring
+//   warp 1      MMA issuer: tcgen05.mma kind::f8f6f4, 128 x BN x 32, four per 128-wide K block,
+//               each K block into a fresh TMEM accumulator buffer (two buffers, ping-pong)
+//   warps 2-3   MoE only: gather activation rows by sorted id with cp.async into the same swizzled
+//               image TMA would have produced
+//   warps 4-11  epilogue: tcgen05.ld the K-block partial, acc = fma(partial, sa*sb, acc) in fp32
+//               registers (the per-128-K scale promotion), release the TMEM buffer, and after the
+//               last K block convert and store (dense), SiLU(gate)*up (stage 1) or weight and
+//               scatter / atomically add (stage 2)
+//
+// The computation follows kernel_gemm / compute_tile_blockscale of the reference
+// (kernels/blockscale_preshuffle_gemm.py:161-839, :509-587) and the stage kernels of
+// kernels/moe_blockscale_2stage.py (:206-1161, :1386-2387); none of its AMD data movement is kept.
+#include "common.cuh"
+
+namespace flyb200 {
+
+constexpr int BM = 128;            // MMA M = accumulator lanes
+constexpr int BK = 128;            // K bytes per pipeline stage = one scale block
+constexpr int kThreads = 384;
+constexpr int kEpiWarp0 = 4;       // first epilogue warp
+constexpr int kATileBytes = BM * BK;
+
+enum Mode : int { kDense = 0, kMoe1 = 1, kMoe2 = 2 };
+
+struct GemmParams {
+  const uint8_t* a;        // MoE: activation rows to gather from (dense uses the tensor map)
+  const uint8_t* b;        // repacked weights
+  const float* scale_a;    // [K/128, rows]
+  const float* scale_b;    // [blocks_n, K/128]
+  void* out;
+  int* err;                // device error word
+  int M;                   // dense: rows of A; MoE: tokens T
+  int N;                   // dense: N; stage 1: inter_dim I; stage 2: model_dim H
+  int K;
+  int a_box_rows;          // dense: rows the A tensor-map box brings per stage
+  // MoE only
+  const int* sorted_ids;
+  const int* expert_ids;
+  const float* sorted_weights;
+  const int* num_valid;
+  int topk;
+  int tile_m;
+  int num_blocks;
+  int experts;
+  int doweight;
+  int accumulate;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int kBTileBytes = BN * BK;
+  static constexpr int kStageBytes = kATileBytes + kBTileBytes;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128) ? 6 : (BN == 64) ? 8 : 10;
+  static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;  // two accumulator buffers
+  static constexpr int kCH = BN / 4;  // columns per epilogue thread per column group
+  static constexpr int kBarBytes = 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;  // + align slack
+};
+
+template <typename OutT>
+__device__ __forceinline__ void store8(OutT* dst, const float* v) {
+  uint4 q;
+  q.x = pack2(v[0], v[1], OutT());
+  q.y = pack2(v[2], v[3], OutT());
+  q.z = pack2(v[4], v[5], OutT());
+  q.w = pack2(v[6], v[7], OutT());
+  *reinterpret_cast<uint4*>(dst) = q;
+}
+template <>
+__device__ __forceinline__ void store8<float>(float* dst, const float* v) {
+  *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+// Atomic accumulate of 8 consecutive outputs (stage 2, accumulate mode).
+__device__ __forceinline__ void red8(__nv_bfloat16* dst, const float* v) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t p = pack2(v[2 * i], v[2 * i + 1], __nv_bfloat16());
+    asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(dst + 2 * i), "r"(p) : "memory");
+  }
+}
+__device__ __forceinline__ void red8(__half* dst, const float* v) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t p = pack2(v[2 * i], v[2 * i + 1], __half());
+    asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(dst + 2 * i), "r"(p) : "memory");
+  }
+}
+__device__ __forceinline__ void red8(float* dst, const float* v) {
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * i),
+                 "f"(v[4 * i]), "f"(v[4 * i + 1]), "f"(v[4 * i + 2]), "f"(v[4 * i + 3])
+                 : "memory");
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  // silu(g) * u with the fast exp, as the reference does (moe_blockscale_2stage.py:239-251).
+  return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+
+// Tile bookkeeping shared by every role so that all of them walk the same sequence.
+template <int BN, int MODE>
+struct TileWalker {
+  int num_m, num_n, total;
+  __device__ __forceinline__ TileWalker(const GemmParams& p) {
+    if constexpr (MODE == kDense) {
+      num_m = (p.M + BM - 1) / BM;
+      num_n = (p.N + BN - 1) / BN;
+    } else {
+      int valid_rows = p.num_valid[0];
+      int nb = (valid_rows + p.tile_m - 1) / p.tile_m;
+      num_m = nb < p.num_blocks ? nb : p.num_blocks;
+      if (num_m < 0) num_m = 0;
+      constexpr int kColsPerTile = (MODE == kMoe1) ? BN / 2 : BN;
+      num_n = (p.N + kColsPerTile - 1) / kColsPerTile;
+    }
+    total = num_m * num_n;
+  }
+  // tile -> (m block, n tile); consecutive CTAs share the weight tile and differ in rows.
+  __device__ __forceinline__ void decode(int tile, int& m_blk, int& n_tile) const {
+    n_tile = tile / num_m;
+    m_blk = tile - n_tile * num_m;
+  }
+};
+
+template <int BN, int MODE, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
+  using C = Cfg<BN>;
+  constexpr int kStages = C::kStages;
+  constexpr int CH = C::kCH;
+  extern __shared__ uint8_t smem_raw[];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + kStages * C::kStageBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
+  uint8_t* misc = smem_al + kStages * C::kStageBytes + 8 * (2 * kStages + 4);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 4);
+
+  constexpr int kFullCount = (MODE == kDense) ? 1 : 3;  // producer (+ two gather warps)
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), kFullCount);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 8);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_proxy_async_smem();
+    fence_barrier_init();
+    if constexpr (MODE == kDense) prefetch_tensormap(&tmap_a);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const TileWalker<BN, MODE> walk(p);
+  const int KB = p.K / BK;
+
+  if (warp < kEpiWarp0) {
+    reg_dealloc<48>();
+    if (warp == 0 && lane == 0) {
+      // ---------------- producer: weights (and dense A) via TMA ----------------
+      uint32_t it = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < walk.total && alive; tile += gridDim.x) {
+        int m_blk, n_tile;
+        walk.decode(tile, m_blk, n_tile);
+        const uint8_t* wbase = p.b;
+        int rows_b;  // weight rows this tile brings per column group
+        size_t row_stride_kb;  // bytes between consecutive K blocks of the repacked weight
+        int n0;
+        if constexpr (MODE == kDense) {
+          n0 = n_tile * BN;
+          rows_b = min(BN, p.N - n0);
+          row_stride_kb = static_cast<size_t>(p.N) * BK;
+        } else {
+          const int e = p.expert_ids[m_blk];
+          if (e < 0 || e >= p.experts) continue;
+          if constexpr (MODE == kMoe1) {
+            n0 = n_tile * (BN / 2);
+            rows_b = min(BN / 2, p.N - n0);
+            wbase += static_cast<size_t>(e) * 2 * p.N * p.K;
+            row_stride_kb = static_cast<size_t>(2 * p.N) * BK;
+          } else {
+            n0 = n_tile * BN;
+            rows_b = min(BN, p.N - n0);
+            wbase += static_cast<size_t>(e) * p.N * p.K;
+            row_stride_kb = static_cast<size_t>(p.N) * BK;
+          }
+        }
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.err, kErrWaitSmemEmpty)) {
+            alive = false;
+            break;
+          }
+          const uint32_t sa = smem_base + s * C::kStageBytes;
+          const uint32_t sb = sa + kATileBytes;
+          const uint8_t* src = wbase + kb * row_stride_kb + static_cast<size_t>(n0) * BK;
+          if constexpr (MODE == kDense) {
+            mbar_arrive_expect_tx(full_bar(s), p.a_box_rows * BK + rows_b * BK);
+            tma_load_2d(sa, &tmap_a, kb * BK, m_blk * BM, full_bar(s));
+            bulk_load(sb, src, rows_b * BK, full_bar(s));
+          } else if constexpr (MODE == kMoe1) {
+            mbar_arrive_expect_tx(full_bar(s), 2 * rows_b * BK);
+            bulk_load(sb, src, rows_b * BK, full_bar(s));
+            bulk_load(sb + (BN / 2) * BK, src + static_cast<size_t>(p.N) * BK, rows_b * BK,
+                      full_bar(s));
+          } else {
+            mbar_arrive_expect_tx(full_bar(s), rows_b * BK);
+            bulk_load(sb, src, rows_b * BK, full_bar(s));
+          }
+        }
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ---------------- MMA issuer ----------------
+      constexpr uint32_t idesc = umma_idesc_e4m3_f32(BM, BN);
+      uint32_t it = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < walk.total && alive; tile += gridDim.x) {
+        if constexpr (MODE != kDense) {
+          int m_blk, n_tile;
+          walk.decode(tile, m_blk, n_tile);
+          const int e = p.expert_ids[m_blk];
+          if (e < 0 || e >= p.experts) continue;
+        }
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          const int buf = it & 1;
+          const uint32_t tph = (it >> 1) & 1;
+          if (!mbar_wait(tempty_bar(buf), tph ^ 1, abort_flag, p.err, kErrWaitTmemEmpty) ||
+              !mbar_wait(full_bar(s), ph, abort_flag, p.err, kErrWaitSmemFull)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * C::kStageBytes;
+          const uint64_t adesc = umma_desc_sw128(sa);
+          const uint64_t bdesc = umma_desc_sw128(sa + kATileBytes);
+          const uint32_t d = tmem_base + buf * BN;
+#pragma unroll
+          for (int k = 0; k < BK / 32; ++k)
+            tc_mma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
+          tc_commit(empty_bar(s));    // stage reusable once these MMAs have read it
+          tc_commit(tfull_bar(buf));  // partial sums of this K block are in TMEM
+        }
+      }
+    } else if (MODE != kDense && warp >= 2) {
+      // ---------------- MoE: gather activation rows with cp.async ----------------
+      // Thread g owns rows g and g+64 of the tile; row r, 16-byte chunk c lands at
+      // r*128 + ((c ^ (r & 7)) << 4): the 128-byte-swizzled K-major image.
+      constexpr int kDepth = (kStages > 4) ? 3 : 2;  // groups in flight before a stage is published
+      const int g = threadIdx.x - 64;
+      uint32_t it = 0, published = 0;
+      bool alive = true;
+      const size_t row_bytes = static_cast<size_t>(p.K);
+      for (int tile = blockIdx.x; tile < walk.total && alive; tile += gridDim.x) {
+        int m_blk, n_tile;
+        walk.decode(tile, m_blk, n_tile);
+        const int e = p.expert_ids[m_blk];
+        if (e < 0 || e >= p.experts) continue;
+        const uint8_t* src_row[2];
+        uint32_t src_ok[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int r = g + 64 * h;
+          src_row[h] = p.a;
+          src_ok[h] = 0;
+          if (r < p.tile_m) {
+            const int id = p.sorted_ids[m_blk * p.tile_m + r];
+            const int t = id & 0xFFFFFF;
+            const int slot = static_cast<unsigned>(id) >> 24;
+            if (t < p.M && slot < p.topk) {
+              const size_t row = (MODE == kMoe1) ? static_cast<size_t>(t)
+                                                 : static_cast<size_t>(t) * p.topk + slot;
+              src_row[h] = p.a + row * row_bytes;
+              src_ok[h] = 16;
+            }
+          }
+        }
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.err, kErrWaitGather)) {
+            alive = false;
+            break;
+          }
+          const uint32_t sa = smem_base + s * C::kStageBytes;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int r = g + 64 * h;
+            if (r < p.tile_m) {
+              const uint8_t* src = src_row[h] + (src_ok[h] ? kb * BK : 0);
+#pragma unroll
+              for (int c = 0; c < 8; ++c)
+                cp_async_16(sa + r * 128 + ((c ^ (r & 7)) << 4), src + c * 16, src_ok[h]);
+            }
+          }
+          cp_async_commit();
+          if (it - published >= static_cast<uint32_t>(kDepth)) {
+            cp_async_wait<kDepth>();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_bar(published % kStages));
+            ++published;
+          }
+        }
+      }
+      // drain: publish whatever was issued
+      cp_async_wait<0>();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (alive && lane == 0)
+        for (; published < it; ++published) mbar_arrive(full_bar(published % kStages));
+    }
+  } else {
+    // ---------------- epilogue warps: scale promotion + output ----------------
+    reg_alloc<232>();
+    const int ew = warp - kEpiWarp0;
+    const int quad = warp & 3;   // TMEM lane quadrant this warp may read
+    const int half = ew >> 2;    // which CH-wide slice of each column group
+    const int r = quad * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    constexpr int LD = (CH > 32) ? 16 : CH;  // columns per tcgen05.ld (bounded by registers)
+    constexpr int NSUB = CH / LD;
+    OutT* const out = reinterpret_cast<OutT*>(p.out);
+
+    uint32_t it = 0;
+    bool alive = true;
+    for (int tile = blockIdx.x; tile < walk.total && alive; tile += gridDim.x) {
+      int m_blk, n_tile;
+      walk.decode(tile, m_blk, n_tile);
+
+      // Row identity, scale pointers and output columns of this thread for this tile.
+      bool row_ok;
+      const float* sa_ptr;      // + kb * sa_stride
+      size_t sa_stride;
+      const float* sb_ptr0;     // + kb
+      const float* sb_ptr1;
+      int col0, col1;           // first output column of group 0 / group 1 (MoE1: same column)
+      size_t out_row = 0;
+      float route_w = 1.0f;
+      const int KBs = KB;
+      if constexpr (MODE == kDense) {
+        const int row = m_blk * BM + r;
+        row_ok = row < p.M;
+        sa_ptr = p.scale_a + (row_ok ? row : 0);
+        sa_stride = static_cast<size_t>(p.M);
+        const int n0 = n_tile * BN;
+        col0 = n0 + half * CH;
+        col1 = n0 + BN / 2 + half * CH;
+        const int nblk_max = (p.N + 127) / 128 - 1;
+        sb_ptr0 = p.scale_b + static_cast<size_t>(min(col0 / 128, nblk_max)) * KBs;
+        sb_ptr1 = p.scale_b + static_cast<size_t>(min(col1 / 128, nblk_max)) * KBs;
+        out_row = static_cast<size_t>(row) * p.N;
+      } else {
+        const int e = p.expert_ids[m_blk];
+        if (e < 0 || e >= p.experts) continue;
+        int t = 0, slot = 0;
+        row_ok = false;
+        if (r < p.tile_m) {
+          const int id = p.sorted_ids[m_blk * p.tile_m + r];
+          t = id & 0xFFFFFF;
+          slot = static_cast<unsigned>(id) >> 24;
+          row_ok = (t < p.M) && (slot < p.topk);
+          if (row_ok && p.doweight) route_w = p.sorted_weights[m_blk * p.tile_m + r];
+        }
+        if (!row_ok) { t = 0; slot = 0; }
+        if constexpr (MODE == kMoe1) {
+          sa_ptr = p.scale_a + t;
+          sa_stride = static_cast<size_t>(p.M);
+          const int n0 = n_tile * (BN / 2);
+          col0 = col1 = n0 + half * CH;
+          const int nb_exp = (2 * p.N) / 128;  // scale rows per expert
+          sb_ptr0 = p.scale_b + (static_cast<size_t>(e) * nb_exp + min(col0, p.N - 1) / 128) * KBs;
+          sb_ptr1 = p.scale_b +
+                    (static_cast<size_t>(e) * nb_exp + (p.N + min(col0, p.N - 1)) / 128) * KBs;
+          out_row = (static_cast<size_t>(t) * p.topk + slot) * p.N;
+        } else {
+          sa_ptr = p.scale_a + static_cast<size_t>(t) * p.topk + slot;
+          sa_stride = static_cast<size_t>(p.M) * p.topk;
+          const int n0 = n_tile * BN;
+          col0 = n0 + half * CH;
+          col1 = n0 + BN / 2 + half * CH;
+          const int nb_exp = p.N / 128;
+          sb_ptr0 = p.scale_b + (static_cast<size_t>(e) * nb_exp + min(col0, p.N - 1) / 128) * KBs;
+          sb_ptr1 = p.scale_b + (static_cast<size_t>(e) * nb_exp + min(col1, p.N - 1) / 128) * KBs;
+          out_row = p.accumulate ? static_cast<size_t>(t) * p.N
+                                 : (static_cast<size_t>(t) * p.topk + slot) * p.N;
+        }
+      }
+
+      float acc0[CH], acc1[CH];
+#pragma unroll
+      for (int j = 0; j < CH; ++j) { acc0[j] = 0.f; acc1[j] = 0.f; }
+
+      // Scales are prefetched four K blocks ahead into a register ring.
+      float ring_a[4], ring_b0[4], ring_b1[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const bool in = j < KB;
+        ring_a[j] = (in && row_ok) ? __ldg(sa_ptr + j * sa_stride) : 0.f;
+        ring_b0[j] = in ? __ldg(sb_ptr0 + j) : 0.f;
+        ring_b1[j] = in ? __ldg(sb_ptr1 + j) : 0.f;
+      }
+
+      for (int kb0 = 0; kb0 < KB && alive; kb0 += 4) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int kb = kb0 + j;
+          if (kb < KB && alive) {
+            const int buf = it & 1;
+            const uint32_t tph = (it >> 1) & 1;
+            const float s0 = ring_a[j] * ring_b0[j];
+            const float s1 = ring_a[j] * ring_b1[j];
+            {
+              const int nk = kb + 4;
+              const bool in = nk < KB;
+              ring_a[j] = (in && row_ok) ? __ldg(sa_ptr + nk * sa_stride) : 0.f;
+              ring_b0[j] = in ? __ldg(sb_ptr0 + nk) : 0.f;
+              ring_b1[j] = in ? __ldg(sb_ptr1 + nk) : 0.f;
+            }
+            // warp-uniform outcome: the tcgen05.ld below needs the whole warp
+            const bool got = mbar_wait(tfull_bar(buf), tph, abort_flag, p.err, kErrWaitTmemFull);
+            if (!__all_sync(0xffffffffu, got)) {
+              alive = false;
+            } else {
+              tc_fence_after();
+              const uint32_t t0 = tmem_base + lane_base + buf * BN + half * CH;
+#pragma unroll
+              for (int sub = 0; sub < NSUB; ++sub) {
+                uint32_t v0[LD], v1[LD];
+                tmem_ld<LD>(t0 + sub * LD, v0);
+                tmem_ld<LD>(t0 + BN / 2 + sub * LD, v1);
+                tc_wait_ld();
+                if (sub == NSUB - 1) {
+                  tc_fence_before();
+                  __syncwarp();
+                  if (lane == 0) mbar_arrive(tempty_bar(buf));
+                }
+#pragma unroll
+                for (int c = 0; c < LD; ++c) {
+                  acc0[sub * LD + c] = fmaf(__uint_as_float(v0[c]), s0, acc0[sub * LD + c]);
+                  acc1[sub * LD + c] = fmaf(__uint_as_float(v1[c]), s1, acc1[sub * LD + c]);
+                }
+              }
+              ++it;
+            }
+          }
+        }
+      }
+      if (!alive) break;
+
+      // ---- output ----
+      if (row_ok) {
+        if constexpr (MODE == kMoe1) {
+#pragma unroll
+          for (int j = 0; j < CH; j += 8) {
+            if (col0 + j + 8 <= p.N) {
+              float y[8];
+#pragma unroll
+              for (int q = 0; q < 8; ++q) y[q] = silu_mul(acc0[j + q], acc1[j + q]) * route_w;
+              store8<OutT>(out + out_row + col0 + j, y);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int grp = 0; grp < 2; ++grp) {
+            const int cb = grp ? col1 : col0;
+            const float* acc = grp ? acc1 : acc0;
+#pragma unroll
+            for (int j = 0; j < CH; j += 8) {
+              if (cb + j + 8 <= p.N) {
+                float y[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) y[q] = acc[j + q] * route_w;
+                if (MODE == kMoe2 && p.accumulate)
+                  red8(out + out_row + cb + j, y);
+                else
+                  store8<OutT>(out + out_row + cb + j, y);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // A role gave up: let copies that are still in flight land before the CTA's shared memory and
+    // TMEM are handed back.
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ================================= host side =====================================================
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// A [M, K] fp8 row-major; box = 128 bytes of K x box_rows rows; 128-byte swizzle; OOB rows read 0.
+static int make_a_tensor_map(CUtensorMap* map, const void* a, int M, int K, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return set_error(FLYB200_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(K)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(a), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(FLYB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d",
+                     static_cast<int>(r));
+  return FLYB200_OK;
+}
+
+template <int BN, int MODE, typename OutT>
+static int launch(const CUtensorMap& tmap, const GemmParams& p, int grid, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  auto kern = bs_gemm_kernel<BN, MODE, OutT>;
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  FLYB200_CUDA_CHECK(cudaGetDevice(&dev));
+  if (configured_dev != dev) {
+    FLYB200_CUDA_CHECK(
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    configured_dev = dev;
+  }
+  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(tmap, p);
+  FLYB200_CUDA_CHECK(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+template <int MODE, typename OutT>
+static int launch_bn(int bn, const CUtensorMap& tmap, const GemmParams& p, int grid,
+                     cudaStream_t stream) {
+  switch (bn) {
+    case 32:
+      if constexpr (MODE == kMoe1) break;  // 16 gate + 16 up columns: not built
+      else return launch<32, MODE, OutT>(tmap, p, grid, stream);
+    case 64: return launch<64, MODE, OutT>(tmap, p, grid, stream);
+    case 128: return launch<128, MODE, OutT>(tmap, p, grid, stream);
+    case 256: return launch<256, MODE, OutT>(tmap, p, grid, stream);
+    default: break;
+  }
+  return set_error(FLYB200_ERR_INVALID_ARGUMENT, "block_n must be 32, 64, 128 or 256 (got %d)", bn);
+}
+
+static inline int cdiv(int a, int b) { return (a + b - 1) / b; }
+
+// Tile-width heuristic (role of select_tile_config in the reference's test): the widest tile whose
+// tile count still fills the SMs; among those, the fewest rounds of the persistent loop.
+static int pick_block_n(int m_blocks, int n_cols, int sms, bool moe1) {
+  const int cands[4] = {256, 128, 64, 32};
+  int best = 128;
+  double best_cost = 1e30;
+  for (int i = 0; i < 4; ++i) {
+    const int bn = cands[i];
+    if (moe1 && bn < 64) continue;
+    const int cols = moe1 ? bn / 2 : bn;
+    const long tiles = static_cast<long>(m_blocks) * cdiv(n_cols, cols);
+    const long rounds = (tiles + sms - 1) / sms;
+    // per-tile time ~ max(MMA, B traffic) is proportional to bn, with a fixed per-tile overhead
+    const double cost = rounds * (bn + 24.0);
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
+
+static int check_ptr(const void* p, size_t align, const char* name) {
+  if (!p) return set_error(FLYB200_ERR_INVALID_ARGUMENT, "%s is NULL", name);
+  if (reinterpret_cast<uintptr_t>(p) % align)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "%s must be %zu-byte aligned", name, align);
+  return FLYB200_OK;
+}
+
+}  // namespace flyb200
+
+using namespace flyb200;
+
+extern "C" int flyb200_blockscale_gemm(void* c, const void* a, const void* b_repacked,
+                                       const float* scale_a_t, const float* scale_b, int32_t M,
+                                       int32_t N, int32_t K, int32_t out_dtype,
+                                       const flyb200_gemm_cfg* cfg, void* stream) {
+  int rc;
+  if ((rc = check_ptr(c, 16, "c")) || (rc = check_ptr(a, 16, "a")) ||
+      (rc = check_ptr(b_repacked, 16, "b_repacked")) || (rc = check_ptr(scale_a_t, 4, "scale_a_t")) ||
+      (rc = check_ptr(scale_b, 4, "scale_b")))
+    return rc;
+  if (M < 1 || N < 16 || K < 128)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "bad shape M=%d N=%d K=%d", M, N, K);
+  if (N % 16) return set_error(FLYB200_ERR_INVALID_ARGUMENT, "N (%d) must be a multiple of 16", N);
+  if (K % 128) return set_error(FLYB200_ERR_INVALID_ARGUMENT, "K (%d) must be a multiple of 128", K);
+  if (out_dtype != FLYB200_BF16 && out_dtype != FLYB200_F16)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "out_dtype must be BF16 or F16");
+
+  const int sms = sm_count();
+  if (sms <= 0) return FLYB200_ERR_CUDA;
+  const int m_blocks = cdiv(M, BM);
+  int bn = (cfg && cfg->block_n) ? cfg->block_n : pick_block_n(m_blocks, N, sms, false);
+  int grid = sms;
+  if (cfg && cfg->max_ctas > 0 && cfg->max_ctas < grid) grid = cfg->max_ctas;
+  const long tiles = static_cast<long>(m_blocks) * cdiv(N, bn);
+  if (tiles < grid) grid = static_cast<int>(tiles);
+
+  GemmParams p{};
+  p.a = reinterpret_cast<const uint8_t*>(a);
+  p.b = reinterpret_cast<const uint8_t*>(b_repacked);
+  p.scale_a = scale_a_t;
+  p.scale_b = scale_b;
+  p.out = c;
+  p.err = device_error_word();
+  if (!p.err) return FLYB200_ERR_CUDA;
+  p.M = M; p.N = N; p.K = K;
+  // Small M: bring only as many rows as exist (rounded up to the 8-row swizzle atom).
+  p.a_box_rows = M >= BM ? BM : ((M + 7) / 8) * 8;
+
+  CUtensorMap tmap;
+  if ((rc = make_a_tensor_map(&tmap, a, M, K, p.a_box_rows))) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (out_dtype == FLYB200_BF16) return launch_bn<kDense, __nv_bfloat16>(bn, tmap, p, grid, st);
+  return launch_bn<kDense, __half>(bn, tmap, p, grid, st);
+}
+
+static int moe_common_checks(const void* out, const void* x, const void* w, const float* scale_x,
+                             const float* scale_w, const int32_t* sorted_ids,
+                             const int32_t* expert_ids, const float* sorted_weights,
+                             const int32_t* num_valid_ids, int T, int n, int kdim, int num_blocks,
+                             int E, int k, int tile_m, int doweight) {
+  int rc;
+  if ((rc = check_ptr(out, 16, "out")) || (rc = check_ptr(x, 16, "x")) ||
+      (rc = check_ptr(w, 16, "w")) || (rc = check_ptr(scale_x, 4, "scale_x")) ||
+      (rc = check_ptr(scale_w, 4, "scale_w")) || (rc = check_ptr(sorted_ids, 4, "sorted_ids")) ||
+      (rc = check_ptr(expert_ids, 4, "expert_ids")) ||
+      (rc = check_ptr(num_valid_ids, 4, "num_valid_ids")))
+    return rc;
+  if (doweight && (rc = check_ptr(sorted_weights, 4, "sorted_weights"))) return rc;
+  if (T < 1 || T >= (1 << 24) || E < 1 || k < 1 || k > 255 || num_blocks < 0)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "bad MoE sizes T=%d E=%d k=%d blocks=%d", T, E, k,
+                     num_blocks);
+  if (tile_m < 1 || tile_m > BM)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "tile_m (%d) must be in [1,128]", tile_m);
+  if (n % 128 || kdim % 128 || n < 128 || kdim < 128)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT,
+                     "MoE dims must be multiples of 128 (n=%d, k=%d)", n, kdim);
+  return FLYB200_OK;
+}
+
+extern "C" int flyb200_moe_gemm1(void* out, const void* x, const void* w_repacked,
+                                 const float* scale_x, const float* scale_w,
+                                 const int32_t* sorted_ids, const int32_t* expert_ids,
+                                 const float* sorted_weights, const int32_t* num_valid_ids,
+                                 int32_t T, int32_t I, int32_t H, int32_t num_blocks, int32_t E,
+                                 int32_t k, int32_t tile_m, int32_t doweight, int32_t out_dtype,
+                                 const flyb200_gemm_cfg* cfg, void* stream) {
+  int rc = moe_common_checks(out, x, w_repacked, scale_x, scale_w, sorted_ids, expert_ids,
+                             sorted_weights, num_valid_ids, T, I, H, num_blocks, E, k, tile_m,
+                             doweight);
+  if (rc) return rc;
+  if (out_dtype != FLYB200_BF16 && out_dtype != FLYB200_F16)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "stage-1 out_dtype must be BF16 or F16");
+  if (num_blocks == 0) return FLYB200_OK;
+  const int sms = sm_count();
+  if (sms <= 0) return FLYB200_ERR_CUDA;
+  int bn = (cfg && cfg->block_n) ? cfg->block_n : pick_block_n(num_blocks, I, sms, true);
+  if (bn < 64) return set_error(FLYB200_ERR_INVALID_ARGUMENT, "stage-1 block_n must be >= 64");
+  int grid = sms;
+  if (cfg && cfg->max_ctas > 0 && cfg->max_ctas < grid) grid = cfg->max_ctas;
+  const long tiles = static_cast<long>(num_blocks) * cdiv(I, bn / 2);
+  if (tiles < grid) grid = static_cast<int>(tiles);
+
+  GemmParams p{};
+  p.a = reinterpret_cast<const uint8_t*>(x);
+  p.b = reinterpret_cast<const uint8_t*>(w_repacked);
+  p.scale_a = scale_x; p.scale_b = scale_w; p.out = out;
+  p.err = device_error_word();
+  if (!p.err) return FLYB200_ERR_CUDA;
+  p.M = T; p.N = I; p.K = H; p.a_box_rows = 0;
+  p.sorted_ids = sorted_ids; p.expert_ids = expert_ids; p.sorted_weights = sorted_weights;
+  p.num_valid = num_valid_ids; p.topk = k; p.tile_m = tile_m; p.num_blocks = num_blocks;
+  p.experts = E; p.doweight = doweight; p.accumulate = 0;
+  CUtensorMap tmap{};
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (out_dtype == FLYB200_BF16) return launch_bn<kMoe1, __nv_bfloat16>(bn, tmap, p, grid, st);
+  return launch_bn<kMoe1, __half>(bn, tmap, p, grid, st);
+}
+
+extern "C" int flyb200_moe_gemm2(void* out, const void* a2, const void* w_repacked,
+                                 const float* scale_x, const float* scale_w,
+                                 const int32_t* sorted_ids, const int32_t* expert_ids,
+                                 const float* sorted_weights, const int32_t* num_valid_ids,
+                                 int32_t T, int32_t H, int32_t I, int32_t num_blocks, int32_t E,
+                                 int32_t k, int32_t tile_m, int32_t doweight, int32_t accumulate,
+                                 int32_t out_dtype, const flyb200_gemm_cfg* cfg, void* stream) {
+  int rc = moe_common_checks(out, a2, w_repacked, scale_x, scale_w, sorted_ids, expert_ids,
+                             sorted_weights, num_valid_ids, T, H, I, num_blocks, E, k, tile_m,
+                             doweight);
+  if (rc) return rc;
+  if (out_dtype != FLYB200_BF16 && out_dtype != FLYB200_F16 && out_dtype != FLYB200_F32)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "stage-2 out_dtype must be BF16, F16 or F32");
+  if (num_blocks == 0) return FLYB200_OK;
+  const int sms = sm_count();
+  if (sms <= 0) return FLYB200_ERR_CUDA;
+  int bn = (cfg && cfg->block_n) ? cfg->block_n : pick_block_n(num_blocks, H, sms, false);
+  int grid = sms;
+  if (cfg && cfg->max_ctas > 0 && cfg->max_ctas < grid) grid = cfg->max_ctas;
+  const long tiles = static_cast<long>(num_blocks) * cdiv(H, bn);
+  if (tiles < grid) grid = static_cast<int>(tiles);
+
+  GemmParams p{};
+  p.a = reinterpret_cast<const uint8_t*>(a2);
+  p.b = reinterpret_cast<const uint8_t*>(w_repacked);
+  p.scale_a = scale_x; p.scale_b = scale_w; p.out = out;
+  p.err = device_error_word();
+  if (!p.err) return FLYB200_ERR_CUDA;
+  p.M = T; p.N = H; p.K = I; p.a_box_rows = 0;
+  p.sorted_ids = sorted_ids; p.expert_ids = expert_ids; p.sorted_weights = sorted_weights;
+  p.num_valid = num_valid_ids; p.topk = k; p.tile_m = tile_m; p.num_blocks = num_blocks;
+  p.experts = E; p.doweight = doweight; p.accumulate = accumulate ? 1 : 0;
+  CUtensorMap tmap{};
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (out_dtype == FLYB200_BF16) return launch_bn<kMoe2, __nv_bfloat16>(bn, tmap, p, grid, st);
+  if (out_dtype == FLYB200_F16) return launch_bn<kMoe2, __half>(bn, tmap, p, grid, st);
+  return launch_bn<kMoe2, float>(bn, tmap, p, grid, st);
+}

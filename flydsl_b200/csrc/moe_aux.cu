@@ -1,0 +1,187 @@
+// Bandwidth-bound helpers around the MoE GEMMs:
+//   * top-k reduce  Y[t,d] = sum_s X[t,s,d]           (compile_moe_reduction,
+//                                                       kernels/moe_blockscale_2stage.py:2446-2638)
+//   * 1x128 group quantiser to fp8 e4m3 with transposed scales (the re-quantisation between the
+//     stages, tests/kernels/test_moe_blockscale.py:346-361 + pertoken_quant tests/utils.py:29-73)
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace flyb200 {
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// One thread owns VEC consecutive d for one token and walks the k slots in order (fixed summation
+// order => deterministic). 16-byte loads.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_reduce_kernel(const T* __restrict__ x, T* __restrict__ y, const uint8_t* __restrict__ mask,
+                  int tokens, int k, int H) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int vec_per_row = H / VEC;
+  const int64_t total = static_cast<int64_t>(tokens) * vec_per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i / vec_per_row);
+    const int v = static_cast<int>(i - static_cast<int64_t>(t) * vec_per_row);
+    float acc[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+    for (int s = 0; s < k; ++s) {
+      if (mask && mask[t * k + s] == 0) continue;
+      const uint4 raw = *reinterpret_cast<const uint4*>(
+          x + (static_cast<int64_t>(t) * k + s) * H + static_cast<int64_t>(v) * VEC);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) acc[j] += to_f32<T>(e[j]);
+    }
+    uint4 outv;
+    T* o = reinterpret_cast<T*>(&outv);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) o[j] = from_f32<T>(acc[j]);
+    *reinterpret_cast<uint4*>(y + static_cast<int64_t>(t) * H + static_cast<int64_t>(v) * VEC) = outv;
+  }
+}
+
+// One warp per (row, 128-wide group): lane owns 4 consecutive elements.
+template <typename T>
+__global__ void __launch_bounds__(256)
+quant_1x128_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale_t,
+                   int64_t rows, int cols) {
+  const int groups = cols / 128;
+  const int64_t total = rows * groups;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t w = warp0; w < total; w += nwarps) {
+    const int64_t row = w / groups;
+    const int g = static_cast<int>(w - row * groups);
+    const T* src = x + row * cols + g * 128 + lane * 4;
+    float v[4];
+    if constexpr (sizeof(T) == 4) {
+      const float4 raw = *reinterpret_cast<const float4*>(src);
+      v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+    } else {
+      const uint2 raw = *reinterpret_cast<const uint2*>(src);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = to_f32<T>(e[j]);
+    }
+    // NaN -> 0, +-Inf -> +-448, as pertoken_quant's nan_to_num does.
+    float vmax = -3.4e38f, vmin = 3.4e38f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (v[j] != v[j]) v[j] = 0.f;
+      else if (isinf(v[j])) v[j] = v[j] > 0 ? 448.f : -448.f;
+      vmax = fmaxf(vmax, v[j]);
+      vmin = fminf(vmin, v[j]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+      vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, o));
+    }
+    const float amax = fmaxf(vmax, -vmin);
+    float scale = __fdiv_rn(amax, 448.f);
+    if (scale == 0.f) scale = 1.f;
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_fp8_storage_t b =
+          __nv_cvt_float_to_fp8(__fdiv_rn(v[j], scale), __NV_SATFINITE, __NV_E4M3);
+      packed |= static_cast<uint32_t>(b) << (8 * j);
+    }
+    *reinterpret_cast<uint32_t*>(q + row * cols + g * 128 + lane * 4) = packed;
+    if (lane == 0) scale_t[static_cast<int64_t>(g) * rows + row] = scale;
+  }
+}
+
+}  // namespace flyb200
+
+using namespace flyb200;
+
+extern "C" int flyb200_moe_reduce(const void* x, void* y, const uint8_t* valid_mask, int32_t T,
+                                  int32_t k, int32_t H, int32_t dtype, void* stream) {
+  if (!x || !y) return set_error(FLYB200_ERR_INVALID_ARGUMENT, "moe_reduce: NULL buffer");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "moe_reduce: buffers must be 16-byte aligned");
+  if (T < 0 || k < 1 || H < 8)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "moe_reduce: bad sizes T=%d k=%d H=%d", T, k, H);
+  const int vec = dtype == FLYB200_F32 ? 4 : 8;
+  if (H % vec) return set_error(FLYB200_ERR_INVALID_ARGUMENT, "moe_reduce: H %% %d != 0", vec);
+  if (T == 0) return FLYB200_OK;
+  const int sms = sm_count();
+  if (sms <= 0) return FLYB200_ERR_CUDA;
+  const int64_t total = static_cast<int64_t>(T) * (H / vec);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > static_cast<int64_t>(sms) * 16) blocks = static_cast<int64_t>(sms) * 16;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int g = static_cast<int>(blocks);
+  switch (dtype) {
+    case FLYB200_BF16:
+      moe_reduce_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(
+          static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), valid_mask, T, k, H);
+      break;
+    case FLYB200_F16:
+      moe_reduce_kernel<__half><<<g, 256, 0, st>>>(static_cast<const __half*>(x),
+                                                   static_cast<__half*>(y), valid_mask, T, k, H);
+      break;
+    case FLYB200_F32:
+      moe_reduce_kernel<float><<<g, 256, 0, st>>>(static_cast<const float*>(x),
+                                                  static_cast<float*>(y), valid_mask, T, k, H);
+      break;
+    default:
+      return set_error(FLYB200_ERR_INVALID_ARGUMENT, "moe_reduce: bad dtype %d", dtype);
+  }
+  FLYB200_CUDA_CHECK(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+extern "C" int flyb200_quant_1x128(const void* x, void* q, float* scale_t, int64_t rows,
+                                   int32_t cols, int32_t in_dtype, void* stream) {
+  if (!x || !q || !scale_t) return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant: NULL buffer");
+  if ((reinterpret_cast<uintptr_t>(x) % 16) || (reinterpret_cast<uintptr_t>(q) % 4))
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant: x must be 16-byte, q 4-byte aligned");
+  if (rows < 0 || cols < 128 || cols % 128)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant: cols (%d) must be a multiple of 128", cols);
+  if (rows == 0) return FLYB200_OK;
+  const int sms = sm_count();
+  if (sms <= 0) return FLYB200_ERR_CUDA;
+  const int64_t warps = rows * (cols / 128);
+  int64_t blocks = (warps + 7) / 8;
+  if (blocks > static_cast<int64_t>(sms) * 16) blocks = static_cast<int64_t>(sms) * 16;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int g = static_cast<int>(blocks);
+  uint8_t* qo = static_cast<uint8_t*>(q);
+  switch (in_dtype) {
+    case FLYB200_BF16:
+      quant_1x128_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), qo,
+                                                           scale_t, rows, cols);
+      break;
+    case FLYB200_F16:
+      quant_1x128_kernel<__half><<<g, 256, 0, st>>>(static_cast<const __half*>(x), qo, scale_t,
+                                                    rows, cols);
+      break;
+    case FLYB200_F32:
+      quant_1x128_kernel<float><<<g, 256, 0, st>>>(static_cast<const float*>(x), qo, scale_t, rows,
+                                                   cols);
+      break;
+    default:
+      return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant: bad in_dtype %d", in_dtype);
+  }
+  FLYB200_CUDA_CHECK(cudaGetLastError());
+  return FLYB200_OK;
+}

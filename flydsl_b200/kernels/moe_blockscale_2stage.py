@@ -1,0 +1,284 @@
+"""Two-stage FP8 block-scale MoE behind the reference's factory signatures
+(kernels/moe_blockscale_2stage.py of the reference).
+
+compile_moe_blockscale_gemm1     reference :74-89   -> launcher args of :1165-1214
+compile_moe_blockscale_gemm2     reference :1219-1238 -> launcher args of :2390-2440
+compile_moe_reduction            reference :2446-2638
+MoeGemm2Mode / compile_moe_blockscale_gemm2_ex   reference :2642-2826
+
+The factories validate like the reference, are ``functools.lru_cache``d like the reference, and
+return launchers that forward to the prebuilt CUDA library; nothing is compiled at run time.
+"""
+from __future__ import annotations
+
+import ctypes
+import functools
+import logging
+
+from .. import _lib
+
+_OUT_CODES = {
+    "f16": _lib.F16, "fp16": _lib.F16, "half": _lib.F16,
+    "bf16": _lib.BF16, "bfloat16": _lib.BF16,
+    "f32": _lib.F32, "fp32": _lib.F32, "float": _lib.F32,
+}
+
+
+def _cfg(block_n):
+    cfg = _lib.GemmCfg(int(block_n or 0), 0, 0, 0)
+    return cfg, ctypes.byref(cfg)
+
+
+class MoeGemm1Launcher:
+    """``fn(out, x, w, scale_x, scale_w, sorted_token_ids, expert_ids, sorted_weights,
+    max_token_ids, tokens, inter, k, size_expert_ids, stream)``.
+
+    out f16/bf16 ``[tokens, topk, inter]``; x fp8 ``[tokens, model_dim]``; w fp8 repacked
+    ``[E, 2*inter, model_dim]`` (gate rows then up rows per expert); scale_x f32
+    ``[model_dim/128, tokens]``; scale_w f32 ``[E*(2*inter/128), model_dim/128]``.
+    """
+
+    def __init__(self, model_dim, inter_dim, experts, topk, tile_m, doweight, out_code, block_n):
+        self.model_dim, self.inter_dim = int(model_dim), int(inter_dim)
+        self.experts, self.topk, self.tile_m = int(experts), int(topk), int(tile_m)
+        self.doweight, self.out_code = int(bool(doweight)), out_code
+        self._cfg, self._cfg_ref = _cfg(block_n)
+        self._fn = _lib.load().flyb200_moe_gemm1
+
+    def __call__(self, out, x, w, scale_x, scale_w, sorted_token_ids, expert_ids, sorted_weights,
+                 max_token_ids, tokens, inter, k, size_expert_ids, stream=None):
+        if int(inter) != self.inter_dim or int(k) != self.model_dim:
+            raise ValueError(f"launcher was built for inter_dim={self.inter_dim}, model_dim={self.model_dim}; "
+                             f"got inter={inter}, k={k}")
+        _lib.check(self._fn(
+            out.data_ptr(), x.data_ptr(), w.data_ptr(), scale_x.data_ptr(), scale_w.data_ptr(),
+            sorted_token_ids.data_ptr(), expert_ids.data_ptr(), sorted_weights.data_ptr(),
+            max_token_ids.data_ptr(), int(tokens), self.inter_dim, self.model_dim,
+            int(size_expert_ids), self.experts, self.topk, self.tile_m, self.doweight,
+            self.out_code, self._cfg_ref, _lib.stream_handle(stream)))
+
+
+class MoeGemm2Launcher:
+    """``fn(out, x, w, scale_x, scale_w, sorted_token_ids, expert_ids, sorted_weights,
+    num_valid_ids, tokens, n, k, size_expert_ids, stream)``.
+
+    x fp8 ``[tokens*topk, inter]``; w fp8 repacked ``[E, model_dim, inter]``; scale_x f32
+    ``[inter/128, tokens*topk]``; scale_w f32 ``[E*(model_dim/128), inter/128]``. With
+    ``accumulate=True`` out is ``[tokens, model_dim]``, pre-zeroed by the caller, and routes are
+    added atomically; with ``accumulate=False`` out is ``[tokens*topk, model_dim]``.
+    """
+
+    def __init__(self, model_dim, inter_dim, experts, topk, tile_m, doweight, accumulate, out_code,
+                 block_n):
+        self.model_dim, self.inter_dim = int(model_dim), int(inter_dim)
+        self.experts, self.topk, self.tile_m = int(experts), int(topk), int(tile_m)
+        self.doweight, self.accumulate, self.out_code = int(bool(doweight)), int(bool(accumulate)), out_code
+        self._cfg, self._cfg_ref = _cfg(block_n)
+        self._fn = _lib.load().flyb200_moe_gemm2
+
+    def __call__(self, out, x, w, scale_x, scale_w, sorted_token_ids, expert_ids, sorted_weights,
+                 num_valid_ids, tokens, n, k, size_expert_ids, stream=None):
+        if int(n) != self.model_dim or int(k) != self.inter_dim:
+            raise ValueError(f"launcher was built for model_dim={self.model_dim}, inter_dim={self.inter_dim}; "
+                             f"got n={n}, k={k}")
+        _lib.check(self._fn(
+            out.data_ptr(), x.data_ptr(), w.data_ptr(), scale_x.data_ptr(), scale_w.data_ptr(),
+            sorted_token_ids.data_ptr(), expert_ids.data_ptr(), sorted_weights.data_ptr(),
+            num_valid_ids.data_ptr(), int(tokens), self.model_dim, self.inter_dim,
+            int(size_expert_ids), self.experts, self.topk, self.tile_m, self.doweight,
+            self.accumulate, self.out_code, self._cfg_ref, _lib.stream_handle(stream)))
+
+
+class MoeReduceLauncher:
+    """``fn(X, Y, valid_mask, m_tokens, stream)``: ``Y[t,d] = sum_s X[t,s,d]`` (f32 accumulate)."""
+
+    def __init__(self, topk, model_dim, dtype_code, use_mask):
+        self.topk, self.model_dim = int(topk), int(model_dim)
+        self.dtype_code, self.use_mask = dtype_code, bool(use_mask)
+        self._fn = _lib.load().flyb200_moe_reduce
+
+    def __call__(self, X, Y, valid_mask, m_tokens, stream=None):
+        mask_ptr = None
+        if self.use_mask:
+            if valid_mask is None or valid_mask.numel() != int(m_tokens) * self.topk:
+                raise ValueError("use_mask=True needs valid_mask [tokens, topk]")
+            if valid_mask.element_size() != 1:
+                raise ValueError("valid_mask must be a 1-byte dtype (uint8/int8/bool)")
+            mask_ptr = valid_mask.data_ptr()
+        _lib.check(self._fn(X.data_ptr(), Y.data_ptr(), mask_ptr, int(m_tokens), self.topk,
+                            self.model_dim, self.dtype_code, _lib.stream_handle(stream)))
+
+
+def _check_tiles(tile_m, tile_k, scale_block_k):
+    if int(tile_k) % 64 != 0:
+        raise ValueError(f"tile_k_bytes must be divisible by 64, got tile_k_bytes={tile_k} "
+                         f"(tile_k={tile_k}, elem_bytes=1)")
+    if int(scale_block_k) != 128:
+        raise ValueError(f"scale_block_k must be 128 on this build, got {scale_block_k}")
+    if not 1 <= int(tile_m) <= 128:
+        raise ValueError(f"tile_m must be in [1, 128] (one routing block per 128-row MMA tile), got {tile_m}")
+
+
+@functools.lru_cache(maxsize=1024)
+def compile_moe_blockscale_gemm1(
+    *,
+    model_dim: int,
+    inter_dim: int,
+    experts: int,
+    topk: int,
+    tile_m: int,
+    tile_n: int,
+    tile_k: int,
+    doweight_stage1: bool,
+    scale_block_k: int = 128,
+    out_dtype: str = "f16",
+    use_cshuffle_epilog=None,
+    waves_per_eu=None,
+    block_n=None,
+):
+    """Stage 1: ``out[t, slot, :] = silu(x[t] @ Wgate[e]^T) * (x[t] @ Wup[e]^T)`` (optionally times
+    the route weight). ``tile_m`` must equal the block size the routing buffers were sorted with;
+    ``tile_n/tile_k`` are validated only; ``block_n`` (64/128/256 = gate+up MMA width) overrides
+    the heuristic. ``use_cshuffle_epilog`` / ``waves_per_eu`` are AMD switches, ignored."""
+    if out_dtype not in ("f16", "bf16"):
+        raise ValueError(f"out_dtype must be 'f16' or 'bf16', got {out_dtype!r}")
+    _check_tiles(tile_m, tile_k, scale_block_k)
+    if model_dim % scale_block_k != 0:
+        raise ValueError(f"model_dim ({model_dim}) must be divisible by scale_block_k ({scale_block_k})")
+    if inter_dim % 128 != 0:
+        raise ValueError(f"inter_dim ({inter_dim}) must be divisible by 128 (ScaleBlockN)")
+    if block_n not in (None, 0, 64, 128, 256):
+        raise ValueError(f"block_n must be one of 64, 128, 256, got {block_n}")
+    return MoeGemm1Launcher(model_dim, inter_dim, experts, topk, tile_m, doweight_stage1,
+                            _OUT_CODES[out_dtype], block_n)
+
+
+@functools.lru_cache(maxsize=1024)
+def compile_moe_blockscale_gemm2(
+    *,
+    model_dim: int,
+    inter_dim: int,
+    experts: int,
+    topk: int,
+    tile_m: int,
+    tile_n: int,
+    tile_k: int,
+    doweight_stage2: bool,
+    scale_block_k: int = 128,
+    out_dtype: str = "f16",
+    use_cshuffle_epilog=None,
+    accumulate: bool = True,
+    waves_per_eu=None,
+    block_n=None,
+):
+    """Stage 2: ``A2[t*topk+slot] @ W2[e]^T`` (times the route weight when ``doweight_stage2``),
+    atomically added into ``out[t]`` (``accumulate=True``) or stored per route."""
+    out_s = str(out_dtype).strip().lower()
+    if out_s not in _OUT_CODES:
+        raise ValueError(f"out_dtype must be 'f16', 'bf16', or 'f32', got {out_dtype!r}")
+    out_code = _OUT_CODES[out_s]
+    if (not bool(accumulate)) and out_code == _lib.F32:
+        raise ValueError("compile_moe_blockscale_gemm2(accumulate=False) only supports out_dtype in {'f16','bf16'}")
+    _check_tiles(tile_m, tile_k, scale_block_k)
+    if inter_dim % scale_block_k != 0:
+        raise ValueError(f"inter_dim ({inter_dim}) must be divisible by scale_block_k ({scale_block_k})")
+    if model_dim % 128 != 0:
+        raise ValueError(f"model_dim ({model_dim}) must be divisible by 128 (ScaleBlockN)")
+    if block_n not in (None, 0, 32, 64, 128, 256):
+        raise ValueError(f"block_n must be one of 32, 64, 128, 256, got {block_n}")
+    return MoeGemm2Launcher(model_dim, inter_dim, experts, topk, tile_m, doweight_stage2,
+                            accumulate, out_code, block_n)
+
+
+@functools.lru_cache(maxsize=1024)
+def compile_moe_reduction(*, topk: int, model_dim: int, dtype_str: str = "f16", use_mask: bool = False):
+    """Reduction over the top-k slots, the companion of ``accumulate=False`` stage 2."""
+    ds = str(dtype_str).strip().lower()
+    if ds not in _OUT_CODES:
+        raise ValueError(f"dtype_str must be 'f16', 'bf16' or 'f32', got {dtype_str!r}")
+    return MoeReduceLauncher(topk, model_dim, _OUT_CODES[ds], use_mask)
+
+
+class MoeGemm2Mode:
+    """Execution mode for stage 2."""
+
+    ATOMIC = "atomic"  # atomic accumulation into [tokens, model_dim]
+    REDUCE = "reduce"  # per-route store, then a fixed-order reduce (deterministic)
+
+
+class _MoeGemm2ReduceWrapper:
+    """Stage 2 without atomics followed by the top-k reduce; allocates the ``[tokens*topk,
+    model_dim]`` intermediate per call, like the reference wrapper (:2709-2715)."""
+
+    def __init__(self, gemm2_exe, reduce_exe, topk, model_dim, out_dtype_str="f16", use_mask=False):
+        self._gemm2_exe, self._reduce_exe = gemm2_exe, reduce_exe
+        self._topk, self._model_dim = int(topk), int(model_dim)
+        self._out_dtype_str, self._use_mask = out_dtype_str, bool(use_mask)
+
+    def _get_torch_dtype(self):
+        import torch
+
+        return {"f16": torch.float16, "fp16": torch.float16, "bf16": torch.bfloat16,
+                "f32": torch.float32}.get(self._out_dtype_str, torch.float16)
+
+    def __call__(self, arg_out, arg_x, arg_w, arg_scale_x, arg_scale_w, arg_sorted_token_ids,
+                 arg_expert_ids, arg_sorted_weights, arg_num_valid_ids, tokens_in, n_in, k_in,
+                 size_expert_ids_in, valid_mask=None, stream=None):
+        import torch
+
+        if stream is None:
+            stream = torch.cuda.current_stream()
+        inter = torch.empty(tokens_in * self._topk, self._model_dim, device=arg_out.device,
+                            dtype=self._get_torch_dtype())
+        if not self._use_mask:
+            inter.zero_()
+        self._gemm2_exe(inter.view(-1), arg_x, arg_w, arg_scale_x, arg_scale_w,
+                        arg_sorted_token_ids, arg_expert_ids, arg_sorted_weights, arg_num_valid_ids,
+                        tokens_in, n_in, k_in, size_expert_ids_in, stream)
+        if not self._use_mask and valid_mask is not None:
+            logging.warning("valid_mask provided but use_mask=False; ignoring valid_mask")
+        self._reduce_exe(inter.view(tokens_in, self._topk, self._model_dim),
+                         arg_out.view(tokens_in, self._model_dim),
+                         valid_mask if self._use_mask else None, tokens_in, stream)
+
+    @property
+    def mode(self) -> str:
+        return MoeGemm2Mode.REDUCE
+
+
+def compile_moe_blockscale_gemm2_ex(
+    *,
+    model_dim: int,
+    inter_dim: int,
+    experts: int,
+    topk: int,
+    tile_m: int,
+    tile_n: int,
+    tile_k: int,
+    doweight_stage2: bool,
+    in_dtype: str = "fp8",
+    out_dtype: str = "f16",
+    use_cshuffle_epilog=None,
+    mode: str = MoeGemm2Mode.ATOMIC,
+    valid_mask=None,
+):
+    """Stage 2 with explicit mode control. The reference's version forwards ``in_dtype=`` to a
+    factory that does not take it and so cannot be called as shipped (:2784, :2822); this one
+    accepts ``in_dtype="fp8"`` only and works."""
+    if in_dtype != "fp8":
+        raise ValueError(f"block-scale MoE is fp8-only, got in_dtype={in_dtype!r}")
+    common = dict(model_dim=model_dim, inter_dim=inter_dim, experts=experts, topk=topk,
+                  tile_m=tile_m, tile_n=tile_n, tile_k=tile_k, doweight_stage2=doweight_stage2,
+                  out_dtype=out_dtype, use_cshuffle_epilog=use_cshuffle_epilog)
+    if mode == MoeGemm2Mode.REDUCE:
+        use_mask = valid_mask is not None
+        gemm2_exe = compile_moe_blockscale_gemm2(accumulate=False, **common)
+        out_s = str(out_dtype).strip().lower()
+        dtype_str = "f16" if out_s in ("f16", "fp16", "half") else (
+            "bf16" if out_s in ("bf16", "bfloat16") else "f32")
+        reduce_exe = compile_moe_reduction(topk=topk, model_dim=model_dim, dtype_str=dtype_str,
+                                           use_mask=use_mask)
+        return _MoeGemm2ReduceWrapper(gemm2_exe, reduce_exe, topk, model_dim, dtype_str, use_mask)
+    if mode != MoeGemm2Mode.ATOMIC:
+        raise ValueError(f"mode must be 'atomic' or 'reduce', got {mode!r}")
+    return compile_moe_blockscale_gemm2(accumulate=True, **common)

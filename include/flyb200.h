@@ -1,0 +1,133 @@
+/*
+ * flyb200.h — C ABI of libflyb200.so: FP8 (e4m3) block-scale GEMM and two-stage block-scale MoE
+ * kernels for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point
+ *   - takes plain device pointers, sizes and a CUDA stream handle (cudaStream_t passed as void*;
+ *     NULL = the legacy default stream),
+ *   - enqueues work on that stream and returns without synchronising it,
+ *   - returns FLYB200_OK (0) or a negative flyb200_status; flyb200_last_error_string() describes
+ *     the last failure on the calling thread,
+ *   - allocates no device memory (workspaces, where needed, are caller-provided).
+ *
+ * Each declaration names the interface of the reference project (FlyDSL, paths relative to its
+ * root) that it stands in for.
+ *
+ * Conventions shared by all GEMM entry points (identical to the reference kernels):
+ *   activations   fp8 e4m3fn, row-major [rows, K]
+ *   act. scales   fp32, TRANSPOSED [K/128, rows]  (one scale per row per 128-wide K block)
+ *   weights       fp8 e4m3fn, repacked by flyb200_repack_weight_fp8 (NOT the reference's AMD layout)
+ *   weight scales fp32, [ceil(N/128), K/128] row-major (experts concatenated along N)
+ *   result        C[m,n] = sum_kb ( sum_{k in kb} A[m,k] * B[n,k] ) * sa[kb,m] * sb[n/128,kb]
+ *                 accumulated in fp32, rounded once to the output type.
+ */
+#ifndef FLYB200_H_
+#define FLYB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum flyb200_status {
+  FLYB200_OK = 0,
+  FLYB200_ERR_INVALID_ARGUMENT = -1, /* null pointer, misaligned pointer, bad size            */
+  FLYB200_ERR_UNSUPPORTED = -2,      /* legal in the reference but not built here             */
+  FLYB200_ERR_CUDA = -3,             /* a CUDA runtime / driver call failed                   */
+  FLYB200_ERR_WORKSPACE = -4,        /* caller workspace too small                            */
+  FLYB200_ERR_DEVICE_TIMEOUT = -5    /* a kernel gave up on a bounded wait (device error word) */
+} flyb200_status;
+
+typedef enum flyb200_dtype {
+  FLYB200_BF16 = 0,
+  FLYB200_F16 = 1,
+  FLYB200_F32 = 2
+} flyb200_dtype;
+
+/* Optional tuning knobs; a NULL pointer or zero fields select the built-in heuristic
+ * (role of select_tile_config, tests/kernels/test_blockscale_preshuffle_gemm.py:52-83). */
+typedef struct flyb200_gemm_cfg {
+  int32_t block_n;  /* MMA N / CTA tile width: 32, 64, 128 or 256; 0 = auto */
+  int32_t max_ctas; /* cap on the persistent grid; 0 = one CTA per SM       */
+  int32_t reserved0;
+  int32_t reserved1;
+} flyb200_gemm_cfg;
+
+/* Weight repack [batch, N, K] (row-major fp8 bytes) -> per batch [K/128][N/8][8 rows][128 B], the
+ * 128-byte-swizzled K-major shared-memory image that tcgen05.mma consumes, so a CTA fetches a
+ * (rows x 128 B) weight tile with one bulk copy. Same byte count in and out. N % 8 == 0,
+ * K % 128 == 0. Replaces shuffle_weight (tests/utils.py:76-96). */
+int flyb200_repack_weight_fp8(void* dst, const void* src, int64_t batch, int64_t N, int64_t K,
+                              void* stream);
+
+/* Dense block-scale GEMM. Replaces the launcher returned by compile_blockscale_preshuffle_gemm
+ * (kernels/blockscale_preshuffle_gemm.py:39-52, launch_gemm :842-876, kernel_gemm :161-839).
+ * c [M,N] out_dtype (BF16|F16); a [M,K]; b_repacked [N,K] repacked; scale_a_t [K/128, M];
+ * scale_b [ceil(N/128), K/128]. Any M >= 1; N % 16 == 0; K % 128 == 0. */
+int flyb200_blockscale_gemm(void* c, const void* a, const void* b_repacked, const float* scale_a_t,
+                            const float* scale_b, int32_t M, int32_t N, int32_t K,
+                            int32_t out_dtype, const flyb200_gemm_cfg* cfg, void* stream);
+
+/* MoE routing sort. Bit-exact stand-in for moe_sorting_torch_native
+ * (tests/kernels/test_moe_gemm.py:97-161) and the sorter half of build_routing_buffers (:223-295).
+ * topk_ids i32 [T,k]; topk_weights f32 [T,k]; expert_mask i32 [E] or NULL; num_local_tokens: < 0
+ * means all T tokens. Outputs: sorted_ids i32 [T*k + E*block_m - k] = (slot<<24)|token, padding =
+ * (k<<24)|T; sorted_weights f32 same length (padding rows get 0.0); sorted_expert_ids i32
+ * [ceil(len/block_m)] (-1 beyond the used blocks); num_valid_ids i32 [2] = {padded rows, T}. */
+int flyb200_moe_sort(const int32_t* topk_ids, const float* topk_weights, int32_t T, int32_t k,
+                     int32_t E, int32_t block_m, const int32_t* expert_mask,
+                     int32_t num_local_tokens, int32_t* sorted_ids, float* sorted_weights,
+                     int32_t* sorted_expert_ids, int32_t* num_valid_ids, void* stream);
+
+/* MoE stage 1: gather rows by sorted id, X * W1^T (gate rows [0,I), up rows [I,2I) per expert),
+ * out[(t*k+s), col] = silu(gate) * up [* route weight]. Replaces
+ * launch_moe_blockscale_gemm1 (kernels/moe_blockscale_2stage.py:1165-1214; factory :74-89).
+ * x [T,H]; w repacked [E, 2I, H]; scale_x [H/128, T]; scale_w [E*(2I/128), H/128];
+ * out [T,k,I] out_dtype (F16|BF16). tile_m = rows per routing block (<= 128). */
+int flyb200_moe_gemm1(void* out, const void* x, const void* w_repacked, const float* scale_x,
+                      const float* scale_w, const int32_t* sorted_ids, const int32_t* expert_ids,
+                      const float* sorted_weights, const int32_t* num_valid_ids, int32_t T,
+                      int32_t I, int32_t H, int32_t num_blocks, int32_t E, int32_t k,
+                      int32_t tile_m, int32_t doweight, int32_t out_dtype,
+                      const flyb200_gemm_cfg* cfg, void* stream);
+
+/* MoE stage 2: gather rows (t*k+s) of a2, A2 * W2^T, [* route weight], then either atomically add
+ * into out[t, col] (accumulate != 0; caller zeroes out) or store to out[(t*k+s), col]. Replaces
+ * launch_moe_blockscale_gemm2 (kernels/moe_blockscale_2stage.py:2390-2440; factory :1219-1238).
+ * a2 [T*k, I]; w repacked [E, H, I]; scale_x [I/128, T*k]; scale_w [E*(H/128), I/128];
+ * out out_dtype (F16|BF16|F32). */
+int flyb200_moe_gemm2(void* out, const void* a2, const void* w_repacked, const float* scale_x,
+                      const float* scale_w, const int32_t* sorted_ids, const int32_t* expert_ids,
+                      const float* sorted_weights, const int32_t* num_valid_ids, int32_t T,
+                      int32_t H, int32_t I, int32_t num_blocks, int32_t E, int32_t k,
+                      int32_t tile_m, int32_t doweight, int32_t accumulate, int32_t out_dtype,
+                      const flyb200_gemm_cfg* cfg, void* stream);
+
+/* Y[t,d] = sum_s X[t,s,d] (fp32 accumulate, slot order 0..k-1), optional u8 mask [T,k].
+ * Replaces the launcher of compile_moe_reduction (kernels/moe_blockscale_2stage.py:2446-2638). */
+int flyb200_moe_reduce(const void* x, void* y, const uint8_t* valid_mask, int32_t T, int32_t k,
+                       int32_t H, int32_t dtype, void* stream);
+
+/* 1x128 group quantiser: x [rows, cols] (in_dtype) -> q fp8 e4m3fn [rows, cols] and
+ * scale_t f32 [cols/128, rows]; scale = amax/448 (0 -> 1). Replaces the host re-quantisation between
+ * the MoE stages (tests/kernels/test_moe_blockscale.py:346-361, pertoken_quant tests/utils.py:29-73). */
+int flyb200_quant_1x128(const void* x, void* q, float* scale_t, int64_t rows, int32_t cols,
+                        int32_t in_dtype, void* stream);
+
+/* Reads and clears the device error word of the current device after synchronising `stream`.
+ * *code_out = 0 when no kernel reported a problem. The reference only prints GPU errors
+ * (lib/Runtime/FlyRocmRuntimeWrappers.cpp:22-30); this is the status-returning equivalent. */
+int flyb200_query_device_error(void* stream, int32_t* code_out);
+
+/* Text for the last non-OK status returned on this thread ("" if none). */
+const char* flyb200_last_error_string(void);
+
+/* Library version, major*10000 + minor*100 + patch. */
+int flyb200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLYB200_H_ */

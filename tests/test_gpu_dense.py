@@ -1,0 +1,119 @@
+"""Dense FP8 block-scale GEMM on the GPU, through the reference-shaped Python API (which calls the
+C ABI), against the golden vectors and the CPU oracle."""
+import pytest
+import torch
+
+from oracle import blockscale_ref as O
+from tests.helpers import assert_close_to_oracle, bf16_from_bits, fp8_from_u8, load_golden
+
+pytestmark = pytest.mark.gpu
+
+
+def _run_dense(a_q, a_scale, b_q, b_scale, out_dtype="bf16", block_n=None, tiles=(64, 128, 128)):
+    from flydsl_b200 import _lib
+    from flydsl_b200.kernels import compile_blockscale_preshuffle_gemm
+    from flydsl_b200.utils import shuffle_weight
+
+    dev = torch.device("cuda")
+    M, K = a_q.shape
+    N = b_q.shape[0]
+    fn = compile_blockscale_preshuffle_gemm(M=M, N=N, K=K, tile_m=tiles[0], tile_n=tiles[1], tile_k=tiles[2],
+                                            out_dtype=out_dtype, block_n=block_n)
+    tdt = torch.bfloat16 if out_dtype == "bf16" else torch.float16
+    c = torch.zeros((M, N), dtype=tdt, device=dev)
+    b_sh = shuffle_weight(b_q.to(dev))
+    sa_t = a_scale.to(dev).t().contiguous().view(-1)
+    sb = b_scale.to(dev).contiguous().view(-1)
+    fn(c, a_q.to(dev), b_sh, sa_t, sb, M, N, torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    assert _lib.query_device_error() == 0
+    return c
+
+
+def test_repack_matches_layout_oracle():
+    from flydsl_b200.utils import shuffle_weight
+
+    g = torch.Generator().manual_seed(1)
+    w = torch.randint(0, 256, (3, 48, 384), generator=g, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    got = shuffle_weight(w.cuda()).cpu()
+    want = O.repack_weight_ref(w)
+    assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
+    assert getattr(shuffle_weight(w.cuda()), "is_shuffled", False)
+
+
+@pytest.mark.parametrize("tag", ["a", "b", "c", "q"])
+@pytest.mark.parametrize("block_n", [None, 32, 64, 128, 256])
+def test_dense_vs_golden(tag, block_n):
+    g = load_golden("dense.npz")
+    x, w = fp8_from_u8(g[f"{tag}_x"]), fp8_from_u8(g[f"{tag}_w"])
+    xs, ws = torch.from_numpy(g[f"{tag}_xs"]), torch.from_numpy(g[f"{tag}_ws"])
+    c = _run_dense(x, xs, w, ws, block_n=block_n)
+    assert_close_to_oracle(c, bf16_from_bits(g[f"{tag}_c_bf16_bits"]), f"golden {tag} bn={block_n}")
+
+
+# The reference's own test grid (tests/kernels/test_blockscale_preshuffle_gemm.py:121-142), trimmed to
+# what the CPU oracle finishes in seconds, plus BASELINE config 1.
+@pytest.mark.parametrize("M", [1, 7, 16, 33, 64, 256])
+@pytest.mark.parametrize("N,K", [(7168, 2304), (2112, 7168), (3072, 1536)])
+@pytest.mark.parametrize("out_dtype", ["bf16", "fp16"])
+def test_dense_reference_shapes(M, N, K, out_dtype):
+    case = O.make_dense_case(M, N, K, seed=M + N)
+    ref = O.run_torch_blockscale(case["a_q"], case["b_q"], case["a_scale"], case["b_scale"], dtype=torch.float32)
+    c = _run_dense(case["a_q"], case["a_scale"], case["b_q"], case["b_scale"], out_dtype=out_dtype)
+    assert_close_to_oracle(c, ref, f"M={M} N={N} K={K} {out_dtype}")
+
+
+def test_dense_config1_and_m_tail():
+    for (M, N, K) in [(128, 1536, 7168), (1024 + 5, 1536, 512)]:
+        case = O.make_dense_case(M, N, K, seed=0)
+        ref = O.run_torch_blockscale(case["a_q"], case["b_q"], case["a_scale"], case["b_scale"], dtype=torch.float32)
+        for bn in (None, 256):
+            c = _run_dense(case["a_q"], case["a_scale"], case["b_q"], case["b_scale"], block_n=bn)
+            assert_close_to_oracle(c, ref, f"M={M} N={N} K={K} bn={bn}")
+
+
+def test_dense_is_deterministic_and_stream_forms():
+    from flydsl_b200.kernels import compile_blockscale_preshuffle_gemm
+    from flydsl_b200.utils import shuffle_weight
+    import flydsl_b200 as flyc
+
+    case = O.make_dense_case(96, 512, 1024, seed=5)
+    dev = torch.device("cuda")
+    fn = compile_blockscale_preshuffle_gemm(M=96, N=512, K=1024, tile_m=32, tile_n=128, tile_k=128)
+    a, b = case["a_q"].to(dev), shuffle_weight(case["b_q"].to(dev))
+    sa, sb = case["a_scale"].to(dev).t().contiguous().view(-1), case["b_scale"].to(dev).view(-1)
+    outs = []
+    side = torch.cuda.Stream()
+    for stream in (None, torch.cuda.current_stream(), torch.cuda.current_stream().cuda_stream, side):
+        c = torch.zeros((96, 512), dtype=torch.bfloat16, device=dev)
+        if stream is side:
+            side.wait_stream(torch.cuda.current_stream())
+        fn(c, a, b, sa, sb, 96, 512, stream)
+        torch.cuda.synchronize()
+        outs.append(c)
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+    # flyc.compile-style pre-binding and CUDA-graph capture, as the reference's tests exercise
+    c = torch.zeros((96, 512), dtype=torch.bfloat16, device=dev)
+    exe = flyc.compile(fn, c, a, b, sa, sb, 96, 512, torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    c.zero_()
+    with torch.cuda.graph(graph):
+        exe(c, a, b, sa, sb, 96, 512, torch.cuda.current_stream())
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(c, outs[0])
+
+
+def test_dense_bad_arguments_raise():
+    from flydsl_b200.kernels import compile_blockscale_preshuffle_gemm
+
+    with pytest.raises(ValueError):
+        compile_blockscale_preshuffle_gemm(M=8, N=128, K=256, tile_m=16, tile_n=64, tile_k=128, out_dtype="f32")
+    with pytest.raises(ValueError):
+        compile_blockscale_preshuffle_gemm(M=8, N=128, K=200, tile_m=16, tile_n=64, tile_k=128)
+    fn = compile_blockscale_preshuffle_gemm(M=8, N=128, K=256, tile_m=16, tile_n=64, tile_k=128)
+    z = torch.zeros(8 * 256, dtype=torch.uint8, device="cuda")
+    with pytest.raises(ValueError):  # misaligned output pointer is rejected by the C ABI, nothing launches
+        fn(z[1:], z, z, z.view(torch.float32), z.view(torch.float32), 8, 128, None)
