@@ -182,8 +182,11 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
   const TileWalker<BN, MODE> walk(p);
   const int KB = p.K / BK;
 
+  // Register re-balancing. setmaxnreg.inc blocks until the CTA's own pool (registers per thread at
+  // launch x 384 threads = 168 x 384) can satisfy it, so the totals after the exchange must fit in
+  // that pool: 40 x 128 + 224 x 256 = 62464 <= 64512.
   if (warp < kEpiWarp0) {
-    reg_dealloc<48>();
+    reg_dealloc<40>();
     if (warp == 0 && lane == 0) {
       // ---------------- producer: weights (and dense A) via TMA ----------------
       uint32_t it = 0;
@@ -343,7 +346,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
     }
   } else {
     // ---------------- epilogue warps: scale promotion + output ----------------
-    reg_alloc<232>();
+    reg_alloc<224>();
     const int ew = warp - kEpiWarp0;
     const int quad = warp & 3;   // TMEM lane quadrant this warp may read
     const int half = ew >> 2;    // which CH-wide slice of each column group

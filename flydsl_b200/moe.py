@@ -1,0 +1,127 @@
+"""Two-stage block-scale MoE layer assembled from the reference-shaped launchers.
+
+The reference ships the two stage kernels and leaves the chaining to its test
+(tests/kernels/test_moe_blockscale.py:293-380): routing sort -> stage 1 -> 1x128 re-quantisation ->
+stage 2 (-> top-k reduce). ``BlockscaleMoE`` is that chain with persistent buffers, so a step
+launches kernels only (sort, gemm1, quant, gemm2[, reduce]) and allocates nothing after warm-up.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .kernels.moe_blockscale_2stage import (
+    compile_moe_blockscale_gemm1,
+    compile_moe_blockscale_gemm2,
+    compile_moe_reduction,
+)
+from .utils import moe_sorting, quant_1x128, shuffle_weight
+
+_DT_NAME = {torch.float16: "f16", torch.bfloat16: "bf16", torch.float32: "f32"}
+
+
+def _as_torch_stream(stream):
+    """torch.cuda.Stream | raw handle | None -> a torch stream object."""
+    if stream is None:
+        return torch.cuda.current_stream()
+    if isinstance(stream, int):
+        return torch.cuda.ExternalStream(stream)
+    return stream
+
+
+class BlockscaleMoE:
+    """Expert weights (already repacked) plus the launchers and scratch buffers for one layer.
+
+    w1 fp8 ``[E, 2*I, H]`` repacked (gate rows then up rows), w1_scale f32 ``[E, (2I/128)*(H/128)]``;
+    w2 fp8 ``[E, H, I]`` repacked, w2_scale f32 ``[E, (H/128)*(I/128)]``.
+    ``mode``: "reduce" (per-route store + fixed-order reduce, deterministic) or "atomic".
+    """
+
+    def __init__(self, w1, w1_scale, w2, w2_scale, *, topk: int, tile_m: int = 128,
+                 mid_dtype=torch.float16, out_dtype=torch.bfloat16, mode: str = "reduce",
+                 block_n1: Optional[int] = None, block_n2: Optional[int] = None):
+        if mode not in ("reduce", "atomic"):
+            raise ValueError(f"mode must be 'reduce' or 'atomic', got {mode!r}")
+        self.E, two_i, self.H = w1.shape
+        self.I = two_i // 2
+        if tuple(w2.shape) != (self.E, self.H, self.I):
+            raise ValueError(f"w2 shape {tuple(w2.shape)} does not match w1 {tuple(w1.shape)}")
+        self.w1, self.w2 = w1, w2
+        self.w1_scale = w1_scale.contiguous().view(-1)
+        self.w2_scale = w2_scale.contiguous().view(-1)
+        self.topk, self.tile_m, self.mode = int(topk), int(tile_m), mode
+        self.mid_dtype, self.out_dtype = mid_dtype, out_dtype
+        common = dict(model_dim=self.H, inter_dim=self.I, experts=self.E, topk=self.topk,
+                      tile_m=self.tile_m, tile_n=256, tile_k=128)
+        self.gemm1 = compile_moe_blockscale_gemm1(doweight_stage1=False, out_dtype=_DT_NAME[mid_dtype],
+                                                  block_n=block_n1, **common)
+        self.gemm2 = compile_moe_blockscale_gemm2(doweight_stage2=True, out_dtype=_DT_NAME[out_dtype],
+                                                  accumulate=(mode == "atomic"), block_n=block_n2,
+                                                  **common)
+        self.reduce = compile_moe_reduction(topk=self.topk, model_dim=self.H,
+                                            dtype_str=_DT_NAME[out_dtype]) if mode == "reduce" else None
+        self._buf = {}
+
+    @classmethod
+    def from_unpacked(cls, w1_q, w1_scale, w2_q, w2_scale, **kw):
+        """Build from plain row-major fp8 weights (repacks them on the GPU)."""
+        return cls(shuffle_weight(w1_q), w1_scale, shuffle_weight(w2_q), w2_scale, **kw)
+
+    def _buffers(self, T: int, dev):
+        key = (T, dev)
+        b = self._buf.get(key)
+        if b is None:
+            b = {
+                "out1": torch.empty((T, self.topk, self.I), dtype=self.mid_dtype, device=dev),
+                "a2_q": torch.empty((T * self.topk, self.I), dtype=torch.float8_e4m3fn, device=dev),
+                "a2_s": torch.empty((self.I // 128, T * self.topk), dtype=torch.float32, device=dev),
+                "routes": torch.empty((T * self.topk, self.H), dtype=self.out_dtype, device=dev)
+                if self.mode == "reduce" else None,
+            }
+            self._buf[key] = b
+        return b
+
+    def forward(self, x_q, x_scale_t, topk_ids, topk_weights, out=None, stream=None,
+                routing=None):
+        """x_q fp8 ``[T, H]``; x_scale_t f32 ``[H/128, T]``; topk_ids i32 ``[T, k]``; topk_weights f32.
+        Returns ``out [T, H]``. ``routing`` may carry precomputed sort buffers
+        ``(sorted_ids, sorted_weights, sorted_expert_ids, num_valid_ids)``."""
+        with torch.cuda.stream(_as_torch_stream(stream)):
+            return self._forward(x_q, x_scale_t, topk_ids, topk_weights, out, routing)
+
+    def _forward(self, x_q, x_scale_t, topk_ids, topk_weights, out, routing):
+        # every launch below goes to torch's current stream (stream=None)
+        T = x_q.shape[0]
+        dev = x_q.device
+        b = self._buffers(T, dev)
+        if routing is None:
+            sid, sw, seid, npp = moe_sorting(topk_ids, topk_weights, num_experts=self.E,
+                                             block_size=self.tile_m)
+        else:
+            sid, sw, seid, npp = routing
+        nblk = seid.numel()
+        self.gemm1(b["out1"], x_q, self.w1, x_scale_t, self.w1_scale, sid, seid, sw, npp, T, self.I,
+                   self.H, nblk, None)
+        _lib.check(_lib.load().flyb200_quant_1x128(
+            b["out1"].data_ptr(), b["a2_q"].data_ptr(), b["a2_s"].data_ptr(), T * self.topk, self.I,
+            {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}[self.mid_dtype],
+            _lib.stream_handle(None)))
+        if out is None:
+            out = torch.empty((T, self.H), dtype=self.out_dtype, device=dev)
+        if self.mode == "atomic":
+            out.zero_()
+            self.gemm2(out, b["a2_q"], self.w2, b["a2_s"], self.w2_scale, sid, seid, sw, npp, T,
+                       self.H, self.I, nblk, None)
+        else:
+            self.gemm2(b["routes"], b["a2_q"], self.w2, b["a2_s"], self.w2_scale, sid, seid, sw, npp,
+                       T, self.H, self.I, nblk, None)
+            self.reduce(b["routes"], out, None, T, None)
+        return out
+
+    #: kernels one forward() launches (sort, gemm1, quant, gemm2, reduce | memset+gemm2)
+    @property
+    def launches_per_step(self) -> int:
+        return 5
+
