@@ -10,10 +10,11 @@
 //               each K block into a fresh TMEM accumulator buffer (two buffers, ping-pong)
 //   warps 2-3   MoE only: gather activation rows by sorted id with cp.async into the same swizzled
 //               image TMA would have produced
-//   warps 4-11  epilogue: tcgen05.ld the K-block partial, acc = fma(partial, sa*sb, acc) in fp32
-//               registers (the per-128-K scale promotion), release the TMEM buffer, and after the
-//               last K block convert and store (dense), SiLU(gate)*up (stage 1) or weight and
-//               scatter / atomically add (stage 2)
+//   warps 4-11  epilogue: tcgen05.ld the K-block partial (loads pipelined against the FMAs),
+//               acc = fma(partial, sa*sb, acc) in fp32 registers (the per-128-K scale promotion),
+//               release the TMEM buffer; after the last K block convert, stage the tile in shared
+//               memory and write it with TMA (dense) or with coalesced row stores / vector
+//               reductions to the scattered (token, slot) rows (MoE)
 //
 // The computation follows kernel_gemm / compute_tile_blockscale of the reference
 // (kernels/blockscale_preshuffle_gemm.py:161-839, :509-587) and the stage kernels of
@@ -26,7 +27,9 @@ constexpr int BM = 128;            // MMA M = accumulator lanes
 constexpr int BK = 128;            // K bytes per pipeline stage = one scale block
 constexpr int kThreads = 384;
 constexpr int kEpiWarp0 = 4;       // first epilogue warp
+constexpr int kEpiWarps = 8;
 constexpr int kATileBytes = BM * BK;
+constexpr int kRegionBytes = BM * 128;  // one 64-column (16-bit) slab of the staged output tile
 
 enum Mode : int { kDense = 0, kMoe1 = 1, kMoe2 = 2 };
 
@@ -54,25 +57,37 @@ struct GemmParams {
   int accumulate;
 };
 
-template <int BN>
+template <int BN, int MODE, typename OutT>
 struct Cfg {
+  static constexpr int kOutCols = (MODE == kMoe1) ? BN / 2 : BN;   // output columns per tile
+  // 16-bit outputs of tiles at least 64 wide go through a shared-memory staging tile.
+  static constexpr bool kStaged = (sizeof(OutT) == 2) && (kOutCols >= 32) && (BN >= 64);
+  static constexpr int kRegions = (kOutCols + 63) / 64;
+  static constexpr int kCBytes = kStaged ? kRegions * kRegionBytes : 0;
   static constexpr int kBTileBytes = BN * BK;
   static constexpr int kStageBytes = kATileBytes + kBTileBytes;
-  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128) ? 6 : (BN == 64) ? 8 : 10;
+  static constexpr int kMiscBytes = 2048;  // row offsets (1 KB) + barriers + flags
+  static constexpr int kAvail = 232448 - 1024 - kMiscBytes;  // 227 KB less alignment slack and misc
+  static constexpr int kStagesFit = (kAvail - kCBytes) / kStageBytes;
+  static constexpr int kStages = kStagesFit > 10 ? 10 : kStagesFit;
   static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;  // two accumulator buffers
   static constexpr int kCH = BN / 4;  // columns per epilogue thread per column group
-  static constexpr int kBarBytes = 256;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;  // + align slack
+  static constexpr int kSmemBytes = kStages * kStageBytes + kCBytes + kMiscBytes + 1024;
+  static_assert(kStages >= 3, "pipeline too shallow");
 };
 
 template <typename OutT>
-__device__ __forceinline__ void store8(OutT* dst, const float* v) {
+__device__ __forceinline__ uint4 pack8(const float* v) {
   uint4 q;
   q.x = pack2(v[0], v[1], OutT());
   q.y = pack2(v[2], v[3], OutT());
   q.z = pack2(v[4], v[5], OutT());
   q.w = pack2(v[6], v[7], OutT());
-  *reinterpret_cast<uint4*>(dst) = q;
+  return q;
+}
+template <typename OutT>
+__device__ __forceinline__ void store8(OutT* dst, const float* v) {
+  *reinterpret_cast<uint4*>(dst) = pack8<OutT>(v);
 }
 template <>
 __device__ __forceinline__ void store8<float>(float* dst, const float* v) {
@@ -81,21 +96,23 @@ __device__ __forceinline__ void store8<float>(float* dst, const float* v) {
 }
 
 // Atomic accumulate of 8 consecutive outputs (stage 2, accumulate mode).
-__device__ __forceinline__ void red8(__nv_bfloat16* dst, const float* v) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    uint32_t p = pack2(v[2 * i], v[2 * i + 1], __nv_bfloat16());
-    asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(dst + 2 * i), "r"(p) : "memory");
-  }
+__device__ __forceinline__ void red8_packed(__nv_bfloat16* dst, const uint4& q) {
+  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(q.x),
+               "r"(q.y), "r"(q.z), "r"(q.w)
+               : "memory");
 }
-__device__ __forceinline__ void red8(__half* dst, const float* v) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    uint32_t p = pack2(v[2 * i], v[2 * i + 1], __half());
-    asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(dst + 2 * i), "r"(p) : "memory");
-  }
+__device__ __forceinline__ void red8_packed(__half* dst, const uint4& q) {
+  asm volatile("red.global.add.noftz.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(q.x),
+               "r"(q.y), "r"(q.z), "r"(q.w)
+               : "memory");
 }
-__device__ __forceinline__ void red8(float* dst, const float* v) {
+__device__ __forceinline__ void red8_packed(float*, const uint4&) {}  // f32 never takes the staged path
+template <typename OutT>
+__device__ __forceinline__ void red8(OutT* dst, const float* v) {
+  red8_packed(dst, pack8<OutT>(v));
+}
+template <>
+__device__ __forceinline__ void red8<float>(float* dst, const float* v) {
 #pragma unroll
   for (int i = 0; i < 2; ++i)
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * i),
@@ -135,8 +152,9 @@ struct TileWalker {
 
 template <int BN, int MODE, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
-bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
-  using C = Cfg<BN>;
+bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_c,
+               const GemmParams p) {
+  using C = Cfg<BN, MODE, OutT>;
   constexpr int kStages = C::kStages;
   constexpr int CH = C::kCH;
   extern __shared__ uint8_t smem_raw[];
@@ -146,14 +164,18 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t bar_base = smem_base + kStages * C::kStageBytes;
+  const uint32_t cstage_base = smem_base + kStages * C::kStageBytes;       // 1024-aligned
+  const uint32_t misc_base = cstage_base + C::kCBytes;
+  uint8_t* misc = smem_al + kStages * C::kStageBytes + C::kCBytes;
+  long long* row_off = reinterpret_cast<long long*>(misc);                 // [128], MoE staged output
+  const uint32_t bar_base = misc_base + 1024;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
   auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
-  uint8_t* misc = smem_al + kStages * C::kStageBytes + 8 * (2 * kStages + 4);
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 4);
+  const uint32_t epi_bar = bar_base + 8u * (2 * kStages + 4);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc + 1024 + 8 * (2 * kStages + 5));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 1024 + 8 * (2 * kStages + 5) + 4);
 
   constexpr int kFullCount = (MODE == kDense) ? 1 : 3;  // producer (+ two gather warps)
   if (threadIdx.x == 0) {
@@ -163,12 +185,16 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 8);  // one arrival per epilogue warp
+      mbar_init(tempty_bar(b), kEpiWarps);  // one arrival per epilogue warp
     }
+    mbar_init(epi_bar, kEpiWarps);
     *abort_flag = 0;
     fence_proxy_async_smem();
     fence_barrier_init();
-    if constexpr (MODE == kDense) prefetch_tensormap(&tmap_a);
+    if constexpr (MODE == kDense) {
+      prefetch_tensormap(&tmap_a);
+      if constexpr (C::kStaged) prefetch_tensormap(&tmap_c);
+    }
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
@@ -184,7 +210,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
 
   // Register re-balancing. setmaxnreg.inc blocks until the CTA's own pool (registers per thread at
   // launch x 384 threads = 168 x 384) can satisfy it, so the totals after the exchange must fit in
-  // that pool: 40 x 128 + 224 x 256 = 62464 <= 64512.
+  // that pool: 40 x 128 + 232 x 256 = 64512 <= 64512.
   if (warp < kEpiWarp0) {
     reg_dealloc<40>();
     if (warp == 0 && lane == 0) {
@@ -281,6 +307,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
       // Thread g owns rows g and g+64 of the tile; row r, 16-byte chunk c lands at
       // r*128 + ((c ^ (r & 7)) << 4): the 128-byte-swizzled K-major image.
       constexpr int kDepth = (kStages > 4) ? 3 : 2;  // groups in flight before a stage is published
+      static_assert(kDepth < kStages, "gather look-ahead must stay below the ring depth");
       const int g = threadIdx.x - 64;
       uint32_t it = 0, published = 0;
       bool alive = true;
@@ -346,18 +373,30 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
     }
   } else {
     // ---------------- epilogue warps: scale promotion + output ----------------
-    reg_alloc<224>();
+    reg_alloc<232>();
     const int ew = warp - kEpiWarp0;
     const int quad = warp & 3;   // TMEM lane quadrant this warp may read
     const int half = ew >> 2;    // which CH-wide slice of each column group
     const int r = quad * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-    constexpr int LD = (CH > 32) ? 16 : CH;  // columns per tcgen05.ld (bounded by registers)
-    constexpr int NSUB = CH / LD;
+    constexpr int LD = (CH > 32) ? 16 : CH;  // columns per tcgen05.ld (two buffers in flight; bounded by registers)
+    constexpr int NSUB = CH / LD;            // loads per column group
+    constexpr int NQ = 2 * NSUB;             // loads per K block (two column groups)
     OutT* const out = reinterpret_cast<OutT*>(p.out);
+    const bool store_thread = (threadIdx.x == kEpiWarp0 * 32);
 
     uint32_t it = 0;
+    uint32_t epi_phase = 0;
     bool alive = true;
+    // Barrier among the 256 epilogue threads (bounded like every other wait).
+    auto epi_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(epi_bar);
+      const bool ok = mbar_wait(epi_bar, epi_phase, abort_flag, p.err, kErrWaitEpilogue);
+      epi_phase ^= 1;
+      return __all_sync(0xffffffffu, ok);
+    };
+
     for (int tile = blockIdx.x; tile < walk.total && alive; tile += gridDim.x) {
       int m_blk, n_tile;
       walk.decode(tile, m_blk, n_tile);
@@ -368,21 +407,21 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
       size_t sa_stride;
       const float* sb_ptr0;     // + kb
       const float* sb_ptr1;
-      int col0, col1;           // first output column of group 0 / group 1 (MoE1: same column)
+      int n0;                   // first output column of the tile
+      int col0, col1;           // tile-relative first output column of group 0 / group 1
       size_t out_row = 0;
       float route_w = 1.0f;
-      const int KBs = KB;
       if constexpr (MODE == kDense) {
         const int row = m_blk * BM + r;
         row_ok = row < p.M;
         sa_ptr = p.scale_a + (row_ok ? row : 0);
         sa_stride = static_cast<size_t>(p.M);
-        const int n0 = n_tile * BN;
-        col0 = n0 + half * CH;
-        col1 = n0 + BN / 2 + half * CH;
+        n0 = n_tile * BN;
+        col0 = half * CH;
+        col1 = BN / 2 + half * CH;
         const int nblk_max = (p.N + 127) / 128 - 1;
-        sb_ptr0 = p.scale_b + static_cast<size_t>(min(col0 / 128, nblk_max)) * KBs;
-        sb_ptr1 = p.scale_b + static_cast<size_t>(min(col1 / 128, nblk_max)) * KBs;
+        sb_ptr0 = p.scale_b + static_cast<size_t>(min((n0 + col0) / 128, nblk_max)) * KB;
+        sb_ptr1 = p.scale_b + static_cast<size_t>(min((n0 + col1) / 128, nblk_max)) * KB;
         out_row = static_cast<size_t>(row) * p.N;
       } else {
         const int e = p.expert_ids[m_blk];
@@ -400,30 +439,31 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
         if constexpr (MODE == kMoe1) {
           sa_ptr = p.scale_a + t;
           sa_stride = static_cast<size_t>(p.M);
-          const int n0 = n_tile * (BN / 2);
-          col0 = col1 = n0 + half * CH;
+          n0 = n_tile * (BN / 2);
+          col0 = col1 = half * CH;
           const int nb_exp = (2 * p.N) / 128;  // scale rows per expert
-          sb_ptr0 = p.scale_b + (static_cast<size_t>(e) * nb_exp + min(col0, p.N - 1) / 128) * KBs;
-          sb_ptr1 = p.scale_b +
-                    (static_cast<size_t>(e) * nb_exp + (p.N + min(col0, p.N - 1)) / 128) * KBs;
+          const int cg = min(n0 + col0, p.N - 1);
+          sb_ptr0 = p.scale_b + (static_cast<size_t>(e) * nb_exp + cg / 128) * KB;
+          sb_ptr1 = p.scale_b + (static_cast<size_t>(e) * nb_exp + (p.N + cg) / 128) * KB;
           out_row = (static_cast<size_t>(t) * p.topk + slot) * p.N;
         } else {
           sa_ptr = p.scale_a + static_cast<size_t>(t) * p.topk + slot;
           sa_stride = static_cast<size_t>(p.M) * p.topk;
-          const int n0 = n_tile * BN;
-          col0 = n0 + half * CH;
-          col1 = n0 + BN / 2 + half * CH;
+          n0 = n_tile * BN;
+          col0 = half * CH;
+          col1 = BN / 2 + half * CH;
           const int nb_exp = p.N / 128;
-          sb_ptr0 = p.scale_b + (static_cast<size_t>(e) * nb_exp + min(col0, p.N - 1) / 128) * KBs;
-          sb_ptr1 = p.scale_b + (static_cast<size_t>(e) * nb_exp + min(col1, p.N - 1) / 128) * KBs;
+          sb_ptr0 = p.scale_b + (static_cast<size_t>(e) * nb_exp + min(n0 + col0, p.N - 1) / 128) * KB;
+          sb_ptr1 = p.scale_b + (static_cast<size_t>(e) * nb_exp + min(n0 + col1, p.N - 1) / 128) * KB;
           out_row = p.accumulate ? static_cast<size_t>(t) * p.N
                                  : (static_cast<size_t>(t) * p.topk + slot) * p.N;
         }
       }
 
-      float acc0[CH], acc1[CH];
+      // acc[0 .. CH/2) = column group 0, acc[CH/2 .. CH) = column group 1, two columns per float2.
+      float2 acc[CH];
 #pragma unroll
-      for (int j = 0; j < CH; ++j) { acc0[j] = 0.f; acc1[j] = 0.f; }
+      for (int j = 0; j < CH; ++j) acc[j] = make_float2(0.f, 0.f);
 
       // Scales are prefetched four K blocks ahead into a register ring.
       float ring_a[4], ring_b0[4], ring_b1[4];
@@ -458,21 +498,32 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
             } else {
               tc_fence_after();
               const uint32_t t0 = tmem_base + lane_base + buf * BN + half * CH;
+              // load q covers LD columns: q < NSUB -> group 0, else group 1 (BN/2 columns further)
+              auto taddr = [&](int q) {
+                return t0 + (q >= NSUB ? BN / 2 : 0) + (q % NSUB) * LD;
+              };
+              uint32_t va[LD], vb[LD];
+              tmem_ld<LD>(taddr(0), va);
+              tmem_wait_dep<LD>(va);
 #pragma unroll
-              for (int sub = 0; sub < NSUB; ++sub) {
-                uint32_t v0[LD], v1[LD];
-                tmem_ld<LD>(t0 + sub * LD, v0);
-                tmem_ld<LD>(t0 + BN / 2 + sub * LD, v1);
-                tc_wait_ld();
-                if (sub == NSUB - 1) {
-                  tc_fence_before();
-                  __syncwarp();
-                  if (lane == 0) mbar_arrive(tempty_bar(buf));
-                }
+              for (int q = 0; q < NQ; ++q) {
+                uint32_t* cur = (q & 1) ? vb : va;
+                uint32_t* nxt = (q & 1) ? va : vb;
+                if (q + 1 < NQ) tmem_ld<LD>(taddr(q + 1), nxt);   // in flight during the FMAs
+                const float s = (q >= NSUB) ? s1 : s0;
+                const float2 s2 = make_float2(s, s);
+                float2* a = acc + (q >= NSUB ? CH / 2 : 0) + (q % NSUB) * (LD / 2);
 #pragma unroll
-                for (int c = 0; c < LD; ++c) {
-                  acc0[sub * LD + c] = fmaf(__uint_as_float(v0[c]), s0, acc0[sub * LD + c]);
-                  acc1[sub * LD + c] = fmaf(__uint_as_float(v1[c]), s1, acc1[sub * LD + c]);
+                for (int c = 0; c < LD / 2; ++c)
+                  a[c] = __ffma2_rn(make_float2(__uint_as_float(cur[2 * c]),
+                                                __uint_as_float(cur[2 * c + 1])), s2, a[c]);
+                if (q + 1 < NQ) {
+                  tmem_wait_dep<LD>(nxt);
+                  if (q + 2 == NQ) {  // every load of this buffer has landed: hand it back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(buf));
+                  }
                 }
               }
               ++it;
@@ -483,37 +534,123 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
       if (!alive) break;
 
       // ---- output ----
-      if (row_ok) {
+      const float* accf = reinterpret_cast<const float*>(acc);  // [0,CH) group 0, [CH,2CH) group 1
+      if constexpr (C::kStaged) {
+        // (1) the staging tile must be free: previous TMA store has read it / previous tile's
+        //     cooperative row stores are done (every thread passes this barrier after its own)
+        if constexpr (MODE == kDense) {
+          if (store_thread) bulk_wait_group_read0();
+        }
+        if (!epi_sync()) { alive = false; break; }
+        // (2) thread r writes its columns of row r into the swizzled staging tile
+        auto stage8 = [&](int col, const float* v) {   // col: tile-relative output column, % 8 == 0
+          const uint32_t addr = cstage_base + (col >> 6) * kRegionBytes + r * 128 +
+                                ((((col & 63) >> 3) ^ (r & 7)) << 4);
+          const uint4 q = pack8<OutT>(v);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(q.x), "r"(q.y),
+                       "r"(q.z), "r"(q.w)
+                       : "memory");
+        };
         if constexpr (MODE == kMoe1) {
 #pragma unroll
           for (int j = 0; j < CH; j += 8) {
-            if (col0 + j + 8 <= p.N) {
-              float y[8];
+            float y[8];
 #pragma unroll
-              for (int q = 0; q < 8; ++q) y[q] = silu_mul(acc0[j + q], acc1[j + q]) * route_w;
-              store8<OutT>(out + out_row + col0 + j, y);
-            }
+            for (int q = 0; q < 8; ++q) y[q] = silu_mul(accf[j + q], accf[CH + j + q]) * route_w;
+            stage8(col0 + j, y);
           }
         } else {
 #pragma unroll
           for (int grp = 0; grp < 2; ++grp) {
-            const int cb = grp ? col1 : col0;
-            const float* acc = grp ? acc1 : acc0;
 #pragma unroll
             for (int j = 0; j < CH; j += 8) {
-              if (cb + j + 8 <= p.N) {
+              float y[8];
+#pragma unroll
+              for (int q = 0; q < 8; ++q) y[q] = accf[grp * CH + j + q] * route_w;
+              stage8((grp ? col1 : col0) + j, y);
+            }
+          }
+        }
+        if constexpr (MODE != kDense) {
+          if (half == 0) row_off[r] = row_ok ? static_cast<long long>(out_row) : -1LL;
+        } else {
+          fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA store
+        }
+        if (!epi_sync()) { alive = false; break; }
+        // (3) write the tile out
+        if constexpr (MODE == kDense) {
+          if (store_thread) {
+#pragma unroll
+            for (int reg = 0; reg < C::kRegions; ++reg)
+              if (n0 + reg * 64 < p.N)
+                tma_store_2d(&tmap_c, cstage_base + reg * kRegionBytes, n0 + reg * 64, m_blk * BM);
+            bulk_commit_group();
+          }
+        } else {
+          constexpr int CPR = C::kOutCols / 8;   // 16-byte chunks per output row
+          constexpr int RPI = 32 / CPR;          // rows per warp instruction
+          const int rows = min(BM, p.tile_m);
+          const int ch = lane % CPR;
+          const int col = ch * 8;
+          if (n0 + col + 8 <= p.N) {
+            for (int r0 = ew * RPI; r0 < rows; r0 += kEpiWarps * RPI) {
+              const int rr = r0 + lane / CPR;
+              if (rr < rows) {
+                const long long off = row_off[rr];
+                if (off >= 0) {
+                  const uint32_t addr = cstage_base + (col >> 6) * kRegionBytes + rr * 128 +
+                                        ((((col & 63) >> 3) ^ (rr & 7)) << 4);
+                  uint4 q;
+                  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                               : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                               : "r"(addr)
+                               : "memory");
+                  OutT* dst = out + off + n0 + col;
+                  if (MODE == kMoe2 && p.accumulate)
+                    red8_packed(dst, q);
+                  else
+                    *reinterpret_cast<uint4*>(dst) = q;
+                }
+              }
+            }
+          }
+        }
+      } else {
+        // direct path (narrow tiles, f32 output): each thread stores its own row segments
+        if (row_ok) {
+          if constexpr (MODE == kMoe1) {
+#pragma unroll
+            for (int j = 0; j < CH; j += 8) {
+              if (n0 + col0 + j + 8 <= p.N) {
                 float y[8];
 #pragma unroll
-                for (int q = 0; q < 8; ++q) y[q] = acc[j + q] * route_w;
-                if (MODE == kMoe2 && p.accumulate)
-                  red8(out + out_row + cb + j, y);
-                else
-                  store8<OutT>(out + out_row + cb + j, y);
+                for (int q = 0; q < 8; ++q) y[q] = silu_mul(accf[j + q], accf[CH + j + q]) * route_w;
+                store8<OutT>(out + out_row + n0 + col0 + j, y);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int grp = 0; grp < 2; ++grp) {
+              const int cb = n0 + (grp ? col1 : col0);
+#pragma unroll
+              for (int j = 0; j < CH; j += 8) {
+                if (cb + j + 8 <= p.N) {
+                  float y[8];
+#pragma unroll
+                  for (int q = 0; q < 8; ++q) y[q] = accf[grp * CH + j + q] * route_w;
+                  if (MODE == kMoe2 && p.accumulate)
+                    red8<OutT>(out + out_row + cb + j, y);
+                  else
+                    store8<OutT>(out + out_row + cb + j, y);
+                }
               }
             }
           }
         }
       }
+    }
+    if constexpr (C::kStaged && MODE == kDense) {
+      if (store_thread) bulk_wait_group0();  // the last tile's TMA store must finish before exit
     }
   }
 
@@ -552,16 +689,19 @@ static EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// A [M, K] fp8 row-major; box = 128 bytes of K x box_rows rows; 128-byte swizzle; OOB rows read 0.
-static int make_a_tensor_map(CUtensorMap* map, const void* a, int M, int K, int box_rows) {
+// Row-major 2-D tensor [rows, cols] of elem_bytes-wide elements; box = 128 bytes x box_rows rows;
+// 128-byte swizzle; out-of-range parts read as 0 / are not written.
+static int make_tensor_map(CUtensorMap* map, const void* base, int rows, int cols, int elem_bytes,
+                           int box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return set_error(FLYB200_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
-  cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(K)};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * elem_bytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elem_bytes), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(a), dims, strides, box,
-                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+  CUresult r = fn(map, elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16,
+                  2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return set_error(FLYB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d",
@@ -570,8 +710,9 @@ static int make_a_tensor_map(CUtensorMap* map, const void* a, int M, int K, int 
 }
 
 template <int BN, int MODE, typename OutT>
-static int launch(const CUtensorMap& tmap, const GemmParams& p, int grid, cudaStream_t stream) {
-  using C = Cfg<BN>;
+static int launch(const CUtensorMap& tmap_a, const CUtensorMap& tmap_c, const GemmParams& p,
+                  int grid, cudaStream_t stream) {
+  using C = Cfg<BN, MODE, OutT>;
   auto kern = bs_gemm_kernel<BN, MODE, OutT>;
   static thread_local int configured_dev = -1;
   int dev = 0;
@@ -581,21 +722,21 @@ static int launch(const CUtensorMap& tmap, const GemmParams& p, int grid, cudaSt
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
     configured_dev = dev;
   }
-  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(tmap, p);
+  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(tmap_a, tmap_c, p);
   FLYB200_CUDA_CHECK(cudaGetLastError());
   return FLYB200_OK;
 }
 
 template <int MODE, typename OutT>
-static int launch_bn(int bn, const CUtensorMap& tmap, const GemmParams& p, int grid,
-                     cudaStream_t stream) {
+static int launch_bn(int bn, const CUtensorMap& tmap_a, const CUtensorMap& tmap_c,
+                     const GemmParams& p, int grid, cudaStream_t stream) {
   switch (bn) {
     case 32:
       if constexpr (MODE == kMoe1) break;  // 16 gate + 16 up columns: not built
-      else return launch<32, MODE, OutT>(tmap, p, grid, stream);
-    case 64: return launch<64, MODE, OutT>(tmap, p, grid, stream);
-    case 128: return launch<128, MODE, OutT>(tmap, p, grid, stream);
-    case 256: return launch<256, MODE, OutT>(tmap, p, grid, stream);
+      else return launch<32, MODE, OutT>(tmap_a, tmap_c, p, grid, stream);
+    case 64: return launch<64, MODE, OutT>(tmap_a, tmap_c, p, grid, stream);
+    case 128: return launch<128, MODE, OutT>(tmap_a, tmap_c, p, grid, stream);
+    case 256: return launch<256, MODE, OutT>(tmap_a, tmap_c, p, grid, stream);
     default: break;
   }
   return set_error(FLYB200_ERR_INVALID_ARGUMENT, "block_n must be 32, 64, 128 or 256 (got %d)", bn);
@@ -673,11 +814,13 @@ extern "C" int flyb200_blockscale_gemm(void* c, const void* a, const void* b_rep
   // Small M: bring only as many rows as exist (rounded up to the 8-row swizzle atom).
   p.a_box_rows = M >= BM ? BM : ((M + 7) / 8) * 8;
 
-  CUtensorMap tmap;
-  if ((rc = make_a_tensor_map(&tmap, a, M, K, p.a_box_rows))) return rc;
+  CUtensorMap tmap_a, tmap_c;
+  if ((rc = make_tensor_map(&tmap_a, a, M, K, 1, p.a_box_rows))) return rc;
+  if ((rc = make_tensor_map(&tmap_c, c, M, N, 2, p.a_box_rows))) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (out_dtype == FLYB200_BF16) return launch_bn<kDense, __nv_bfloat16>(bn, tmap, p, grid, st);
-  return launch_bn<kDense, __half>(bn, tmap, p, grid, st);
+  if (out_dtype == FLYB200_BF16)
+    return launch_bn<kDense, __nv_bfloat16>(bn, tmap_a, tmap_c, p, grid, st);
+  return launch_bn<kDense, __half>(bn, tmap_a, tmap_c, p, grid, st);
 }
 
 static int moe_common_checks(const void* out, const void* x, const void* w, const float* scale_x,
@@ -739,8 +882,9 @@ extern "C" int flyb200_moe_gemm1(void* out, const void* x, const void* w_repacke
   p.experts = E; p.doweight = doweight; p.accumulate = 0;
   CUtensorMap tmap{};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (out_dtype == FLYB200_BF16) return launch_bn<kMoe1, __nv_bfloat16>(bn, tmap, p, grid, st);
-  return launch_bn<kMoe1, __half>(bn, tmap, p, grid, st);
+  if (out_dtype == FLYB200_BF16)
+    return launch_bn<kMoe1, __nv_bfloat16>(bn, tmap, tmap, p, grid, st);
+  return launch_bn<kMoe1, __half>(bn, tmap, tmap, p, grid, st);
 }
 
 extern "C" int flyb200_moe_gemm2(void* out, const void* a2, const void* w_repacked,
@@ -777,7 +921,8 @@ extern "C" int flyb200_moe_gemm2(void* out, const void* a2, const void* w_repack
   p.experts = E; p.doweight = doweight; p.accumulate = accumulate ? 1 : 0;
   CUtensorMap tmap{};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (out_dtype == FLYB200_BF16) return launch_bn<kMoe2, __nv_bfloat16>(bn, tmap, p, grid, st);
-  if (out_dtype == FLYB200_F16) return launch_bn<kMoe2, __half>(bn, tmap, p, grid, st);
-  return launch_bn<kMoe2, float>(bn, tmap, p, grid, st);
+  if (out_dtype == FLYB200_BF16)
+    return launch_bn<kMoe2, __nv_bfloat16>(bn, tmap, tmap, p, grid, st);
+  if (out_dtype == FLYB200_F16) return launch_bn<kMoe2, __half>(bn, tmap, tmap, p, grid, st);
+  return launch_bn<kMoe2, float>(bn, tmap, tmap, p, grid, st);
 }

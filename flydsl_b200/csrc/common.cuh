@@ -33,6 +33,7 @@ enum DeviceError : int {
   kErrWaitTmemEmpty = 3,  // MMA issuer gave up waiting for a free accumulator buffer
   kErrWaitTmemFull = 4,   // epilogue gave up waiting for an accumulator
   kErrWaitGather = 5,     // gather warps gave up waiting for a free stage
+  kErrWaitEpilogue = 6,   // an epilogue warp gave up waiting for the other epilogue warps
 };
 
 // ---- shared-memory address / mbarrier --------------------------------------------------------
@@ -228,6 +229,40 @@ __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t* r) {
   if constexpr (N == 8) FLYB200_TMEM_LD_X8(taddr, r);
   if constexpr (N == 16) FLYB200_TMEM_LD_X16(taddr, r);
   if constexpr (N == 32) FLYB200_TMEM_LD_X32(taddr, r);
+}
+
+// tcgen05.wait::ld that also names the loaded registers as read-write operands, so the compiler
+// cannot schedule a use of them ahead of the wait.
+#define FLYB200_R8(r, o) "+r"(r[o]), "+r"(r[o + 1]), "+r"(r[o + 2]), "+r"(r[o + 3]), "+r"(r[o + 4]), \
+                         "+r"(r[o + 5]), "+r"(r[o + 6]), "+r"(r[o + 7])
+template <int N>
+__device__ __forceinline__ void tmem_wait_dep(uint32_t* r) {
+  static_assert(N == 8 || N == 16 || N == 32, "chunk width");
+  if constexpr (N == 8)
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : FLYB200_R8(r, 0)::"memory");
+  if constexpr (N == 16)
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : FLYB200_R8(r, 0), FLYB200_R8(r, 8)::"memory");
+  if constexpr (N == 32)
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : FLYB200_R8(r, 0), FLYB200_R8(r, 8), FLYB200_R8(r, 16), FLYB200_R8(r, 24)::"memory");
+}
+
+// TMA tensor store shared -> global (bulk async-group completion). Clips rows/columns outside the
+// tensor. x is the innermost (column) coordinate and must be 16-byte aligned in bytes.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(x), "r"(y), "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_group_read0() {  // sources may be overwritten
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_group0() {  // writes complete
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
 // Register re-balancing between warpgroups (producer/MMA warps need few, epilogue warps many).
