@@ -352,11 +352,7 @@ def moe_layer_bench(rank, world, dev, peaks, quick=False):
 
     H, I, E, topk = 7168, 2048, 256, 8
     if world > 1:
-        try:
-            from flydsl_b200 import parallel
-        except ImportError:
-            return {"skipped": "expert-parallel layer not built yet"}
-        return parallel.bench_ep_layer(rank, world, dev, peaks, make_moe_gpu, quant_1x128_torch, quick=quick)
+        return moe_ep_bench(rank, world, dev, peaks, quick=quick)
     w1, w1_s, w2, w2_s = make_moe_gpu(0, H, I, E, topk, dev, seed=0)
     layer = BlockscaleMoE(w1, w1_s, w2, w2_s, topk=topk, tile_m=128, mode="reduce")
     res = []
@@ -398,6 +394,44 @@ def moe_layer_bench(rank, world, dev, peaks, quick=False):
                     "launches_per_step": layer_t.launches_per_step,
                     "l2": "weights of the active experts (>= 3 GB) exceed L2"})
     return res
+
+
+def moe_ep_bench(rank, world, dev, peaks, quick=False):
+    """Expert-parallel MoE layer: 4096 tokens in total (T/W per rank), 256 experts (E/W per rank),
+    NCCL all-to-all dispatch and combine inside the timed region."""
+    import torch.distributed as dist
+
+    from flydsl_b200 import parallel
+
+    H, I, E, topk, T = 7168, 2048, 256, 8, 4096
+    EL, TL = E // world, T // world
+    w1, w1_s, w2, w2_s = make_moe_gpu(0, H, I, EL, topk, dev, seed=0, e_lo=rank * EL)
+    shard = parallel.LocalExpertShard(w1, w1_s, w2, w2_s, experts=E, topk=topk, rank=rank, world=world)
+    ep = parallel.ExpertParallelMoE(shard, experts=E, topk=topk, model_dim=H, rank=rank, world=world)
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)
+    x_q, x_s = quant_1x128_torch(torch.randn(TL, H, generator=g, device=dev))
+    logits = torch.randn(TL, E, generator=g, device=dev)
+    vals, ids = torch.topk(torch.softmax(logits, dim=1), k=topk, dim=1)
+    tw = (vals / vals.sum(dim=1, keepdim=True)).float()
+    ids = ids.to(torch.int32)
+    for _ in range(3):
+        ep.forward(x_q, x_s, ids, tw)
+    times = []
+    for _ in range(5 if quick else 10):
+        barrier(world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ep.forward(x_q, x_s, ids, tw)
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1))
+    ms = max_over_ranks(statistics.median(times), world)
+    stats = ep.last_stats
+    return [{"tokens": T, "tokens_per_rank": TL, "experts_per_rank": EL, "ms": round(ms, 4),
+             "tokens_per_s": round(T / (ms * 1e-3), 1), "parallelism": f"ep{world}",
+             "dispatch_bytes_per_rank": stats.get("dispatch_bytes"),
+             "combine_bytes_per_rank": stats.get("combine_bytes"),
+             "collective": "NCCL all_to_all_single (variable split), one host sync per step for the counts"}]
 
 
 def run_ours(args):

@@ -10,7 +10,7 @@ import os
 from ctypes import c_char_p, c_int, c_int32, c_int64, c_void_p, POINTER
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG_DIR, "lib", "libflyb200.so")
+LIB_PATH = os.environ.get("FLYB200_LIB_PATH") or os.path.join(_PKG_DIR, "lib", "libflyb200.so")
 
 OK = 0
 ERR_INVALID_ARGUMENT = -1

@@ -253,6 +253,12 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint32_t sa = smem_base + s * C::kStageBytes;
           const uint32_t sb = sa + kATileBytes;
           const uint8_t* src = wbase + kb * row_stride_kb + static_cast<size_t>(n0) * BK;
+#ifdef FLYB200_DBG_NO_LOAD
+          if (it >= static_cast<uint32_t>(kStages)) {  // experiment: MMAs re-read stale stages
+            mbar_arrive(full_bar(s));
+            continue;
+          }
+#endif
           if constexpr (MODE == kDense) {
             mbar_arrive_expect_tx(full_bar(s), p.a_box_rows * BK + rows_b * BK);
             tma_load_2d(sa, &tmap_a, kb * BK, m_blk * BM, full_bar(s));
@@ -379,7 +385,10 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int half = ew >> 2;    // which CH-wide slice of each column group
     const int r = quad * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-    constexpr int LD = (CH > 32) ? 16 : CH;  // columns per tcgen05.ld (two buffers in flight; bounded by registers)
+#ifndef FLYB200_LD_WIDE
+#define FLYB200_LD_WIDE 16
+#endif
+    constexpr int LD = (CH > 32) ? FLYB200_LD_WIDE : CH;  // columns per tcgen05.ld (two buffers in flight; bounded by registers)
     constexpr int NSUB = CH / LD;            // loads per column group
     constexpr int NQ = 2 * NSUB;             // loads per K block (two column groups)
     OutT* const out = reinterpret_cast<OutT*>(p.out);
@@ -497,6 +506,15 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               alive = false;
             } else {
               tc_fence_after();
+#ifdef FLYB200_DBG_SKIP_PROMOTE
+              if (kb + 1 < KB) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(buf));
+                ++it;
+                continue;
+              }
+#endif
               const uint32_t t0 = tmem_base + lane_base + buf * BN + half * CH;
               // load q covers LD columns: q < NSUB -> group 0, else group 1 (BN/2 columns further)
               auto taddr = [&](int q) {

@@ -1,0 +1,237 @@
+"""Multi-GPU layer for the block-scale path: one process per GPU, torch.distributed for plumbing.
+
+The reference is single-GPU (it has no collective anywhere); what it offers for expert parallelism
+are two hooks, which are used here as designed: the sorter's ``expert_mask`` (skip non-local
+experts and compact their ids, tests/kernels/test_moe_gemm.py:103-104,132-141) and the masked
+top-k reduce (``valid_mask``, kernels/moe_blockscale_2stage.py:2554-2563).
+
+* Dense GEMM: column (N) sharding. Rank r owns weight rows ``[r*N/W, (r+1)*N/W)`` and the matching
+  rows of the 128x128 scale grid, computes ``C[:, shard]``. No collective on the GEMM.
+* MoE: expert parallel. Tokens are data-parallel (each rank routes its own tokens); experts are
+  split contiguously, ``E/W`` per rank. One exchange each way:
+    dispatch   every (token, destination rank) pair is sent once (a token that picked several
+               experts of one rank travels once), as one packed row: fp8 activations, their
+               1x128 scales, the token's expert ids and route weights;
+    local      sort with expert_mask -> stage 1 -> re-quantise -> stage 2 (per-route rows) ->
+               masked reduce: one partial output row per received token;
+    combine    partial rows go back the same way; the source rank adds a token's partials in a
+               fixed rank order (deterministic).
+  The collectives are NCCL all-to-alls (``all_to_all_single`` with split sizes) over NVLink;
+  receive buffers are ordinary local memory, which is what the GEMM kernels read.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+# ------------------------------------------------------------------------------------------------
+# dense: N-sharded
+# ------------------------------------------------------------------------------------------------
+def shard_rows(n: int, rank: int, world: int, align: int = 128):
+    """Row range of rank ``rank`` when ``n`` rows are split evenly; the split must respect the
+    128-row scale blocks so that every shard owns whole scale rows."""
+    if n % (world * align) != 0:
+        raise ValueError(f"N={n} cannot be split over {world} ranks in multiples of {align}")
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+class ColumnParallelBlockscaleGemm:
+    """This rank's column shard of ``C = dequant(A) @ dequant(B)^T``."""
+
+    def __init__(self, b_q_full_or_shard, b_scale, *, N: int, K: int, rank: int, world: int,
+                 out_dtype: str = "bf16", already_sharded: bool = False):
+        from .kernels import compile_blockscale_preshuffle_gemm
+        from .utils import shuffle_weight
+
+        lo, hi = shard_rows(N, rank, world)
+        self.rank, self.world, self.N, self.K = rank, world, N, K
+        self.n_local = hi - lo
+        if already_sharded:
+            b_q, b_s = b_q_full_or_shard, b_scale
+        else:
+            b_q = b_q_full_or_shard[lo:hi].contiguous()
+            b_s = b_scale[lo // 128: hi // 128].contiguous()
+        self.b = shuffle_weight(b_q)
+        self.b_scale = b_s.contiguous().view(-1)
+        self.out_dtype = torch.bfloat16 if out_dtype == "bf16" else torch.float16
+        self._out_name = out_dtype
+        self._fns = {}
+        self._compile = compile_blockscale_preshuffle_gemm
+
+    def forward(self, a_q, a_scale_t, out=None, stream=None):
+        """a_q fp8 [M, K] (replicated), a_scale_t f32 [K/128, M]; returns C[:, shard] [M, N/W]."""
+        M = a_q.shape[0]
+        fn = self._fns.get(M)
+        if fn is None:
+            fn = self._compile(M=M, N=self.n_local, K=self.K, tile_m=64, tile_n=128, tile_k=128,
+                               out_dtype=self._out_name)
+            self._fns[M] = fn
+        if out is None:
+            out = torch.empty((M, self.n_local), dtype=self.out_dtype, device=a_q.device)
+        fn(out, a_q, self.b, a_scale_t, self.b_scale, M, self.n_local, stream)
+        return out
+
+
+# ------------------------------------------------------------------------------------------------
+# MoE: expert parallel -- index logic (pure torch, device-agnostic; tested on CPU with gloo)
+# ------------------------------------------------------------------------------------------------
+def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int):
+    """For local tokens ``topk_ids [T, k]`` (global expert ids) decide which ranks each token visits.
+
+    Returns
+      need    bool [T, W]   token t has at least one expert on rank r
+      order   i64  [S]      token index of every sent row, grouped by destination rank, ascending
+                            token inside a group (S = need.sum())
+      counts  i64  [W]      rows per destination rank
+      pos     i64  [T, W]   position of (t, r)'s row inside ``order`` (undefined where not needed)
+    """
+    T = topk_ids.shape[0]
+    dest = torch.div(topk_ids.long(), experts_per_rank, rounding_mode="floor")      # [T, k]
+    ranks = torch.arange(world, device=topk_ids.device).view(1, 1, world)
+    need = (dest.unsqueeze(-1) == ranks).any(dim=1)                                 # [T, W]
+    counts = need.sum(dim=0)
+    need_t = need.t().contiguous()                                                  # [W, T]
+    flat = need_t.reshape(-1)
+    order = torch.nonzero(flat, as_tuple=False).squeeze(1) % max(T, 1)              # rank-major
+    pos_t = torch.cumsum(flat.long(), dim=0) - 1                                    # [W*T]
+    pos = pos_t.view(world, T).t().contiguous()
+    return need, order, counts, pos
+
+
+def pack_rows(x_q_u8, x_scale, topk_ids, topk_weights, order):
+    """One byte row per sent token: [H fp8 | H/128 f32 scales | k i32 ids | k f32 weights]."""
+    parts = [x_q_u8[order],
+             x_scale[order].contiguous().view(torch.uint8).view(order.numel(), -1),
+             topk_ids[order].to(torch.int32).contiguous().view(torch.uint8).view(order.numel(), -1),
+             topk_weights[order].to(torch.float32).contiguous().view(torch.uint8).view(order.numel(), -1)]
+    return torch.cat(parts, dim=1).contiguous()
+
+
+def unpack_rows(buf, H: int, k: int):
+    """Inverse of pack_rows on the receiving side."""
+    R = buf.shape[0]
+    nscale = H // 128
+    o0, o1, o2, o3 = H, H + 4 * nscale, H + 4 * nscale + 4 * k, H + 4 * nscale + 8 * k
+    x_q = buf[:, :o0].contiguous()
+    x_s = buf[:, o0:o1].contiguous().view(torch.float32).view(R, nscale)
+    ids = buf[:, o1:o2].contiguous().view(torch.int32).view(R, k)
+    w = buf[:, o2:o3].contiguous().view(torch.float32).view(R, k)
+    return x_q, x_s, ids, w
+
+
+def combine_partials(recv, need, pos, out_dtype):
+    """out[t] = sum over ranks r (ascending) of the partial row (t, r); fp32 accumulate."""
+    T, W = need.shape
+    H = recv.shape[1]
+    padded = torch.cat([recv, torch.zeros((1, H), dtype=recv.dtype, device=recv.device)], dim=0)
+    idx = torch.where(need, pos, torch.full_like(pos, recv.shape[0]))
+    acc = torch.zeros((T, H), dtype=torch.float32, device=recv.device)
+    for r in range(W):  # fixed order => deterministic
+        acc += padded[idx[:, r]].float()
+    return acc.to(out_dtype)
+
+
+def exchange_counts(counts: torch.Tensor, group=None) -> torch.Tensor:
+    """counts[r] rows go to rank r; returns how many rows each rank sends to me."""
+    recv = torch.empty_like(counts)
+    dist.all_to_all_single(recv, counts, group=group)
+    return recv
+
+
+def all_to_all_rows(rows: torch.Tensor, send_counts, recv_counts, group=None) -> torch.Tensor:
+    """Variable-count row exchange. ``rows`` is grouped by destination rank."""
+    out = rows.new_empty((int(sum(recv_counts)),) + tuple(rows.shape[1:]))
+    dist.all_to_all_single(out, rows, output_split_sizes=list(recv_counts),
+                           input_split_sizes=list(send_counts), group=group)
+    return out
+
+
+class ExpertParallelMoE:
+    """Expert-parallel wrapper around a local two-stage MoE.
+
+    ``local_fn(x_q_u8 [R,H], x_scale [R,H/128], topk_ids [R,k] (global ids), topk_weights [R,k])``
+    must return the partial output ``[R, H]`` that sums only the routes whose expert lives on this
+    rank. On GPUs that is :class:`LocalExpertShard` below; tests plug in a CPU function.
+    """
+
+    def __init__(self, local_fn: Callable, *, experts: int, topk: int, model_dim: int, rank: int,
+                 world: int, group=None, out_dtype=torch.bfloat16):
+        if experts % world:
+            raise ValueError(f"{experts} experts cannot be split over {world} ranks")
+        self.local_fn, self.E, self.k, self.H = local_fn, experts, topk, model_dim
+        self.rank, self.world, self.group, self.out_dtype = rank, world, group, out_dtype
+        self.experts_per_rank = experts // world
+        self.last_stats = {}
+
+    def forward(self, x_q, x_scale, topk_ids, topk_weights):
+        """x_q fp8/uint8 [T, H]; x_scale f32 [T, H/128] (token-major); ids [T, k]; weights [T, k]."""
+        x_u8 = x_q.view(torch.uint8)
+        need, order, counts, pos = plan_dispatch(topk_ids, self.experts_per_rank, self.world)
+        recv_counts = exchange_counts(counts, self.group)
+        send_l, recv_l = counts.tolist(), recv_counts.tolist()       # one host sync per step
+        rows = pack_rows(x_u8, x_scale, topk_ids, topk_weights, order)
+        got = all_to_all_rows(rows, send_l, recv_l, self.group)
+        rx_q, rx_s, rids, rw = unpack_rows(got, self.H, self.k)
+        partial = self.local_fn(rx_q, rx_s, rids, rw)                # [R, H]
+        back = all_to_all_rows(partial.contiguous(), recv_l, send_l, self.group)
+        self.last_stats = {"sent_rows": int(sum(send_l)), "recv_rows": int(sum(recv_l)),
+                           "dispatch_bytes": int(sum(send_l)) * rows.shape[1],
+                           "combine_bytes": int(sum(recv_l)) * self.H * partial.element_size()}
+        return combine_partials(back, need, pos, self.out_dtype)
+
+
+class LocalExpertShard:
+    """The experts of one rank on its GPU: routing sort restricted by ``expert_mask``, the two GEMM
+    stages, and the masked top-k reduce that yields one partial row per received token."""
+
+    def __init__(self, w1, w1_scale, w2, w2_scale, *, experts: int, topk: int, rank: int, world: int,
+                 tile_m: int = 128, mid_dtype=torch.float16, out_dtype=torch.bfloat16):
+        from .kernels import (compile_moe_blockscale_gemm1, compile_moe_blockscale_gemm2,
+                              compile_moe_reduction)
+
+        self.E, self.k, self.rank, self.world = experts, topk, rank, world
+        self.EL = experts // world
+        self.w1, self.w2 = w1, w2                       # repacked local experts [EL, 2I, H], [EL, H, I]
+        self.w1_scale, self.w2_scale = w1_scale.contiguous().view(-1), w2_scale.contiguous().view(-1)
+        self.H, self.I = w1.shape[2], w1.shape[1] // 2
+        self.tile_m, self.mid_dtype, self.out_dtype = tile_m, mid_dtype, out_dtype
+        names = {torch.float16: "f16", torch.bfloat16: "bf16"}
+        common = dict(model_dim=self.H, inter_dim=self.I, experts=self.EL, topk=topk, tile_m=tile_m,
+                      tile_n=256, tile_k=128)
+        self.gemm1 = compile_moe_blockscale_gemm1(doweight_stage1=False, out_dtype=names[mid_dtype], **common)
+        self.gemm2 = compile_moe_blockscale_gemm2(doweight_stage2=True, out_dtype=names[out_dtype],
+                                                  accumulate=False, **common)
+        self.reduce = compile_moe_reduction(topk=topk, model_dim=self.H, dtype_str=names[out_dtype],
+                                            use_mask=True)
+        mask = torch.zeros(experts, dtype=torch.int32, device=w1.device)
+        mask[rank * self.EL:(rank + 1) * self.EL] = 1
+        self.expert_mask = mask
+
+    def __call__(self, x_q_u8, x_scale, topk_ids, topk_weights):
+        from .utils import moe_sorting, quant_1x128
+
+        R = x_q_u8.shape[0]
+        dev = x_q_u8.device
+        out = torch.zeros((R, self.H), dtype=self.out_dtype, device=dev)
+        if R == 0:
+            return out
+        sid, sw, seid, npp = moe_sorting(topk_ids, topk_weights, num_experts=self.E,
+                                         block_size=self.tile_m, expert_mask=self.expert_mask)
+        nblk = seid.numel()
+        out1 = torch.empty((R, self.k, self.I), dtype=self.mid_dtype, device=dev)
+        # rows of non-local routes are never written by stage 1; keep them finite for the quantiser
+        out1.zero_()
+        xs_t = x_scale.t().contiguous()
+        self.gemm1(out1, x_q_u8, self.w1, xs_t, self.w1_scale, sid, seid, sw, npp, R, self.I, self.H,
+                   nblk, None)
+        a2_q, a2_s = quant_1x128(out1.view(R * self.k, self.I))
+        routes = torch.empty((R * self.k, self.H), dtype=self.out_dtype, device=dev)
+        self.gemm2(routes, a2_q, self.w2, a2_s, self.w2_scale, sid, seid, sw, npp, R, self.H, self.I,
+                   nblk, None)
+        valid = self.expert_mask[topk_ids.long()].to(torch.uint8).contiguous()
+        self.reduce(routes, out, valid, R, None)
+        return out
