@@ -241,11 +241,11 @@ def cpu_baseline_dense(M, N, K, budget_s=12.0):
         t0 = time.perf_counter()
         O.run_torch_blockscale(a_q, b_q, a_s, b_s)
         times.append(time.perf_counter() - t0)
-        if len(times) >= 5 or time.perf_counter() - t_start > budget_s:
+        if len(times) >= 200 or time.perf_counter() - t_start > budget_s:
             break
     best = min(times)
     return {"value": 2.0 * M * N * K / best / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
-            "kind": "port", "sample": f"full {M}x{N}x{K} GEMM incl. dequantisation, best of {len(times)} runs",
+            "kind": "port", "sample": f"full {M}x{N}x{K} GEMM incl. dequantisation, best of {len(times)} runs in ~{budget_s:.0f} s",
             "seconds": best}
 
 

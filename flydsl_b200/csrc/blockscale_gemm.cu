@@ -762,8 +762,11 @@ static int launch_bn(int bn, const CUtensorMap& tmap_a, const CUtensorMap& tmap_
 
 static inline int cdiv(int a, int b) { return (a + b - 1) / b; }
 
-// Tile-width heuristic (role of select_tile_config in the reference's test): the widest tile whose
-// tile count still fills the SMs; among those, the fewest rounds of the persistent loop.
+// Tile-width heuristic (role of select_tile_config in the reference's test). Cost model per K block
+// of one tile, fitted to measurements on B200: the tensor-core side costs a fixed ~360 ns (MMA
+// issue, TMEM round trip of the promotion) plus ~0.9 ns per output column; the memory side costs
+// the tile's weight bytes at one SM's share of HBM bandwidth when few row blocks share them. The
+// persistent loop runs ceil(tiles / SMs) rounds; pick the width with the smallest total.
 static int pick_block_n(int m_blocks, int n_cols, int sms, bool moe1) {
   const int cands[4] = {256, 128, 64, 32};
   int best = 128;
@@ -774,8 +777,13 @@ static int pick_block_n(int m_blocks, int n_cols, int sms, bool moe1) {
     const int cols = moe1 ? bn / 2 : bn;
     const long tiles = static_cast<long>(m_blocks) * cdiv(n_cols, cols);
     const long rounds = (tiles + sms - 1) / sms;
-    // per-tile time ~ max(MMA, B traffic) is proportional to bn, with a fixed per-tile overhead
-    const double cost = rounds * (bn + 24.0);
+    const double compute_ns = 360.0 + 0.9 * bn;
+    // weight tile bytes per K block over ~44 GB/s per SM; row blocks that run concurrently on the
+    // same weight tile share one HBM read through L2
+    const int sharing = m_blocks < 8 ? (m_blocks < 1 ? 1 : m_blocks) : 8;
+    const double memory_ns = (bn * 128.0 / 44.0) / sharing;
+    const double per_kb = compute_ns > memory_ns ? compute_ns : memory_ns;
+    const double cost = rounds * per_kb;
     if (cost < best_cost - 1e-9) {
       best_cost = cost;
       best = bn;
