@@ -7,7 +7,7 @@
 //   warp 0      producer: TMA tensor load of the A tile (dense) and bulk copies of the repacked,
 //               pre-swizzled weight tile into a multistage shared-memory ring
 //   warp 1      MMA issuer: tcgen05.mma kind::f8f6f4, 128 x BN x 32, four per 128-wide K block,
-//               each K block into a fresh TMEM accumulator buffer (two buffers, ping-pong)
+//               each K block into a fresh TMEM accumulator buffer (512/BN buffers in rotation)
 //   warps 2-3   MoE only: gather activation rows by sorted id with cp.async into the same swizzled
 //               image TMA would have produced
 //   warps 4-11  epilogue: tcgen05.ld the K-block partial (loads pipelined against the FMAs),
@@ -32,6 +32,17 @@ constexpr int kATileBytes = BM * BK;
 constexpr int kRegionBytes = BM * 128;  // one 64-column (16-bit) slab of the staged output tile
 
 enum Mode : int { kDense = 0, kMoe1 = 1, kMoe2 = 2 };
+
+#ifdef FLYB200_DBG_TRACE
+// Debug build only: per-event timestamps of CTA 0 (event type, iteration, clock64).
+__device__ long long g_trace[8 * 512];
+__device__ __forceinline__ void trace(int type, unsigned it) {
+  if (blockIdx.x == 0 && it < 512) g_trace[type * 512 + it] = clock64();
+}
+#define FLYB200_TRACE(type, it) trace(type, it)
+#else
+#define FLYB200_TRACE(type, it)
+#endif
 
 struct GemmParams {
   const uint8_t* a;        // MoE: activation rows to gather from (dense uses the tensor map)
@@ -70,7 +81,11 @@ struct Cfg {
   static constexpr int kAvail = 232448 - 1024 - kMiscBytes;  // 227 KB less alignment slack and misc
   static constexpr int kStagesFit = (kAvail - kCBytes) / kStageBytes;
   static constexpr int kStages = kStagesFit > 10 ? 10 : kStagesFit;
-  static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;  // two accumulator buffers
+  // Accumulator buffers in TMEM (512 columns per SM): as many as fit, at most 8. The MMA issuer may
+  // run that many K blocks ahead of the epilogue, which hides the MMA-completion -> promotion ->
+  // release round trip (about a thousand cycles) for the narrow tiles.
+  static constexpr int kAccBufs = (512 / BN) > 8 ? 8 : (512 / BN);
+  static constexpr int kTmemCols = BN * kAccBufs;
   static constexpr int kCH = BN / 4;  // columns per epilogue thread per column group
   static constexpr int kSmemBytes = kStages * kStageBytes + kCBytes + kMiscBytes + 1024;
   static_assert(kStages >= 3, "pipeline too shallow");
@@ -169,24 +184,34 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   uint8_t* misc = smem_al + kStages * C::kStageBytes + C::kCBytes;
   long long* row_off = reinterpret_cast<long long*>(misc);                 // [128], MoE staged output
   const uint32_t bar_base = misc_base + 1024;
+  // Barriers. full[s]: operands of stage s have landed. done[i]: the MMAs of K-block iteration i
+  // (mod kDone) have finished -- ONE tcgen05.commit per K block serves both consumers: the loaders
+  // (stage it % kStages may be refilled once iteration it - kStages is done) and the epilogue
+  // (partials of iteration it are in TMEM). kDone > kStages and >= kAccBufs, so a barrier is never
+  // re-armed before every waiter of its previous phase has passed. tempty[b]: the epilogue has read
+  // accumulator buffer b.
+  constexpr int kAccBufs = C::kAccBufs;
+  constexpr int kDone = kStages + kAccBufs;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
-  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
-  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
-  const uint32_t epi_bar = bar_base + 8u * (2 * kStages + 4);
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc + 1024 + 8 * (2 * kStages + 5));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 1024 + 8 * (2 * kStages + 5) + 4);
+  auto done_bar = [&](uint32_t i) { return bar_base + 8u * (kStages + i); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (kStages + kDone + b); };
+  const uint32_t epi_bar = bar_base + 8u * (kStages + kDone + kAccBufs);
+  volatile uint32_t* tmem_slot =
+      reinterpret_cast<volatile uint32_t*>(misc + 1024 + 8 * (kStages + kDone + kAccBufs + 1));
+  volatile int* abort_flag =
+      reinterpret_cast<volatile int*>(misc + 1024 + 8 * (kStages + kDone + kAccBufs + 1) + 4);
+  // wait until the stage that iteration `it` is about to overwrite has been consumed
+  auto wait_stage_free = [&](uint32_t it, int code) -> bool {
+    if (it < static_cast<uint32_t>(kStages)) return true;
+    const uint32_t j = it - kStages;
+    return mbar_wait(done_bar(j % kDone), (j / kDone) & 1, abort_flag, p.err, code);
+  };
 
   constexpr int kFullCount = (MODE == kDense) ? 1 : 3;  // producer (+ two gather warps)
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(full_bar(s), kFullCount);
-      mbar_init(empty_bar(s), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), kEpiWarps);  // one arrival per epilogue warp
-    }
+    for (int s = 0; s < kStages; ++s) mbar_init(full_bar(s), kFullCount);
+    for (int i = 0; i < kDone; ++i) mbar_init(done_bar(i), 1);
+    for (int b = 0; b < kAccBufs; ++b) mbar_init(tempty_bar(b), kEpiWarps);  // one arrival per warp
     mbar_init(epi_bar, kEpiWarps);
     *abort_flag = 0;
     fence_proxy_async_smem();
@@ -245,8 +270,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
-          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.err, kErrWaitSmemEmpty)) {
+          if (!wait_stage_free(it, kErrWaitSmemEmpty)) {
             alive = false;
             break;
           }
@@ -289,23 +313,32 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
-          const int buf = it & 1;
-          const uint32_t tph = (it >> 1) & 1;
+          const int buf = it % kAccBufs;
+          const uint32_t tph = (it / kAccBufs) & 1;
           if (!mbar_wait(tempty_bar(buf), tph ^ 1, abort_flag, p.err, kErrWaitTmemEmpty) ||
               !mbar_wait(full_bar(s), ph, abort_flag, p.err, kErrWaitSmemFull)) {
             alive = false;
             break;
           }
+          FLYB200_TRACE(1, it);
           tc_fence_after();
           const uint32_t sa = smem_base + s * C::kStageBytes;
           const uint64_t adesc = umma_desc_sw128(sa);
           const uint64_t bdesc = umma_desc_sw128(sa + kATileBytes);
+#ifdef FLYB200_DBG_SAMEBUF
+          const uint32_t d = tmem_base;
+#else
           const uint32_t d = tmem_base + buf * BN;
+#endif
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k)
+#ifdef FLYB200_DBG_ACC1
+            tc_mma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, 1u);
+#else
             tc_mma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
-          tc_commit(empty_bar(s));    // stage reusable once these MMAs have read it
-          tc_commit(tfull_bar(buf));  // partial sums of this K block are in TMEM
+#endif
+          tc_commit(done_bar(it % kDone));  // stage reusable + partial sums of this K block in TMEM
+          FLYB200_TRACE(2, it);
         }
       }
     } else if (MODE != kDense && warp >= 2) {
@@ -344,8 +377,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
-          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.err, kErrWaitGather)) {
+          if (!wait_stage_free(it, kErrWaitGather)) {
             alive = false;
             break;
           }
@@ -385,12 +417,6 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int half = ew >> 2;    // which CH-wide slice of each column group
     const int r = quad * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-#ifndef FLYB200_LD_WIDE
-#define FLYB200_LD_WIDE 16
-#endif
-    constexpr int LD = (CH > 32) ? FLYB200_LD_WIDE : CH;  // columns per tcgen05.ld (two buffers in flight; bounded by registers)
-    constexpr int NSUB = CH / LD;            // loads per column group
-    constexpr int NQ = 2 * NSUB;             // loads per K block (two column groups)
     OutT* const out = reinterpret_cast<OutT*>(p.out);
     const bool store_thread = (threadIdx.x == kEpiWarp0 * 32);
 
@@ -406,105 +432,157 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       return __all_sync(0xffffffffu, ok);
     };
 
-    for (int tile = blockIdx.x; tile < walk.total && alive; tile += gridDim.x) {
+    // What the promotion loop needs per tile: where this thread's scales live (32-bit indices, so
+    // that few registers stay live across the loop; addresses are formed at use).
+    struct ScaleCtx {
+      int sa_idx;      // scale_a[kb * sa_stride + sa_idx]
+      int sa_stride;
+      int sb_idx0;     // scale_b[sb_idx0 + kb] for column group 0
+      int sb_idx1;     // ... group 1
+      bool row_ok;
+    };
+    // What the store phase needs; recomputed after the loop instead of being kept live through it.
+    struct OutCtx {
+      size_t out_row;
+      int n0;                // first output column of the tile
+      int col0, col1;        // tile-relative first output column of group 0 / group 1
+      int m_blk;
+      float route_w;
+      bool row_ok;
+    };
+    // decode (token, slot) of this thread's row for MoE tiles
+    auto moe_row = [&](int m_blk, int& t, int& slot) -> bool {
+      t = 0; slot = 0;
+      if (r >= p.tile_m) return false;
+      const int id = p.sorted_ids[m_blk * p.tile_m + r];
+      const int tt = id & 0xFFFFFF;
+      const int ss = static_cast<unsigned>(id) >> 24;
+      if (tt >= p.M || ss >= p.topk) return false;
+      t = tt; slot = ss;
+      return true;
+    };
+    // Fills the scale context of `tile`; false if the tile has nothing to do (MoE block without expert).
+    auto setup_scales = [&](int tile, ScaleCtx& c) -> bool {
       int m_blk, n_tile;
       walk.decode(tile, m_blk, n_tile);
-
-      // Row identity, scale pointers and output columns of this thread for this tile.
-      bool row_ok;
-      const float* sa_ptr;      // + kb * sa_stride
-      size_t sa_stride;
-      const float* sb_ptr0;     // + kb
-      const float* sb_ptr1;
-      int n0;                   // first output column of the tile
-      int col0, col1;           // tile-relative first output column of group 0 / group 1
-      size_t out_row = 0;
-      float route_w = 1.0f;
       if constexpr (MODE == kDense) {
         const int row = m_blk * BM + r;
-        row_ok = row < p.M;
-        sa_ptr = p.scale_a + (row_ok ? row : 0);
-        sa_stride = static_cast<size_t>(p.M);
-        n0 = n_tile * BN;
-        col0 = half * CH;
-        col1 = BN / 2 + half * CH;
+        c.row_ok = row < p.M;
+        c.sa_idx = c.row_ok ? row : 0;
+        c.sa_stride = p.M;
+        const int n0 = n_tile * BN;
         const int nblk_max = (p.N + 127) / 128 - 1;
-        sb_ptr0 = p.scale_b + static_cast<size_t>(min((n0 + col0) / 128, nblk_max)) * KB;
-        sb_ptr1 = p.scale_b + static_cast<size_t>(min((n0 + col1) / 128, nblk_max)) * KB;
-        out_row = static_cast<size_t>(row) * p.N;
+        c.sb_idx0 = min((n0 + half * CH) / 128, nblk_max) * KB;
+        c.sb_idx1 = min((n0 + BN / 2 + half * CH) / 128, nblk_max) * KB;
       } else {
         const int e = p.expert_ids[m_blk];
-        if (e < 0 || e >= p.experts) continue;
-        int t = 0, slot = 0;
-        row_ok = false;
-        if (r < p.tile_m) {
-          const int id = p.sorted_ids[m_blk * p.tile_m + r];
-          t = id & 0xFFFFFF;
-          slot = static_cast<unsigned>(id) >> 24;
-          row_ok = (t < p.M) && (slot < p.topk);
-          if (row_ok && p.doweight) route_w = p.sorted_weights[m_blk * p.tile_m + r];
-        }
-        if (!row_ok) { t = 0; slot = 0; }
+        if (e < 0 || e >= p.experts) return false;
+        int t, slot;
+        c.row_ok = moe_row(m_blk, t, slot);
         if constexpr (MODE == kMoe1) {
-          sa_ptr = p.scale_a + t;
-          sa_stride = static_cast<size_t>(p.M);
-          n0 = n_tile * (BN / 2);
-          col0 = col1 = half * CH;
+          c.sa_idx = t;
+          c.sa_stride = p.M;
           const int nb_exp = (2 * p.N) / 128;  // scale rows per expert
-          const int cg = min(n0 + col0, p.N - 1);
-          sb_ptr0 = p.scale_b + (static_cast<size_t>(e) * nb_exp + cg / 128) * KB;
-          sb_ptr1 = p.scale_b + (static_cast<size_t>(e) * nb_exp + (p.N + cg) / 128) * KB;
-          out_row = (static_cast<size_t>(t) * p.topk + slot) * p.N;
+          const int cg = min(n_tile * (BN / 2) + half * CH, p.N - 1);
+          c.sb_idx0 = (e * nb_exp + cg / 128) * KB;
+          c.sb_idx1 = (e * nb_exp + (p.N + cg) / 128) * KB;
         } else {
-          sa_ptr = p.scale_a + static_cast<size_t>(t) * p.topk + slot;
-          sa_stride = static_cast<size_t>(p.M) * p.topk;
-          n0 = n_tile * BN;
-          col0 = half * CH;
-          col1 = BN / 2 + half * CH;
+          c.sa_idx = t * p.topk + slot;
+          c.sa_stride = p.M * p.topk;
+          const int n0 = n_tile * BN;
           const int nb_exp = p.N / 128;
-          sb_ptr0 = p.scale_b + (static_cast<size_t>(e) * nb_exp + min(n0 + col0, p.N - 1) / 128) * KB;
-          sb_ptr1 = p.scale_b + (static_cast<size_t>(e) * nb_exp + min(n0 + col1, p.N - 1) / 128) * KB;
-          out_row = p.accumulate ? static_cast<size_t>(t) * p.N
-                                 : (static_cast<size_t>(t) * p.topk + slot) * p.N;
+          c.sb_idx0 = (e * nb_exp + min(n0 + half * CH, p.N - 1) / 128) * KB;
+          c.sb_idx1 = (e * nb_exp + min(n0 + BN / 2 + half * CH, p.N - 1) / 128) * KB;
         }
       }
+      return true;
+    };
+    auto setup_output = [&](int tile, OutCtx& c) {
+      int m_blk, n_tile;
+      walk.decode(tile, m_blk, n_tile);
+      c.m_blk = m_blk;
+      c.route_w = 1.0f;
+      if constexpr (MODE == kDense) {
+        const int row = m_blk * BM + r;
+        c.row_ok = row < p.M;
+        c.n0 = n_tile * BN;
+        c.col0 = half * CH;
+        c.col1 = BN / 2 + half * CH;
+        c.out_row = static_cast<size_t>(row) * p.N;
+      } else {
+        int t, slot;
+        c.row_ok = moe_row(m_blk, t, slot);
+        if (c.row_ok && p.doweight) c.route_w = p.sorted_weights[m_blk * p.tile_m + r];
+        if constexpr (MODE == kMoe1) {
+          c.n0 = n_tile * (BN / 2);
+          c.col0 = c.col1 = half * CH;
+          c.out_row = (static_cast<size_t>(t) * p.topk + slot) * p.N;
+        } else {
+          c.n0 = n_tile * BN;
+          c.col0 = half * CH;
+          c.col1 = BN / 2 + half * CH;
+          c.out_row = p.accumulate ? static_cast<size_t>(t) * p.N
+                                   : (static_cast<size_t>(t) * p.topk + slot) * p.N;
+        }
+      }
+    };
+    // first tile >= `tile` (stepping by the grid) that has work; walk.total if none
+    auto find_tile = [&](int tile, ScaleCtx& c) -> int {
+      while (tile < walk.total && !setup_scales(tile, c)) tile += gridDim.x;
+      return tile < walk.total ? tile : walk.total;
+    };
+    auto ld_sa = [&](const ScaleCtx& c, int kb) -> float {
+      return (kb < KB && c.row_ok)
+                 ? __ldg(p.scale_a + static_cast<size_t>(kb) * c.sa_stride + c.sa_idx) : 0.f;
+    };
+    auto ld_sb = [&](int idx, int kb) -> float { return kb < KB ? __ldg(p.scale_b + idx + kb) : 0.f; };
 
+    // Scales are prefetched kRing K blocks ahead into a register ring; the ring of the NEXT tile is
+    // loaded before the current tile's store phase so that its latency hides behind the stores.
+    constexpr int kRing = 2;
+    ScaleCtx cur;
+    float ring_a[kRing], ring_b0[kRing], ring_b1[kRing];
+    int tile = find_tile(blockIdx.x, cur);
+    if (tile < walk.total) {
+#pragma unroll
+      for (int j = 0; j < kRing; ++j) {
+        ring_a[j] = ld_sa(cur, j);
+        ring_b0[j] = ld_sb(cur.sb_idx0, j);
+        ring_b1[j] = ld_sb(cur.sb_idx1, j);
+      }
+    }
+
+#ifndef FLYB200_LD_WIDE
+#define FLYB200_LD_WIDE 16
+#endif
+    constexpr int LDW = (CH > 32) ? FLYB200_LD_WIDE : CH;  // columns per tcgen05.ld
+    constexpr int NSUB = CH / LDW;            // loads per column group
+    constexpr int NQ = 2 * NSUB;              // loads per K block (two column groups)
+
+    while (tile < walk.total && alive) {
       // acc[0 .. CH/2) = column group 0, acc[CH/2 .. CH) = column group 1, two columns per float2.
       float2 acc[CH];
 #pragma unroll
       for (int j = 0; j < CH; ++j) acc[j] = make_float2(0.f, 0.f);
 
-      // Scales are prefetched four K blocks ahead into a register ring.
-      float ring_a[4], ring_b0[4], ring_b1[4];
+      for (int kb0 = 0; kb0 < KB && alive; kb0 += kRing) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const bool in = j < KB;
-        ring_a[j] = (in && row_ok) ? __ldg(sa_ptr + j * sa_stride) : 0.f;
-        ring_b0[j] = in ? __ldg(sb_ptr0 + j) : 0.f;
-        ring_b1[j] = in ? __ldg(sb_ptr1 + j) : 0.f;
-      }
-
-      for (int kb0 = 0; kb0 < KB && alive; kb0 += 4) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < kRing; ++j) {
           const int kb = kb0 + j;
           if (kb < KB && alive) {
-            const int buf = it & 1;
-            const uint32_t tph = (it >> 1) & 1;
+            const int buf = it % kAccBufs;
             const float s0 = ring_a[j] * ring_b0[j];
             const float s1 = ring_a[j] * ring_b1[j];
-            {
-              const int nk = kb + 4;
-              const bool in = nk < KB;
-              ring_a[j] = (in && row_ok) ? __ldg(sa_ptr + nk * sa_stride) : 0.f;
-              ring_b0[j] = in ? __ldg(sb_ptr0 + nk) : 0.f;
-              ring_b1[j] = in ? __ldg(sb_ptr1 + nk) : 0.f;
-            }
+            ring_a[j] = ld_sa(cur, kb + kRing);
+            ring_b0[j] = ld_sb(cur.sb_idx0, kb + kRing);
+            ring_b1[j] = ld_sb(cur.sb_idx1, kb + kRing);
             // warp-uniform outcome: the tcgen05.ld below needs the whole warp
-            const bool got = mbar_wait(tfull_bar(buf), tph, abort_flag, p.err, kErrWaitTmemFull);
+            const bool got = mbar_wait(done_bar(it % kDone), (it / kDone) & 1, abort_flag, p.err,
+                                       kErrWaitTmemFull);
             if (!__all_sync(0xffffffffu, got)) {
               alive = false;
             } else {
+              if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(3, it);
               tc_fence_after();
 #ifdef FLYB200_DBG_SKIP_PROMOTE
               if (kb + 1 < KB) {
@@ -516,31 +594,35 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               }
 #endif
               const uint32_t t0 = tmem_base + lane_base + buf * BN + half * CH;
-              // load q covers LD columns: q < NSUB -> group 0, else group 1 (BN/2 columns further)
-              auto taddr = [&](int q) {
-                return t0 + (q >= NSUB ? BN / 2 : 0) + (q % NSUB) * LD;
+              // Loads of LDW columns are software-pipelined against the FMAs of the previous
+              // load (two register buffers). Measured on B200: wider single-shot loads (32/64
+              // columns per wait) are slower -- the TMEM read port, not latency, bounds a K block
+              // at roughly 350 cycles, and the extra registers spill.
+              auto taddr = [&](int q) {  // load q: q < NSUB -> group 0, else group 1
+                return t0 + (q >= NSUB ? BN / 2 : 0) + (q % NSUB) * LDW;
               };
-              uint32_t va[LD], vb[LD];
-              tmem_ld<LD>(taddr(0), va);
-              tmem_wait_dep<LD>(va);
+              uint32_t va[LDW], vb[LDW];
+              tmem_ld<LDW>(taddr(0), va);
+              tmem_wait_dep<LDW>(va);
 #pragma unroll
               for (int q = 0; q < NQ; ++q) {
-                uint32_t* cur = (q & 1) ? vb : va;
-                uint32_t* nxt = (q & 1) ? va : vb;
-                if (q + 1 < NQ) tmem_ld<LD>(taddr(q + 1), nxt);   // in flight during the FMAs
+                uint32_t* cv = (q & 1) ? vb : va;
+                uint32_t* nv = (q & 1) ? va : vb;
+                if (q + 1 < NQ) tmem_ld<LDW>(taddr(q + 1), nv);   // in flight during the FMAs
                 const float s = (q >= NSUB) ? s1 : s0;
                 const float2 s2 = make_float2(s, s);
-                float2* a = acc + (q >= NSUB ? CH / 2 : 0) + (q % NSUB) * (LD / 2);
+                float2* a = acc + (q >= NSUB ? CH / 2 : 0) + (q % NSUB) * (LDW / 2);
 #pragma unroll
-                for (int c = 0; c < LD / 2; ++c)
-                  a[c] = __ffma2_rn(make_float2(__uint_as_float(cur[2 * c]),
-                                                __uint_as_float(cur[2 * c + 1])), s2, a[c]);
+                for (int c = 0; c < LDW / 2; ++c)
+                  a[c] = __ffma2_rn(make_float2(__uint_as_float(cv[2 * c]),
+                                                __uint_as_float(cv[2 * c + 1])), s2, a[c]);
                 if (q + 1 < NQ) {
-                  tmem_wait_dep<LD>(nxt);
+                  tmem_wait_dep<LDW>(nv);
                   if (q + 2 == NQ) {  // every load of this buffer has landed: hand it back
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(tempty_bar(buf));
+                    if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(4, it);
                   }
                 }
               }
@@ -551,8 +633,29 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       if (!alive) break;
 
-      // ---- output ----
+      if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(0, it);
+      // next tile's scale context and first scales: issued now, consumed after the store phase
+      ScaleCtx nxt;
+      float nring_a[kRing], nring_b0[kRing], nring_b1[kRing];
+      const int tile_next = find_tile(tile + gridDim.x, nxt);
+      if (tile_next < walk.total) {
+#pragma unroll
+        for (int j = 0; j < kRing; ++j) {
+          nring_a[j] = ld_sa(nxt, j);
+          nring_b0[j] = ld_sb(nxt.sb_idx0, j);
+          nring_b1[j] = ld_sb(nxt.sb_idx1, j);
+        }
+      }
+
+      OutCtx oc;
+      setup_output(tile, oc);
+      const bool row_ok = oc.row_ok;
+      const int m_blk = oc.m_blk;
+      const int n0 = oc.n0, col0 = oc.col0, col1 = oc.col1;
+      const size_t out_row = oc.out_row;
+      const float route_w = oc.route_w;
       const float* accf = reinterpret_cast<const float*>(acc);  // [0,CH) group 0, [CH,2CH) group 1
+      // ---- output ----
       if constexpr (C::kStaged) {
         // (1) the staging tile must be free: previous TMA store has read it / previous tile's
         //     cooperative row stores are done (every thread passes this barrier after its own)
@@ -560,6 +663,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (store_thread) bulk_wait_group_read0();
         }
         if (!epi_sync()) { alive = false; break; }
+        if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(5, it);
         // (2) thread r writes its columns of row r into the swizzled staging tile
         auto stage8 = [&](int col, const float* v) {   // col: tile-relative output column, % 8 == 0
           const uint32_t addr = cstage_base + (col >> 6) * kRegionBytes + r * 128 +
@@ -594,7 +698,9 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         } else {
           fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA store
         }
+        if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(6, it);
         if (!epi_sync()) { alive = false; break; }
+        if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(7, it);
         // (3) write the tile out
         if constexpr (MODE == kDense) {
           if (store_thread) {
@@ -666,6 +772,16 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
         }
       }
+
+      // rotate to the prefetched tile
+      cur = nxt;
+#pragma unroll
+      for (int j = 0; j < kRing; ++j) {
+        ring_a[j] = nring_a[j];
+        ring_b0[j] = nring_b0[j];
+        ring_b1[j] = nring_b1[j];
+      }
+      tile = tile_next;
     }
     if constexpr (C::kStaged && MODE == kDense) {
       if (store_thread) bulk_wait_group0();  // the last tile's TMA store must finish before exit
@@ -802,6 +918,12 @@ static int check_ptr(const void* p, size_t align, const char* name) {
 }  // namespace flyb200
 
 using namespace flyb200;
+
+#ifdef FLYB200_DBG_TRACE
+extern "C" int flyb200_debug_read_trace(long long* host, int n) {
+  return cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * n) == cudaSuccess ? 0 : -3;
+}
+#endif
 
 extern "C" int flyb200_blockscale_gemm(void* c, const void* a, const void* b_repacked,
                                        const float* scale_a_t, const float* scale_b, int32_t M,

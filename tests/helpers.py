@@ -24,11 +24,18 @@ def bf16_from_bits(arr):
     return torch.from_numpy(np.ascontiguousarray(arr)).view(torch.bfloat16)
 
 
-def assert_close_to_oracle(out, ref, what=""):
+# 16-bit ATOMIC accumulation (stage 2, accumulate=True, f16/bf16 output) rounds the running sum to
+# 16 bits at every one of the top-k adds, in a non-deterministic order; the reference has the same
+# property (its docstring warns about fp16 atomics, kernels/moe_blockscale_2stage.py:1249-1252).
+# Those cases get twice the max-error budget; the cosine bar is unchanged.
+MAX_REL_ATOMIC16 = 2e-2
+
+
+def assert_close_to_oracle(out, ref, what="", max_rel=MAX_REL):
     from oracle.blockscale_ref import cosine, max_rel_err
 
     out, ref = out.detach().float().cpu(), ref.detach().float().cpu()
     assert torch.isfinite(out).all(), f"{what}: non-finite output"
     mr, cs = max_rel_err(out, ref), cosine(out, ref)
-    assert mr <= MAX_REL and cs >= MIN_COS, f"{what}: max_rel={mr:.3e} (<= {MAX_REL}), cosine={cs:.6f} (>= {MIN_COS})"
+    assert mr <= max_rel and cs >= MIN_COS, f"{what}: max_rel={mr:.3e} (<= {max_rel}), cosine={cs:.6f} (>= {MIN_COS})"
     return mr, cs

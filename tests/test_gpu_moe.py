@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from oracle import blockscale_ref as O
-from tests.helpers import assert_close_to_oracle, fp8_from_u8, load_golden
+from tests.helpers import MAX_REL, MAX_REL_ATOMIC16, assert_close_to_oracle, fp8_from_u8, load_golden
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -140,7 +140,8 @@ def test_stage2_vs_golden(out_dtype, accumulate, tile_m):
         out = torch.empty(T, H, dtype=tdt, device=DEV)
         compile_moe_reduction(topk=k, model_dim=H, dtype_str=out_dtype)(routes.view(T, k, H), out, None, T, None)
     torch.cuda.synchronize()
-    assert_close_to_oracle(out, t["out2"], f"stage2 {out_dtype} acc={accumulate} tile_m={tile_m}")
+    budget = MAX_REL_ATOMIC16 if (accumulate and out_dtype != "f32") else MAX_REL
+    assert_close_to_oracle(out, t["out2"], f"stage2 {out_dtype} acc={accumulate} tile_m={tile_m}", max_rel=budget)
 
 
 def test_gemm2_ex_reduce_mode_matches_atomic():
@@ -160,7 +161,8 @@ def test_gemm2_ex_reduce_mode_matches_atomic():
         exe(out, *args)
         torch.cuda.synchronize()
         outs[mode] = out
-        assert_close_to_oracle(out, t["out2"], f"gemm2_ex {mode}")
+        assert_close_to_oracle(out, t["out2"], f"gemm2_ex {mode}",
+                               max_rel=MAX_REL_ATOMIC16 if mode == MoeGemm2Mode.ATOMIC else MAX_REL)
 
 
 # The reference's own shape grid (tests/kernels/test_moe_blockscale.py:195-210): tile 16x256x128; the
@@ -181,7 +183,8 @@ def test_layer_vs_oracle(T, H, I, E, k, mode):
     out = layer.forward(m["x_q"].to(DEV), xs_t, m["topk_ids"].to(DEV), m["topk_weights"].to(DEV))
     torch.cuda.synchronize()
     assert _lib.query_device_error() == 0
-    assert_close_to_oracle(out, ref, f"layer {T},{H},{I},{E},{k} {mode}")
+    assert_close_to_oracle(out, ref, f"layer {T},{H},{I},{E},{k} {mode}",
+                           max_rel=MAX_REL_ATOMIC16 if mode == "atomic" else MAX_REL)
     if mode == "reduce":  # fixed summation order: bitwise repeatable
         out2 = layer.forward(m["x_q"].to(DEV), xs_t, m["topk_ids"].to(DEV), m["topk_weights"].to(DEV))
         torch.cuda.synchronize()
