@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_int, c_int32, c_int64, c_void_p, POINTER
+from ctypes import c_char_p, c_int, c_int32, c_int64, c_size_t, c_void_p, POINTER
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("FLYB200_LIB_PATH") or os.path.join(_PKG_DIR, "lib", "libflyb200.so")
@@ -25,8 +25,8 @@ BF16, F16, F32 = 0, 1, 2
 class GemmCfg(ctypes.Structure):
     """Mirror of flyb200_gemm_cfg."""
 
-    _fields_ = [("block_n", c_int32), ("max_ctas", c_int32), ("reserved0", c_int32),
-                ("reserved1", c_int32)]
+    _fields_ = [("block_n", c_int32), ("max_ctas", c_int32), ("path", c_int32),
+                ("split_k", c_int32)]
 
 
 class Flyb200Error(RuntimeError):
@@ -46,6 +46,9 @@ SIGNATURES = {
                                  c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "flyb200_moe_gemm1": (c_int, [c_void_p] * 9 + [c_int32] * 9 + [POINTER(GemmCfg), c_void_p]),
     "flyb200_moe_gemm2": (c_int, [c_void_p] * 9 + [c_int32] * 10 + [POINTER(GemmCfg), c_void_p]),
+    "flyb200_moe_gemm2_reduce": (c_int, [c_void_p] * 10 + [c_int32] * 9 + [POINTER(GemmCfg), c_void_p, c_size_t,
+                                         c_void_p]),
+    "flyb200_moe_gemm2_reduce_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32]),
     "flyb200_moe_reduce": (c_int, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
                                    c_void_p]),
     "flyb200_quant_1x128": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32,

@@ -22,7 +22,8 @@ OBJ_DIR = os.path.join(LIB_DIR, "obj")
 LIB_PATH = os.path.join(LIB_DIR, "libflyb200.so")
 INCLUDE_DIR = os.path.join(os.path.dirname(PKG_DIR), "include")
 
-SOURCES = ["api.cu", "repack.cu", "blockscale_gemm.cu", "moe_sort.cu", "moe_aux.cu"]
+SOURCES = ["api.cu", "repack.cu", "blockscale_gemm.cu", "decode_gemm.cu", "moe_sort.cu", "moe_aux.cu",
+           "moe_pipeline.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -825,8 +825,8 @@ static EncodeTiledFn encode_tiled_fn() {
 
 // Row-major 2-D tensor [rows, cols] of elem_bytes-wide elements; box = 128 bytes x box_rows rows;
 // 128-byte swizzle; out-of-range parts read as 0 / are not written.
-static int make_tensor_map(CUtensorMap* map, const void* base, int rows, int cols, int elem_bytes,
-                           int box_rows) {
+int make_tensor_map_2d(CUtensorMap* map, const void* base, int rows, int cols, int elem_bytes,
+                       int box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return set_error(FLYB200_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
@@ -915,6 +915,12 @@ static int check_ptr(const void* p, size_t align, const char* name) {
   return FLYB200_OK;
 }
 
+// decode_gemm.cu
+int launch_decode_gemm(void* c, const void* a, const void* b_repacked, const float* scale_a_t,
+                       const float* scale_b, int M, int N, int K, int out_dtype, int force_splits,
+                       cudaStream_t stream);
+bool decode_path_pays_off(int M, int N, int K);
+
 }  // namespace flyb200
 
 using namespace flyb200;
@@ -941,6 +947,17 @@ extern "C" int flyb200_blockscale_gemm(void* c, const void* a, const void* b_rep
   if (out_dtype != FLYB200_BF16 && out_dtype != FLYB200_F16)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "out_dtype must be BF16 or F16");
 
+  // Decode-size M: the swap-AB split-K kernel (decode_gemm.cu), unless a tile width or the tiled
+  // path was asked for explicitly.
+  const int path = cfg ? cfg->path : 0;
+  if (path < 0 || path > 2)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "cfg.path must be 0 (auto), 1 (tiled) or 2 (decode)");
+  if (path == 2 && M > 64)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "the decode path takes M <= 64 (got %d)", M);
+  if (path == 2 || (path == 0 && M <= 64 && !(cfg && cfg->block_n) && decode_path_pays_off(M, N, K)))
+    return launch_decode_gemm(c, a, b_repacked, scale_a_t, scale_b, M, N, K, out_dtype,
+                              cfg ? cfg->split_k : 0, reinterpret_cast<cudaStream_t>(stream));
+
   const int sms = sm_count();
   if (sms <= 0) return FLYB200_ERR_CUDA;
   const int m_blocks = cdiv(M, BM);
@@ -963,8 +980,8 @@ extern "C" int flyb200_blockscale_gemm(void* c, const void* a, const void* b_rep
   p.a_box_rows = M >= BM ? BM : ((M + 7) / 8) * 8;
 
   CUtensorMap tmap_a, tmap_c;
-  if ((rc = make_tensor_map(&tmap_a, a, M, K, 1, p.a_box_rows))) return rc;
-  if ((rc = make_tensor_map(&tmap_c, c, M, N, 2, p.a_box_rows))) return rc;
+  if ((rc = make_tensor_map_2d(&tmap_a, a, M, K, 1, p.a_box_rows))) return rc;
+  if ((rc = make_tensor_map_2d(&tmap_c, c, M, N, 2, p.a_box_rows))) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (out_dtype == FLYB200_BF16)
     return launch_bn<kDense, __nv_bfloat16>(bn, tmap_a, tmap_c, p, grid, st);

@@ -34,6 +34,7 @@ enum DeviceError : int {
   kErrWaitTmemFull = 4,   // epilogue gave up waiting for an accumulator
   kErrWaitGather = 5,     // gather warps gave up waiting for a free stage
   kErrWaitEpilogue = 6,   // an epilogue warp gave up waiting for the other epilogue warps
+  kErrWaitExchange = 7,   // decode kernel: split-K partials of a cluster neighbour never arrived
 };
 
 // ---- shared-memory address / mbarrier --------------------------------------------------------

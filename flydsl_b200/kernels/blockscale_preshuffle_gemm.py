@@ -18,11 +18,11 @@ _OUT = {"bf16": _lib.BF16, "fp16": _lib.F16}
 class BlockscaleGemmLauncher:
     """Callable returned by the factory. Holds only compile-time constants; buffers are the caller's."""
 
-    def __init__(self, M, N, K, out_dtype, block_n, name):
+    def __init__(self, M, N, K, out_dtype, block_n, name, path=0, split_k=0):
         self.M, self.N, self.K = int(M), int(N), int(K)
         self.out_dtype = out_dtype
         self._out_code = _OUT[out_dtype]
-        self._cfg = _lib.GemmCfg(int(block_n or 0), 0, 0, 0)
+        self._cfg = _lib.GemmCfg(int(block_n or 0), 0, int(path or 0), int(split_k or 0))
         self._cfg_ref = ctypes.byref(self._cfg)
         self.__name__ = name
         self._fn = _lib.load().flyb200_blockscale_gemm
@@ -52,12 +52,15 @@ def compile_blockscale_preshuffle_gemm(
     waves_per_eu: int = None,
     use_async_copy: bool = False,
     block_n: int = None,
+    path: str = "auto",
+    split_k: int = None,
 ):
     """Build a launcher for C = dequant(A) @ dequant(B)^T with 1x128 / 128x128 fp32 block scales.
 
     ``tile_m/tile_n/tile_k`` are validated like the reference does but do not pick the B200 tile
     (the MMA tile is 128 x block_n x 128; ``block_n`` in {32,64,128,256} overrides the built-in
-    heuristic). ``use_cshuffle_epilog``, ``waves_per_eu`` and ``use_async_copy`` are AMD tuning
+    heuristic; ``path`` = "auto" | "tiled" | "decode" picks the kernel: M <= 64 defaults to the
+    swap-AB split-K decode kernel, ``split_k`` its cluster size). ``use_cshuffle_epilog``, ``waves_per_eu`` and ``use_async_copy`` are AMD tuning
     switches, accepted and ignored.
     """
     if out_dtype not in ("fp16", "bf16"):
@@ -80,5 +83,10 @@ def compile_blockscale_preshuffle_gemm(
         raise ValueError(f"N ({N}) must be divisible by 16")
     if block_n not in (None, 0, 32, 64, 128, 256):
         raise ValueError(f"block_n must be one of 32, 64, 128, 256, got {block_n}")
-    name = f"bs_gemm_{out_dtype}_t128x{block_n or 'auto'}x128"
-    return BlockscaleGemmLauncher(M, N, K, out_dtype, block_n, name)
+    paths = {"auto": 0, "tiled": 1, "decode": 2}
+    if path not in paths:
+        raise ValueError(f"path must be one of {sorted(paths)}, got {path!r}")
+    if split_k not in (None, 0, 1, 2, 3, 4, 5, 6, 7, 8):
+        raise ValueError(f"split_k must be in 1..8, got {split_k}")
+    name = f"bs_gemm_{out_dtype}_t128x{block_n or 'auto'}x128_{path}"
+    return BlockscaleGemmLauncher(M, N, K, out_dtype, block_n, name, paths[path], split_k)

@@ -230,16 +230,25 @@ class _MoeGemm2ReduceWrapper:
             stream = torch.cuda.current_stream()
         inter = torch.empty(tokens_in * self._topk, self._model_dim, device=arg_out.device,
                             dtype=self._get_torch_dtype())
-        if not self._use_mask:
-            inter.zero_()
-        self._gemm2_exe(inter.view(-1), arg_x, arg_w, arg_scale_x, arg_scale_w,
-                        arg_sorted_token_ids, arg_expert_ids, arg_sorted_weights, arg_num_valid_ids,
-                        tokens_in, n_in, k_in, size_expert_ids_in, stream)
         if not self._use_mask and valid_mask is not None:
             logging.warning("valid_mask provided but use_mask=False; ignoring valid_mask")
-        self._reduce_exe(inter.view(tokens_in, self._topk, self._model_dim),
-                         arg_out.view(tokens_in, self._model_dim),
-                         valid_mask if self._use_mask else None, tokens_in, stream)
+        g = self._gemm2_exe
+        if int(n_in) != g.model_dim or int(k_in) != g.inter_dim:
+            raise ValueError(f"launcher was built for model_dim={g.model_dim}, inter_dim={g.inter_dim}; "
+                             f"got n={n_in}, k={k_in}")
+        mask_ptr = None
+        if self._use_mask:
+            if valid_mask is None or valid_mask.numel() != int(tokens_in) * self._topk or valid_mask.element_size() != 1:
+                raise ValueError("use_mask=True needs a 1-byte valid_mask [tokens, topk]")
+            mask_ptr = valid_mask.data_ptr()
+        # one C-ABI call: zero-fill (no mask) -> stage 2 per-route rows -> top-k reduce
+        _lib.check(_lib.load().flyb200_moe_gemm2_reduce(
+            arg_out.data_ptr(), arg_x.data_ptr(), arg_w.data_ptr(), arg_scale_x.data_ptr(),
+            arg_scale_w.data_ptr(), arg_sorted_token_ids.data_ptr(), arg_expert_ids.data_ptr(),
+            arg_sorted_weights.data_ptr(), arg_num_valid_ids.data_ptr(), mask_ptr, int(tokens_in),
+            g.model_dim, g.inter_dim, int(size_expert_ids_in), g.experts, g.topk, g.tile_m, g.doweight,
+            g.out_code, g._cfg_ref, inter.data_ptr(), inter.numel() * inter.element_size(),
+            _lib.stream_handle(stream)))
 
     @property
     def mode(self) -> str:

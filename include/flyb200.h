@@ -51,8 +51,8 @@ typedef enum flyb200_dtype {
 typedef struct flyb200_gemm_cfg {
   int32_t block_n;  /* MMA N / CTA tile width: 32, 64, 128 or 256; 0 = auto */
   int32_t max_ctas; /* cap on the persistent grid; 0 = one CTA per SM       */
-  int32_t reserved0;
-  int32_t reserved1;
+  int32_t path;     /* dense GEMM only: 0 = auto, 1 = tiled kernel, 2 = decode kernel (M <= 64) */
+  int32_t split_k;  /* decode kernel: K splits per weight tile (cluster size, 1..8); 0 = auto    */
 } flyb200_gemm_cfg;
 
 /* Weight repack [batch, N, K] (row-major fp8 bytes) -> per batch [K/128][N/8][8 rows][128 B], the
@@ -109,6 +109,23 @@ int flyb200_moe_gemm2(void* out, const void* a2, const void* w_repacked, const f
  * Replaces the launcher of compile_moe_reduction (kernels/moe_blockscale_2stage.py:2446-2638). */
 int flyb200_moe_reduce(const void* x, void* y, const uint8_t* valid_mask, int32_t T, int32_t k,
                        int32_t H, int32_t dtype, void* stream);
+
+/* Stage 2 in its deterministic "reduce" form as one call: the GEMM stores one row per (token, slot)
+ * route into `workspace` ([T*k, H] of out_dtype, BF16|F16), then the top-k reduce adds a token's
+ * rows in slot order into out [T, H]. valid_mask u8 [T,k] or NULL (NULL: the workspace is zeroed
+ * first). Replaces _MoeGemm2ReduceWrapper.__call__ (kernels/moe_blockscale_2stage.py:2642-2737),
+ * which allocates that intermediate itself on every call; here the caller owns it. */
+int flyb200_moe_gemm2_reduce(void* out, const void* a2, const void* w_repacked,
+                             const float* scale_x, const float* scale_w, const int32_t* sorted_ids,
+                             const int32_t* expert_ids, const float* sorted_weights,
+                             const int32_t* num_valid_ids, const uint8_t* valid_mask, int32_t T,
+                             int32_t H, int32_t I, int32_t num_blocks, int32_t E, int32_t k,
+                             int32_t tile_m, int32_t doweight, int32_t out_dtype,
+                             const flyb200_gemm_cfg* cfg, void* workspace, size_t workspace_bytes,
+                             void* stream);
+
+/* Bytes flyb200_moe_gemm2_reduce needs in `workspace`: T*k*H*sizeof(out_dtype). */
+size_t flyb200_moe_gemm2_reduce_workspace_bytes(int32_t T, int32_t k, int32_t H, int32_t out_dtype);
 
 /* 1x128 group quantiser: x [rows, cols] (in_dtype) -> q fp8 e4m3fn [rows, cols] and
  * scale_t f32 [cols/128, rows]; scale = amax/448 (0 -> 1). Replaces the host re-quantisation between

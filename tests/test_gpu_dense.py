@@ -9,7 +9,7 @@ from tests.helpers import assert_close_to_oracle, bf16_from_bits, fp8_from_u8, l
 pytestmark = pytest.mark.gpu
 
 
-def _run_dense(a_q, a_scale, b_q, b_scale, out_dtype="bf16", block_n=None, tiles=(64, 128, 128)):
+def _run_dense(a_q, a_scale, b_q, b_scale, out_dtype="bf16", block_n=None, tiles=(64, 128, 128), **kw):
     from flydsl_b200 import _lib
     from flydsl_b200.kernels import compile_blockscale_preshuffle_gemm
     from flydsl_b200.utils import shuffle_weight
@@ -18,7 +18,7 @@ def _run_dense(a_q, a_scale, b_q, b_scale, out_dtype="bf16", block_n=None, tiles
     M, K = a_q.shape
     N = b_q.shape[0]
     fn = compile_blockscale_preshuffle_gemm(M=M, N=N, K=K, tile_m=tiles[0], tile_n=tiles[1], tile_k=tiles[2],
-                                            out_dtype=out_dtype, block_n=block_n)
+                                            out_dtype=out_dtype, block_n=block_n, **kw)
     tdt = torch.bfloat16 if out_dtype == "bf16" else torch.float16
     c = torch.zeros((M, N), dtype=tdt, device=dev)
     b_sh = shuffle_weight(b_q.to(dev))
@@ -61,6 +61,22 @@ def test_dense_reference_shapes(M, N, K, out_dtype):
     ref = O.run_torch_blockscale(case["a_q"], case["b_q"], case["a_scale"], case["b_scale"], dtype=torch.float32)
     c = _run_dense(case["a_q"], case["a_scale"], case["b_q"], case["b_scale"], out_dtype=out_dtype)
     assert_close_to_oracle(c, ref, f"M={M} N={N} K={K} {out_dtype}")
+
+
+# Decode-size M runs on the swap-AB split-K kernel (cluster reduction through distributed shared
+# memory); every split factor must give the same answer within tolerance, including K ranges that do
+# not divide evenly, N tails and M = 1.
+@pytest.mark.parametrize("M,N,K", [(1, 256, 384), (5, 2112, 1024), (32, 1536, 7168), (64, 3072, 1536), (17, 320, 2304)])
+@pytest.mark.parametrize("split_k", [None, 1, 2, 3, 8])
+def test_decode_path_split_k(M, N, K, split_k):
+    case = O.make_dense_case(M, N, K, seed=M * 7 + N)
+    ref = O.run_torch_blockscale(case["a_q"], case["b_q"], case["a_scale"], case["b_scale"], dtype=torch.float32)
+    c = _run_dense(case["a_q"], case["a_scale"], case["b_q"], case["b_scale"], path="decode", split_k=split_k)
+    assert_close_to_oracle(c, ref, f"decode M={M} N={N} K={K} split_k={split_k}")
+    c2 = _run_dense(case["a_q"], case["a_scale"], case["b_q"], case["b_scale"], path="decode", split_k=split_k)
+    assert torch.equal(c, c2)  # fixed reduction order: bitwise repeatable
+    t = _run_dense(case["a_q"], case["a_scale"], case["b_q"], case["b_scale"], path="tiled")
+    assert_close_to_oracle(t, ref, f"tiled M={M} N={N} K={K}")
 
 
 def test_dense_config1_and_m_tail():
