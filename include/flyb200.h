@@ -127,6 +127,31 @@ int flyb200_moe_gemm2_reduce(void* out, const void* a2, const void* w_repacked,
 /* Bytes flyb200_moe_gemm2_reduce needs in `workspace`: T*k*H*sizeof(out_dtype). */
 size_t flyb200_moe_gemm2_reduce_workspace_bytes(int32_t T, int32_t k, int32_t H, int32_t out_dtype);
 
+/* flyb200_moe_gemm2_reduce for callers that cannot supply scratch memory (no counterpart in the
+ * reference, whose wrapper simply allocates): a bare C/C++ serving loop or plug-in callback that
+ * holds no device allocator, or a host that forbids cudaMalloc after start-up. The per-route rows go
+ * to a fixed array inside the library image instead of `workspace`; the call allocates nothing.
+ *   - Limit: T*k*H*sizeof(out_dtype) <= flyb200_moe_gemm2_reduce_noalloc_max_bytes() (16 MiB);
+ *     larger requests return FLYB200_ERR_WORKSPACE. Every GPU that loads the library holds those
+ *     16 MiB until the process exits.
+ *   - The array is shared by all calls on a device: calls whose kernels can overlap on the GPU race
+ *     on it; serialise them. Stale rows of an earlier call are cleared where this call would read
+ *     them.
+ *   - The first call on each device looks up the array's device address; make that first call
+ *     outside any stream capture.
+ * Arguments and result are those of flyb200_moe_gemm2_reduce without workspace/workspace_bytes. */
+int flyb200_moe_gemm2_reduce_noalloc(void* out, const void* a2, const void* w_repacked,
+                                     const float* scale_x, const float* scale_w,
+                                     const int32_t* sorted_ids, const int32_t* expert_ids,
+                                     const float* sorted_weights, const int32_t* num_valid_ids,
+                                     const uint8_t* valid_mask, int32_t T, int32_t H, int32_t I,
+                                     int32_t num_blocks, int32_t E, int32_t k, int32_t tile_m,
+                                     int32_t doweight, int32_t out_dtype,
+                                     const flyb200_gemm_cfg* cfg, void* stream);
+
+/* Size of the built-in scratch array used by flyb200_moe_gemm2_reduce_noalloc, in bytes. */
+size_t flyb200_moe_gemm2_reduce_noalloc_max_bytes(void);
+
 /* 1x128 group quantiser: x [rows, cols] (in_dtype) -> q fp8 e4m3fn [rows, cols] and
  * scale_t f32 [cols/128, rows]; scale = amax/448 (0 -> 1). Replaces the host re-quantisation between
  * the MoE stages (tests/kernels/test_moe_blockscale.py:346-361, pertoken_quant tests/utils.py:29-73). */
