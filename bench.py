@@ -498,7 +498,10 @@ def run_ours(args):
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
         "gpu_launches": args.steps,
         "roofline": {"bound": "tensor", "achieved": per_gpu_tflops, "peak": fp8_peak, "unit": "TFLOP/s",
-                     "frac": per_gpu_tflops / fp8_peak, "traffic": None,
+                     "frac": per_gpu_tflops / fp8_peak,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at N=1,
+                     # from the ncu capture summarised in profiles/bs_gemm_dense_M4096_N7168_K2048.md
+                     "traffic": 31.1e6 if world == 1 else None,
                      "peak_source": f"2 x bf16_tflops ({peaks['source']}); dense FP8 rate is twice bf16",
                      "frac_of_nominal_4500": per_gpu_tflops / 4500.0},
         "clocks": clk.summary(),
@@ -520,8 +523,58 @@ def run_ours(args):
         print(json.dumps(out))
 
 
+def run_probe(args):
+    """Small single-purpose runs for profiling (ncu) -- not the bench line. ``--probe moe`` runs the
+    MoE layer with 32 experts (1.4 GB of weights) and 512 tokens, the same 128 tokens per expert as
+    the full layer; ``--probe decode`` runs the dense GEMM at M=32 on rotating weight copies."""
+    from flydsl_b200.kernels import compile_blockscale_preshuffle_gemm
+    from flydsl_b200.moe import BlockscaleMoE
+    from flydsl_b200.utils import shuffle_weight
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    if args.probe == "moe":
+        H, I, E, topk, T = 7168, 2048, 32, 8, 512
+        w1, w1_s, w2, w2_s = make_moe_gpu(0, H, I, E, topk, dev, seed=0)
+        layer = BlockscaleMoE(w1, w1_s, w2, w2_s, topk=topk, tile_m=128, mode="reduce")
+        g = torch.Generator(device=dev).manual_seed(T)
+        x_q, x_s = quant_1x128_torch(torch.randn(T, H, generator=g, device=dev))
+        x_st = x_s.t().contiguous()
+        vals, ids = torch.topk(torch.softmax(torch.randn(T, E, generator=g, device=dev), dim=1), k=topk, dim=1)
+        tw = (vals / vals.sum(dim=1, keepdim=True)).float()
+        ids = ids.to(torch.int32)
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        times = []
+        for i in range(args.warmup + args.steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            layer.forward(x_q, x_st, ids, tw, out=out)
+            e1.record()
+            e1.synchronize()
+            if i >= args.warmup:
+                times.append(e0.elapsed_time(e1))
+        print(json.dumps({"probe": "moe", "experts": E, "tokens": T, "ms": statistics.median(times)}))
+    else:
+        M, N, K = 32, 7168, 2048
+        copies = 18
+        sets = []
+        g = torch.Generator(device=dev).manual_seed(0)
+        for _ in range(copies):
+            a = torch.randn(M, K, generator=g, device=dev).to(torch.float8_e4m3fn)
+            b = shuffle_weight((torch.randn(N, K, generator=g, device=dev) * 0.5).to(torch.float8_e4m3fn))
+            sets.append((a, b, torch.rand(K // 128, M, device=dev), torch.rand(N // 128, K // 128, device=dev),
+                         torch.empty(M, N, dtype=torch.bfloat16, device=dev)))
+        fn = compile_blockscale_preshuffle_gemm(M=M, N=N, K=K, tile_m=16, tile_n=64, tile_k=128)
+        for i in range((args.warmup + args.steps)):
+            a, b, sa, sb, c = sets[i % copies]
+            fn(c, a, b, sa, sb, M, N, None)
+        torch.cuda.synchronize()
+        print(json.dumps({"probe": "decode", "M": M, "N": N, "K": K, "launches": args.warmup + args.steps}))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--probe", default=None, choices=["moe", "decode"], help="small profiling run (see run_probe)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
@@ -530,7 +583,9 @@ def main():
     ap.add_argument("--quick", action="store_true", help="shorter extras")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.impl == "reference":
+    if args.probe:
+        run_probe(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
