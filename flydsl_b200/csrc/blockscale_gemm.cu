@@ -66,6 +66,13 @@ struct GemmParams {
   int experts;
   int doweight;
   int accumulate;
+  // MoE, optional "sorted" layouts (cfg.path bits): activations already permuted into routing order
+  // ([a_rows, K] with scales [K/128, a_rows]; row i belongs to sorted position i), fetched by TMA
+  // like the dense A tile instead of being gathered; stage-1 output written in the same order.
+  int a_sorted;
+  int out_sorted;
+  int a_rows;
+  int group;               // tiles a CTA processes back to back (see TileWalker)
 };
 
 template <int BN, int MODE, typename OutT>
@@ -144,7 +151,14 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 template <int BN, int MODE>
 struct TileWalker {
   int num_m, num_n, total;
+  int group;  // consecutive tiles (same weight tile, adjacent row blocks) a CTA takes back to back
+  // A CTA's sequence: tiles [cta*G, cta*G + G), then the same offsets one grid*G further, ...
+  __device__ __forceinline__ int first() const { return static_cast<int>(blockIdx.x) * group; }
+  __device__ __forceinline__ int next(int tile) const {
+    return (tile % group != group - 1) ? tile + 1 : tile + 1 - group + static_cast<int>(gridDim.x) * group;
+  }
   __device__ __forceinline__ TileWalker(const GemmParams& p) {
+    group = p.group > 0 ? p.group : 1;
     if constexpr (MODE == kDense) {
       num_m = (p.M + BM - 1) / BM;
       num_n = (p.N + BN - 1) / BN;
@@ -207,19 +221,18 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     return mbar_wait(done_bar(j % kDone), (j / kDone) & 1, abort_flag, p.err, code);
   };
 
-  constexpr int kFullCount = (MODE == kDense) ? 1 : 3;  // producer (+ two gather warps)
+  // arrivals per stage: the producer's expect_tx (+ the two gather warps when rows are gathered)
+  const bool gather_a = (MODE != kDense) && !p.a_sorted;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) mbar_init(full_bar(s), kFullCount);
+    for (int s = 0; s < kStages; ++s) mbar_init(full_bar(s), gather_a ? 3 : 1);
     for (int i = 0; i < kDone; ++i) mbar_init(done_bar(i), 1);
     for (int b = 0; b < kAccBufs; ++b) mbar_init(tempty_bar(b), kEpiWarps);  // one arrival per warp
     mbar_init(epi_bar, kEpiWarps);
     *abort_flag = 0;
     fence_proxy_async_smem();
     fence_barrier_init();
-    if constexpr (MODE == kDense) {
-      prefetch_tensormap(&tmap_a);
-      if constexpr (C::kStaged) prefetch_tensormap(&tmap_c);
-    }
+    if (MODE == kDense || p.a_sorted) prefetch_tensormap(&tmap_a);
+    if constexpr (MODE == kDense && C::kStaged) prefetch_tensormap(&tmap_c);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
@@ -242,7 +255,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // ---------------- producer: weights (and dense A) via TMA ----------------
       uint32_t it = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < walk.total && alive; tile += gridDim.x) {
+      for (int tile = walk.first(); tile < walk.total && alive; tile = walk.next(tile)) {
         int m_blk, n_tile;
         walk.decode(tile, m_blk, n_tile);
         const uint8_t* wbase = p.b;
@@ -288,12 +301,14 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tma_load_2d(sa, &tmap_a, kb * BK, m_blk * BM, full_bar(s));
             bulk_load(sb, src, rows_b * BK, full_bar(s));
           } else if constexpr (MODE == kMoe1) {
-            mbar_arrive_expect_tx(full_bar(s), 2 * rows_b * BK);
+            mbar_arrive_expect_tx(full_bar(s), 2 * rows_b * BK + (p.a_sorted ? p.a_box_rows * BK : 0));
+            if (p.a_sorted) tma_load_2d(sa, &tmap_a, kb * BK, m_blk * p.tile_m, full_bar(s));
             bulk_load(sb, src, rows_b * BK, full_bar(s));
             bulk_load(sb + (BN / 2) * BK, src + static_cast<size_t>(p.N) * BK, rows_b * BK,
                       full_bar(s));
           } else {
-            mbar_arrive_expect_tx(full_bar(s), rows_b * BK);
+            mbar_arrive_expect_tx(full_bar(s), rows_b * BK + (p.a_sorted ? p.a_box_rows * BK : 0));
+            if (p.a_sorted) tma_load_2d(sa, &tmap_a, kb * BK, m_blk * p.tile_m, full_bar(s));
             bulk_load(sb, src, rows_b * BK, full_bar(s));
           }
         }
@@ -303,7 +318,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       constexpr uint32_t idesc = umma_idesc_e4m3_f32(BM, BN);
       uint32_t it = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < walk.total && alive; tile += gridDim.x) {
+      for (int tile = walk.first(); tile < walk.total && alive; tile = walk.next(tile)) {
         if constexpr (MODE != kDense) {
           int m_blk, n_tile;
           walk.decode(tile, m_blk, n_tile);
@@ -341,7 +356,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           FLYB200_TRACE(2, it);
         }
       }
-    } else if (MODE != kDense && warp >= 2) {
+    } else if (MODE != kDense && warp >= 2 && gather_a) {
       // ---------------- MoE: gather activation rows with cp.async ----------------
       // Thread g owns rows g and g+64 of the tile; row r, 16-byte chunk c lands at
       // r*128 + ((c ^ (r & 7)) << 4): the 128-byte-swizzled K-major image.
@@ -351,7 +366,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t it = 0, published = 0;
       bool alive = true;
       const size_t row_bytes = static_cast<size_t>(p.K);
-      for (int tile = blockIdx.x; tile < walk.total && alive; tile += gridDim.x) {
+      for (int tile = walk.first(); tile < walk.total && alive; tile = walk.next(tile)) {
         int m_blk, n_tile;
         walk.decode(tile, m_blk, n_tile);
         const int e = p.expert_ids[m_blk];
@@ -479,16 +494,24 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (e < 0 || e >= p.experts) return false;
         int t, slot;
         c.row_ok = moe_row(m_blk, t, slot);
+        if (p.a_sorted) {   // scales follow the permuted activations: one per sorted row
+          c.sa_idx = m_blk * p.tile_m + (r < p.tile_m ? r : 0);
+          c.sa_stride = p.a_rows;
+        }
         if constexpr (MODE == kMoe1) {
-          c.sa_idx = t;
-          c.sa_stride = p.M;
+          if (!p.a_sorted) {
+            c.sa_idx = t;
+            c.sa_stride = p.M;
+          }
           const int nb_exp = (2 * p.N) / 128;  // scale rows per expert
           const int cg = min(n_tile * (BN / 2) + half * CH, p.N - 1);
           c.sb_idx0 = (e * nb_exp + cg / 128) * KB;
           c.sb_idx1 = (e * nb_exp + (p.N + cg) / 128) * KB;
         } else {
-          c.sa_idx = t * p.topk + slot;
-          c.sa_stride = p.M * p.topk;
+          if (!p.a_sorted) {
+            c.sa_idx = t * p.topk + slot;
+            c.sa_stride = p.M * p.topk;
+          }
           const int n0 = n_tile * BN;
           const int nb_exp = p.N / 128;
           c.sb_idx0 = (e * nb_exp + min(n0 + half * CH, p.N - 1) / 128) * KB;
@@ -516,7 +539,8 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if constexpr (MODE == kMoe1) {
           c.n0 = n_tile * (BN / 2);
           c.col0 = c.col1 = half * CH;
-          c.out_row = (static_cast<size_t>(t) * p.topk + slot) * p.N;
+          c.out_row = p.out_sorted ? static_cast<size_t>(m_blk * p.tile_m + r) * p.N
+                                   : (static_cast<size_t>(t) * p.topk + slot) * p.N;
         } else {
           c.n0 = n_tile * BN;
           c.col0 = half * CH;
@@ -528,7 +552,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     };
     // first tile >= `tile` (stepping by the grid) that has work; walk.total if none
     auto find_tile = [&](int tile, ScaleCtx& c) -> int {
-      while (tile < walk.total && !setup_scales(tile, c)) tile += gridDim.x;
+      while (tile < walk.total && !setup_scales(tile, c)) tile = walk.next(tile);
       return tile < walk.total ? tile : walk.total;
     };
     auto ld_sa = [&](const ScaleCtx& c, int kb) -> float {
@@ -542,7 +566,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     constexpr int kRing = 2;
     ScaleCtx cur;
     float ring_a[kRing], ring_b0[kRing], ring_b1[kRing];
-    int tile = find_tile(blockIdx.x, cur);
+    int tile = find_tile(walk.first(), cur);
     if (tile < walk.total) {
 #pragma unroll
       for (int j = 0; j < kRing; ++j) {
@@ -637,7 +661,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // next tile's scale context and first scales: issued now, consumed after the store phase
       ScaleCtx nxt;
       float nring_a[kRing], nring_b0[kRing], nring_b1[kRing];
-      const int tile_next = find_tile(tile + gridDim.x, nxt);
+      const int tile_next = find_tile(walk.next(tile), nxt);
       if (tile_next < walk.total) {
 #pragma unroll
         for (int j = 0; j < kRing; ++j) {
@@ -1012,6 +1036,32 @@ static int moe_common_checks(const void* out, const void* x, const void* w, cons
   return FLYB200_OK;
 }
 
+// Tiles a CTA takes back to back (TileWalker::group). Measured on the 256-expert layer: taking the
+// adjacent row blocks of an expert on ONE CTA (so the second finds the weight tile in L2) is slower
+// (4.25 ms) than letting neighbouring CTAs fetch the tile at the same time (3.75 ms), so the
+// grouping stays at 1.
+static int moe_tile_group(int, int, int, int) { return 1; }
+
+// cfg.path of the MoE entry points is a bit set: bit 0 = the activation argument is already in
+// routing order ([T*k + E*tile_m - k, K] rows, scales [K/128, same rows]) and is fetched by TMA;
+// bit 1 (stage 1 only) = write the output in routing order too.
+static int moe_sorted_layout(const flyb200_gemm_cfg* cfg, int T, int E, int k, int tile_m, int kdim,
+                             const void* act, GemmParams* p, CUtensorMap* tmap) {
+  const int bits = cfg ? cfg->path : 0;
+  if (bits < 0 || bits > 3)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "MoE cfg.path must be a combination of bits 0 and 1");
+  p->a_sorted = bits & 1;
+  p->out_sorted = (bits >> 1) & 1;
+  const long long rows = static_cast<long long>(T) * k + static_cast<long long>(E) * tile_m - k;
+  p->a_rows = static_cast<int>(rows);
+  if (!p->a_sorted) return FLYB200_OK;
+  if (tile_m % 8)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT,
+                     "sorted activations need tile_m to be a multiple of 8 (got %d)", tile_m);
+  p->a_box_rows = tile_m;
+  return make_tensor_map_2d(tmap, act, p->a_rows, kdim, 1, tile_m);
+}
+
 extern "C" int flyb200_moe_gemm1(void* out, const void* x, const void* w_repacked,
                                  const float* scale_x, const float* scale_w,
                                  const int32_t* sorted_ids, const int32_t* expert_ids,
@@ -1046,6 +1096,8 @@ extern "C" int flyb200_moe_gemm1(void* out, const void* x, const void* w_repacke
   p.num_valid = num_valid_ids; p.topk = k; p.tile_m = tile_m; p.num_blocks = num_blocks;
   p.experts = E; p.doweight = doweight; p.accumulate = 0;
   CUtensorMap tmap{};
+  if ((rc = moe_sorted_layout(cfg, T, E, k, tile_m, H, x, &p, &tmap))) return rc;
+  p.group = moe_tile_group(T, k, E, tile_m);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (out_dtype == FLYB200_BF16)
     return launch_bn<kMoe1, __nv_bfloat16>(bn, tmap, tmap, p, grid, st);
@@ -1085,6 +1137,10 @@ extern "C" int flyb200_moe_gemm2(void* out, const void* a2, const void* w_repack
   p.num_valid = num_valid_ids; p.topk = k; p.tile_m = tile_m; p.num_blocks = num_blocks;
   p.experts = E; p.doweight = doweight; p.accumulate = accumulate ? 1 : 0;
   CUtensorMap tmap{};
+  if ((rc = moe_sorted_layout(cfg, T, E, k, tile_m, I, a2, &p, &tmap))) return rc;
+  p.group = moe_tile_group(T, k, E, tile_m);
+  if (p.out_sorted)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "stage 2 has no sorted output layout (cfg.path bit 1)");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (out_dtype == FLYB200_BF16)
     return launch_bn<kMoe2, __nv_bfloat16>(bn, tmap, tmap, p, grid, st);

@@ -56,6 +56,76 @@ moe_reduce_kernel(const T* __restrict__ x, T* __restrict__ y, const uint8_t* __r
   }
 }
 
+// 16-bit inputs: half a warp per 128-wide group (16 lanes x 16 bytes), so a warp moves 512 bytes per
+// load instruction; the amax reduction stays inside the half-warp. Returns through q / scale_t.
+template <typename T>
+__device__ __forceinline__ void quant_group16(const T* __restrict__ x, uint8_t* __restrict__ q,
+                                              float* __restrict__ scale_t, int64_t row, int g,
+                                              int cols, int64_t scale_stride, bool active, int sub) {
+  float v[8];
+  if (active) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(x + row * cols + g * 128 + sub * 8);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = to_f32<T>(e[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+  }
+  float vmax = -3.4e38f, vmin = 3.4e38f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (v[j] != v[j]) v[j] = 0.f;
+    else if (isinf(v[j])) v[j] = v[j] > 0 ? 448.f : -448.f;
+    vmax = fmaxf(vmax, v[j]);
+    vmin = fminf(vmin, v[j]);
+  }
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) {  // xor distances < 16 stay inside the half-warp
+    vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+    vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, o));
+  }
+  float scale = __fdiv_rn(fmaxf(vmax, -vmin), 448.f);
+  if (scale == 0.f) scale = 1.f;
+  if (active) {
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      lo |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(__fdiv_rn(v[j], scale), __NV_SATFINITE, __NV_E4M3)) << (8 * j);
+      hi |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(__fdiv_rn(v[j + 4], scale), __NV_SATFINITE, __NV_E4M3)) << (8 * j);
+    }
+    *reinterpret_cast<uint2*>(q + row * cols + g * 128 + sub * 8) = make_uint2(lo, hi);
+    if (sub == 0) scale_t[static_cast<int64_t>(g) * scale_stride + row] = scale;
+  }
+}
+
+// rows x (cols/128) groups, two groups per warp per step (one per half-warp)
+template <typename T>
+__device__ __forceinline__ void quant_rows16(const T* __restrict__ x, uint8_t* __restrict__ q,
+                                             float* __restrict__ scale_t, int64_t rows,
+                                             int64_t scale_stride, int cols) {
+  const int groups = cols / 128;
+  const int64_t total = rows * groups;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane & 15;
+  const int64_t hw0 = ((blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5) * 2 + (lane >> 4);
+  const int64_t nhw = ((static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5) * 2;
+  for (int64_t w = hw0 - (lane >> 4); w < total; w += nhw) {  // warp-uniform trip count
+    const int64_t idx = w + (lane >> 4);
+    const bool active = idx < total;
+    const int64_t row = active ? idx / groups : 0;
+    const int g = active ? static_cast<int>(idx - row * groups) : 0;
+    quant_group16<T>(x, q, scale_t, row, g, cols, scale_stride, active, sub);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+quant_1x128_kernel16(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale_t,
+                     int64_t rows, int cols) {
+  quant_rows16<T>(x, q, scale_t, rows, rows, cols);
+}
+
 // One warp per (row, 128-wide group): lane owns 4 consecutive elements.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -168,12 +238,12 @@ extern "C" int flyb200_quant_1x128(const void* x, void* q, float* scale_t, int64
   uint8_t* qo = static_cast<uint8_t*>(q);
   switch (in_dtype) {
     case FLYB200_BF16:
-      quant_1x128_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), qo,
-                                                           scale_t, rows, cols);
+      quant_1x128_kernel16<__nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), qo,
+                                                             scale_t, rows, cols);
       break;
     case FLYB200_F16:
-      quant_1x128_kernel<__half><<<g, 256, 0, st>>>(static_cast<const __half*>(x), qo, scale_t,
-                                                    rows, cols);
+      quant_1x128_kernel16<__half><<<g, 256, 0, st>>>(static_cast<const __half*>(x), qo, scale_t,
+                                                      rows, cols);
       break;
     case FLYB200_F32:
       quant_1x128_kernel<float><<<g, 256, 0, st>>>(static_cast<const float*>(x), qo, scale_t, rows,
@@ -182,6 +252,95 @@ extern "C" int flyb200_quant_1x128(const void* x, void* q, float* scale_t, int64
     default:
       return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant: bad in_dtype %d", in_dtype);
   }
+  FLYB200_CUDA_CHECK(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Activations into routing order: row i of the output is the activation row of sorted position i
+// (zero for padding rows), with its 1x128 scales in the transposed layout [K/128, rows_out]. Lets
+// the stage kernels fetch their A tiles with TMA instead of gathering rows (cfg.path bit 0).
+namespace flyb200 {
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(const uint4* __restrict__ x, const float* __restrict__ scale_t,
+                       const int* __restrict__ sorted_ids, const int* __restrict__ num_valid,
+                       uint4* __restrict__ x_out, float* __restrict__ scale_out_t, int rows_in,
+                       int K, int topk, int rows_out, int by_slot) {
+  const int chunks = K / 16;               // 16-byte chunks per row
+  const int nscale = K / 128;
+  const int valid = min(num_valid[0], rows_out);
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int i = warp; i < valid; i += nwarps) {
+    const int id = sorted_ids[i];
+    const int t = id & 0xFFFFFF;
+    const int slot = static_cast<unsigned>(id) >> 24;
+    // source row: the token (stage 1) or the (token, slot) route (stage 2 style inputs)
+    const long long src = by_slot ? static_cast<long long>(t) * topk + slot : t;
+    const bool ok = by_slot ? (slot < topk && src < rows_in) : (t < rows_in);
+    for (int c = lane; c < chunks; c += 32)
+      x_out[static_cast<long long>(i) * chunks + c] =
+          ok ? x[src * chunks + c] : make_uint4(0u, 0u, 0u, 0u);
+    for (int s = lane; s < nscale; s += 32)
+      scale_out_t[static_cast<long long>(s) * rows_out + i] =
+          ok ? scale_t[static_cast<long long>(s) * rows_in + src] : 0.f;
+  }
+}
+}  // namespace flyb200
+
+extern "C" int flyb200_moe_gather_rows(const void* x, const float* scale_t, const int32_t* sorted_ids,
+                                       const int32_t* num_valid_ids, void* x_out, float* scale_out_t,
+                                       int32_t rows_in, int32_t K, int32_t topk, int32_t rows_out,
+                                       int32_t by_slot, void* stream) {
+  if (!x || !scale_t || !sorted_ids || !num_valid_ids || !x_out || !scale_out_t)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "moe_gather_rows: NULL buffer");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(x_out)) % 16)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "moe_gather_rows: x and x_out must be 16-byte aligned");
+  if (rows_in < 1 || rows_out < 1 || K < 128 || K % 128 || topk < 1)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "moe_gather_rows: bad sizes");
+  const int sms = sm_count();
+  if (sms <= 0) return FLYB200_ERR_CUDA;
+  moe_gather_rows_kernel<<<sms * 4, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), scale_t, sorted_ids, num_valid_ids, static_cast<uint4*>(x_out),
+      scale_out_t, rows_in, K, topk, rows_out, by_slot ? 1 : 0);
+  FLYB200_CUDA_CHECK(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+// 1x128 quantiser over the first num_rows_dev[0] rows only (row count known on the device, e.g. the
+// padded route count of the sorter); scales go to [cols/128, rows_alloc].
+namespace flyb200 {
+template <typename T>
+__global__ void __launch_bounds__(256)
+quant_1x128_devrows_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale_t,
+                           const int* __restrict__ num_rows_dev, int64_t rows_alloc, int cols) {
+  const int64_t rows = min(static_cast<int64_t>(num_rows_dev[0]), rows_alloc);
+  quant_rows16<T>(x, q, scale_t, rows, rows_alloc, cols);
+}
+}  // namespace flyb200
+
+extern "C" int flyb200_quant_1x128_devrows(const void* x, void* q, float* scale_t,
+                                           const int32_t* num_rows_dev, int64_t rows_alloc,
+                                           int32_t cols, int32_t in_dtype, void* stream) {
+  if (!x || !q || !scale_t || !num_rows_dev)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant_devrows: NULL buffer");
+  if ((reinterpret_cast<uintptr_t>(x) % 16) || (reinterpret_cast<uintptr_t>(q) % 4))
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant_devrows: x must be 16-byte, q 4-byte aligned");
+  if (rows_alloc < 1 || cols < 128 || cols % 128)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant_devrows: bad sizes");
+  if (in_dtype != FLYB200_BF16 && in_dtype != FLYB200_F16)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant_devrows: input must be BF16 or F16");
+  const int sms = sm_count();
+  if (sms <= 0) return FLYB200_ERR_CUDA;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  uint8_t* qo = static_cast<uint8_t*>(q);
+  if (in_dtype == FLYB200_BF16)
+    quant_1x128_devrows_kernel<__nv_bfloat16><<<sms * 16, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(x), qo, scale_t, num_rows_dev, rows_alloc, cols);
+  else
+    quant_1x128_devrows_kernel<__half><<<sms * 16, 256, 0, st>>>(static_cast<const __half*>(x), qo,
+                                                                 scale_t, num_rows_dev, rows_alloc, cols);
   FLYB200_CUDA_CHECK(cudaGetLastError());
   return FLYB200_OK;
 }

@@ -24,8 +24,8 @@ _OUT_CODES = {
 }
 
 
-def _cfg(block_n):
-    cfg = _lib.GemmCfg(int(block_n or 0), 0, 0, 0)
+def _cfg(block_n, path_bits=0):
+    cfg = _lib.GemmCfg(int(block_n or 0), 0, int(path_bits), 0)
     return cfg, ctypes.byref(cfg)
 
 
@@ -38,11 +38,12 @@ class MoeGemm1Launcher:
     ``[model_dim/128, tokens]``; scale_w f32 ``[E*(2*inter/128), model_dim/128]``.
     """
 
-    def __init__(self, model_dim, inter_dim, experts, topk, tile_m, doweight, out_code, block_n):
+    def __init__(self, model_dim, inter_dim, experts, topk, tile_m, doweight, out_code, block_n,
+                 a_sorted=False, out_sorted=False):
         self.model_dim, self.inter_dim = int(model_dim), int(inter_dim)
         self.experts, self.topk, self.tile_m = int(experts), int(topk), int(tile_m)
         self.doweight, self.out_code = int(bool(doweight)), out_code
-        self._cfg, self._cfg_ref = _cfg(block_n)
+        self._cfg, self._cfg_ref = _cfg(block_n, (1 if a_sorted else 0) | (2 if out_sorted else 0))
         self._fn = _lib.load().flyb200_moe_gemm1
 
     def __call__(self, out, x, w, scale_x, scale_w, sorted_token_ids, expert_ids, sorted_weights,
@@ -69,11 +70,11 @@ class MoeGemm2Launcher:
     """
 
     def __init__(self, model_dim, inter_dim, experts, topk, tile_m, doweight, accumulate, out_code,
-                 block_n):
+                 block_n, a_sorted=False):
         self.model_dim, self.inter_dim = int(model_dim), int(inter_dim)
         self.experts, self.topk, self.tile_m = int(experts), int(topk), int(tile_m)
         self.doweight, self.accumulate, self.out_code = int(bool(doweight)), int(bool(accumulate)), out_code
-        self._cfg, self._cfg_ref = _cfg(block_n)
+        self._cfg, self._cfg_ref = _cfg(block_n, 1 if a_sorted else 0)
         self._fn = _lib.load().flyb200_moe_gemm2
 
     def __call__(self, out, x, w, scale_x, scale_w, sorted_token_ids, expert_ids, sorted_weights,
@@ -135,11 +136,17 @@ def compile_moe_blockscale_gemm1(
     use_cshuffle_epilog=None,
     waves_per_eu=None,
     block_n=None,
+    a_sorted=False,
+    out_sorted=False,
 ):
     """Stage 1: ``out[t, slot, :] = silu(x[t] @ Wgate[e]^T) * (x[t] @ Wup[e]^T)`` (optionally times
     the route weight). ``tile_m`` must equal the block size the routing buffers were sorted with;
     ``tile_n/tile_k`` are validated only; ``block_n`` (64/128/256 = gate+up MMA width) overrides
-    the heuristic. ``use_cshuffle_epilog`` / ``waves_per_eu`` are AMD switches, ignored."""
+    the heuristic. ``use_cshuffle_epilog`` / ``waves_per_eu`` are AMD switches, ignored.
+
+    Extensions (off by default, so the reference call is unchanged): ``a_sorted`` -- ``x`` and
+    ``scale_x`` are already in routing order (``utils.moe_gather_rows``), fetched by TMA instead of
+    gathered; ``out_sorted`` -- write ``out`` in routing order ``[T*k + E*tile_m - k, inter]``."""
     if out_dtype not in ("f16", "bf16"):
         raise ValueError(f"out_dtype must be 'f16' or 'bf16', got {out_dtype!r}")
     _check_tiles(tile_m, tile_k, scale_block_k)
@@ -149,8 +156,10 @@ def compile_moe_blockscale_gemm1(
         raise ValueError(f"inter_dim ({inter_dim}) must be divisible by 128 (ScaleBlockN)")
     if block_n not in (None, 0, 64, 128, 256):
         raise ValueError(f"block_n must be one of 64, 128, 256, got {block_n}")
+    if (a_sorted or out_sorted) and int(tile_m) % 8:
+        raise ValueError(f"sorted layouts need tile_m to be a multiple of 8, got {tile_m}")
     return MoeGemm1Launcher(model_dim, inter_dim, experts, topk, tile_m, doweight_stage1,
-                            _OUT_CODES[out_dtype], block_n)
+                            _OUT_CODES[out_dtype], block_n, a_sorted, out_sorted)
 
 
 @functools.lru_cache(maxsize=1024)
@@ -170,9 +179,11 @@ def compile_moe_blockscale_gemm2(
     accumulate: bool = True,
     waves_per_eu=None,
     block_n=None,
+    a_sorted=False,
 ):
     """Stage 2: ``A2[t*topk+slot] @ W2[e]^T`` (times the route weight when ``doweight_stage2``),
-    atomically added into ``out[t]`` (``accumulate=True``) or stored per route."""
+    atomically added into ``out[t]`` (``accumulate=True``) or stored per route. ``a_sorted``: ``x`` /
+    ``scale_x`` are in routing order (rows = sorted positions), fetched by TMA."""
     out_s = str(out_dtype).strip().lower()
     if out_s not in _OUT_CODES:
         raise ValueError(f"out_dtype must be 'f16', 'bf16', or 'f32', got {out_dtype!r}")
@@ -186,8 +197,10 @@ def compile_moe_blockscale_gemm2(
         raise ValueError(f"model_dim ({model_dim}) must be divisible by 128 (ScaleBlockN)")
     if block_n not in (None, 0, 32, 64, 128, 256):
         raise ValueError(f"block_n must be one of 32, 64, 128, 256, got {block_n}")
+    if a_sorted and int(tile_m) % 8:
+        raise ValueError(f"sorted layouts need tile_m to be a multiple of 8, got {tile_m}")
     return MoeGemm2Launcher(model_dim, inter_dim, experts, topk, tile_m, doweight_stage2,
-                            accumulate, out_code, block_n)
+                            accumulate, out_code, block_n, a_sorted)
 
 
 @functools.lru_cache(maxsize=1024)

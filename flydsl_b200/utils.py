@@ -168,3 +168,25 @@ def build_routing_buffers(*, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
         topk_ids, topk_weights, num_experts=int(experts), block_size=int(tile_m))
     num_valid_ids = post_pad[:1].contiguous()
     return ids, weights, expert_ids, num_valid_ids, int(ids.numel()), int(expert_ids.numel())
+
+
+def moe_gather_rows(x, scale_t, sorted_ids, num_valid_ids, *, topk: int, by_slot: bool = False,
+                    out=None, scale_out=None, stream=None):
+    """Activations into routing order for the TMA-fed stage kernels (``a_sorted=True``).
+
+    ``x`` fp8 ``[rows_in, K]`` and ``scale_t`` f32 ``[K/128, rows_in]``; row i of the result is the
+    row of sorted position i (token ``t``, or route ``t*topk+slot`` with ``by_slot``), zero for
+    padding. Returns ``(x_sorted [len(sorted_ids), K], scale_sorted_t [K/128, len(sorted_ids)])``."""
+    _require_cuda(x, "x")
+    rows_in, K = x.shape
+    rows_out = sorted_ids.numel()
+    if out is None:
+        out = torch.empty((rows_out, K), dtype=x.dtype, device=x.device)
+    if scale_out is None:
+        scale_out = torch.empty((K // 128, rows_out), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().flyb200_moe_gather_rows(
+            x.data_ptr(), scale_t.data_ptr(), sorted_ids.data_ptr(), num_valid_ids.data_ptr(),
+            out.data_ptr(), scale_out.data_ptr(), rows_in, K, int(topk), rows_out, int(bool(by_slot)),
+            _lib.stream_handle(stream)))
+    return out, scale_out

@@ -51,7 +51,9 @@ typedef enum flyb200_dtype {
 typedef struct flyb200_gemm_cfg {
   int32_t block_n;  /* MMA N / CTA tile width: 32, 64, 128 or 256; 0 = auto */
   int32_t max_ctas; /* cap on the persistent grid; 0 = one CTA per SM       */
-  int32_t path;     /* dense GEMM only: 0 = auto, 1 = tiled kernel, 2 = decode kernel (M <= 64) */
+  int32_t path;     /* dense GEMM: 0 = auto, 1 = tiled kernel, 2 = decode kernel (M <= 64).
+                     * MoE stages: bit 0 = activations already in routing order (TMA-fed),
+                     *             bit 1 = stage-1 output in routing order                   */
   int32_t split_k;  /* decode kernel: K splits per weight tile (cluster size, 1..8); 0 = auto    */
 } flyb200_gemm_cfg;
 
@@ -157,6 +159,22 @@ size_t flyb200_moe_gemm2_reduce_noalloc_max_bytes(void);
  * the MoE stages (tests/kernels/test_moe_blockscale.py:346-361, pertoken_quant tests/utils.py:29-73). */
 int flyb200_quant_1x128(const void* x, void* q, float* scale_t, int64_t rows, int32_t cols,
                         int32_t in_dtype, void* stream);
+
+/* Activations into routing order (a helper with no reference counterpart: the reference gathers rows
+ * inside its stage kernels, kernels/moe_blockscale_2stage.py:394-439). Row i < num_valid_ids[0] of
+ * x_out is the source row of sorted position i -- token t (by_slot = 0) or route t*topk+slot
+ * (by_slot != 0) -- zero for padding; scale_out_t [K/128, rows_out] likewise. x [rows_in, K] fp8,
+ * scale_t [K/128, rows_in]. With inputs prepared this way flyb200_moe_gemm1/2 take cfg.path bit 0
+ * (A fetched by TMA) and stage 1 may write in routing order with cfg.path bit 1. */
+int flyb200_moe_gather_rows(const void* x, const float* scale_t, const int32_t* sorted_ids,
+                            const int32_t* num_valid_ids, void* x_out, float* scale_out_t,
+                            int32_t rows_in, int32_t K, int32_t topk, int32_t rows_out,
+                            int32_t by_slot, void* stream);
+
+/* flyb200_quant_1x128 over the first num_rows_dev[0] rows only (row count known on the device, e.g.
+ * the sorter's padded route count); scale_t is [cols/128, rows_alloc]. Input BF16|F16. */
+int flyb200_quant_1x128_devrows(const void* x, void* q, float* scale_t, const int32_t* num_rows_dev,
+                                int64_t rows_alloc, int32_t cols, int32_t in_dtype, void* stream);
 
 /* Reads and clears the device error word of the current device after synchronising `stream`.
  * *code_out = 0 when no kernel reported a problem. The reference only prints GPU errors

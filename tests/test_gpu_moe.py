@@ -191,6 +191,40 @@ def test_layer_vs_oracle(T, H, I, E, k, mode):
         assert torch.equal(out, out2)
 
 
+def test_sorted_layout_matches_gathered_layout():
+    """Routing-order intermediates (activations permuted once, TMA-fed stages) against the
+    reference-shaped gather path: same arithmetic, so the results must agree bit for bit in the
+    deterministic reduce mode; the helper kernels are checked against torch indexing."""
+    from flydsl_b200.moe import BlockscaleMoE
+    from flydsl_b200.utils import moe_gather_rows, moe_sorting
+
+    m = O.make_moe_case(T=96, H=1024, I=512, E=16, topk=4, seed=11, hot_experts=2, hot_bias=3.0)
+    args = (m["x_q"].to(DEV), m["x_scale"].to(DEV).t().contiguous(), m["topk_ids"].to(DEV), m["topk_weights"].to(DEV))
+    outs = {}
+    for flag in (False, True):
+        layer = BlockscaleMoE.from_unpacked(m["w1_q"].to(DEV), m["w1_scale"].to(DEV), m["w2_q"].to(DEV),
+                                            m["w2_scale"].to(DEV), topk=4, tile_m=32, sorted_layout=flag)
+        outs[flag] = layer.forward(*args)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[True], outs[False])
+    ref, _, _, _ = O.torch_moe_two_stage_ref(m["x_q"], m["x_scale"], m["w1_q"], m["w1_scale"], m["w2_q"],
+                                             m["w2_scale"], m["topk_ids"], m["topk_weights"], 512)
+    assert_close_to_oracle(outs[True], ref, "sorted layout")
+    # gather helper: rows and scales land at their sorted positions, padding is zero
+    sid, sw, seid, npp = moe_sorting(args[2], args[3], num_experts=16, block_size=32)
+    xs, ss = moe_gather_rows(args[0], args[1], sid, npp, topk=4)
+    n = int(npp[0])
+    ids = sid[:n].cpu().long()
+    tok = ids & 0xFFFFFF
+    valid = tok < 96
+    want = torch.zeros(n, 1024, dtype=torch.uint8)
+    want[valid] = m["x_q"].view(torch.uint8)[tok[valid]]
+    assert torch.equal(xs[:n].cpu().view(torch.uint8), want)
+    want_s = torch.zeros(n, 8)
+    want_s[valid] = m["x_scale"][tok[valid]]
+    assert torch.equal(ss[:, :n].cpu().t().contiguous(), want_s)
+
+
 def test_skewed_routing_and_empty_experts():
     """Decode-style stress: hot experts, many experts with zero tokens, tile_m larger than any count."""
     from flydsl_b200.moe import BlockscaleMoE
