@@ -58,6 +58,7 @@ SIGNATURES = {
     "flyb200_moe_gather_rows": (c_int, [c_void_p] * 6 + [c_int32] * 5 + [c_void_p]),
     "flyb200_quant_1x128_devrows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32,
                                             c_void_p]),
+    "flyb200_ep_plan_pack": (c_int, [c_void_p] * 4 + [c_int32] * 5 + [c_void_p] * 5),
     "flyb200_query_device_error": (c_int, [c_void_p, POINTER(c_int32)]),
     "flyb200_last_error_string": (c_char_p, []),
     "flyb200_version": (c_int, []),

@@ -102,6 +102,89 @@ def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int):
     return need, order, counts, pos
 
 
+def plan_dispatch_fixed(topk_ids: torch.Tensor, experts_per_rank: int, world: int):
+    """Sync-free variant of plan_dispatch: every (source, destination) pair owns a fixed block of
+    ``T`` row slots, so no count has to travel or reach the host.
+
+    Returns
+      need   bool [T, W]
+      slot   i64  [T, W]   row slot of token t inside destination r's block (valid where need)
+      src    i64  [W*T]    token index feeding send row r*T + s, or -1 for an unused slot
+    """
+    T = topk_ids.shape[0]
+    dest = torch.div(topk_ids.long(), experts_per_rank, rounding_mode="floor")
+    ranks = torch.arange(world, device=topk_ids.device).view(1, 1, world)
+    need = (dest.unsqueeze(-1) == ranks).any(dim=1)                                 # [T, W]
+    slot = torch.cumsum(need.long(), dim=0) - 1                                     # [T, W]
+    # scatter without boolean indexing (that would need the count on the host): entries that are
+    # not needed go to one spare slot at the end, which is cut off
+    src = torch.full((world * T + 1,), -1, dtype=torch.long, device=topk_ids.device)
+    flat = (torch.arange(world, device=topk_ids.device).view(1, world) * T + slot)  # [T, W]
+    flat = torch.where(need, flat, torch.full_like(flat, world * T))
+    tok = torch.arange(T, device=topk_ids.device).view(T, 1).expand(T, world)
+    tok = torch.where(need, tok, torch.full_like(tok, -1))
+    src.scatter_(0, flat.reshape(-1), tok.reshape(-1))
+    return need, slot, src[: world * T]
+
+
+def pack_rows_fixed(x_q_u8, x_scale, topk_ids, topk_weights, src):
+    """Send buffer [W*T, row bytes]; unused slots carry expert id -1 in every top-k position so the
+    receiver's sorter drops them."""
+    valid = src >= 0
+    idx = src.clamp(min=0)
+    ids = torch.where(valid.view(-1, 1), topk_ids[idx].to(torch.int32),
+                      torch.full_like(topk_ids[idx], -1, dtype=torch.int32))
+    n = idx.numel()
+    parts = [x_q_u8[idx],
+             x_scale[idx].contiguous().view(torch.uint8).view(n, -1),
+             ids.contiguous().view(torch.uint8).view(n, -1),
+             topk_weights[idx].to(torch.float32).contiguous().view(torch.uint8).view(n, -1)]
+    return torch.cat(parts, dim=1).contiguous()
+
+
+def plan_pack_cuda(x_u8, x_scale, topk_ids, topk_weights, experts_per_rank, world):
+    """plan_dispatch_fixed + pack_rows_fixed as two CUDA launches (flyb200_ep_plan_pack)."""
+    from . import _lib
+
+    T, H = x_u8.shape
+    k = topk_ids.shape[1]
+    dev = x_u8.device
+    ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
+    w = topk_weights if topk_weights.dtype == torch.float32 else topk_weights.float()
+    need = torch.empty((T, world), dtype=torch.uint8, device=dev)
+    slot = torch.empty((T, world), dtype=torch.int32, device=dev)
+    src = torch.empty((world * T,), dtype=torch.int32, device=dev)
+    rows = torch.empty((world * T, H + 4 * (H // 128) + 8 * k), dtype=torch.uint8, device=dev)
+    _lib.check(_lib.load().flyb200_ep_plan_pack(
+        x_u8.data_ptr(), x_scale.contiguous().data_ptr(), ids.contiguous().data_ptr(),
+        w.contiguous().data_ptr(), T, H, k, world, experts_per_rank, need.data_ptr(), slot.data_ptr(),
+        src.data_ptr(), rows.data_ptr(), _lib.stream_handle(None)))
+    return need.bool(), slot.long(), rows
+
+
+def combine_partials_fixed(back, need, slot, out_dtype):
+    """out[t] = sum over ranks r (ascending) of back[r*T + slot[t, r]] where needed; fp32."""
+    T, W = need.shape
+    if back.is_cuda and back.dtype in (torch.bfloat16, torch.float16) and back.shape[1] % 8 == 0:
+        # one gather into [T, W, H], then the masked fixed-order reduce kernel
+        from . import _lib
+
+        base = torch.arange(W, device=back.device).view(1, W) * T
+        gathered = back[(base + slot.clamp(min=0)).reshape(-1)]                  # [T*W, H]
+        out = torch.empty((T, back.shape[1]), dtype=back.dtype, device=back.device)
+        mask = need.to(torch.uint8).contiguous()
+        _lib.check(_lib.load().flyb200_moe_reduce(
+            gathered.data_ptr(), out.data_ptr(), mask.data_ptr(), T, W, back.shape[1],
+            _lib.BF16 if back.dtype == torch.bfloat16 else _lib.F16, _lib.stream_handle(None)))
+        return out.to(out_dtype)
+    acc = torch.zeros((T, back.shape[1]), dtype=torch.float32, device=back.device)
+    base = torch.arange(W, device=back.device).view(1, W) * T
+    idx = (base + slot.clamp(min=0))
+    for r in range(W):  # fixed order => deterministic
+        acc += back[idx[:, r]].float() * need[:, r].view(T, 1).float()
+    return acc.to(out_dtype)
+
+
 def pack_rows(x_q_u8, x_scale, topk_ids, topk_weights, order):
     """One byte row per sent token: [H fp8 | H/128 f32 scales | k i32 ids | k f32 weights]."""
     parts = [x_q_u8[order],
@@ -159,17 +242,24 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, local_fn: Callable, *, experts: int, topk: int, model_dim: int, rank: int,
-                 world: int, group=None, out_dtype=torch.bfloat16):
+                 world: int, group=None, out_dtype=torch.bfloat16, exchange: str = "fixed"):
         if experts % world:
             raise ValueError(f"{experts} experts cannot be split over {world} ranks")
         self.local_fn, self.E, self.k, self.H = local_fn, experts, topk, model_dim
         self.rank, self.world, self.group, self.out_dtype = rank, world, group, out_dtype
         self.experts_per_rank = experts // world
         self.last_stats = {}
+        if exchange not in ("fixed", "exact"):
+            raise ValueError("exchange must be 'fixed' (T row slots per rank pair, no host sync) or "
+                             "'exact' (only the needed rows travel; one host sync for the counts)")
+        self.exchange = exchange
+        self.trace = False
 
     def forward(self, x_q, x_scale, topk_ids, topk_weights):
         """x_q fp8/uint8 [T, H]; x_scale f32 [T, H/128] (token-major); ids [T, k]; weights [T, k]."""
         x_u8 = x_q.view(torch.uint8)
+        if self.exchange == "fixed":
+            return self._forward_fixed(x_u8, x_scale, topk_ids, topk_weights)
         need, order, counts, pos = plan_dispatch(topk_ids, self.experts_per_rank, self.world)
         recv_counts = exchange_counts(counts, self.group)
         send_l, recv_l = counts.tolist(), recv_counts.tolist()       # one host sync per step
@@ -184,15 +274,63 @@ class ExpertParallelMoE:
         return combine_partials(back, need, pos, self.out_dtype)
 
 
+def _forward_fixed(self, x_u8, x_scale, topk_ids, topk_weights):
+    """Equal-split all-to-alls: nothing depends on a host-visible count, so the whole step is
+    enqueued without synchronising (the price: T row slots per destination instead of the ~T*(1 -
+    ((W-1)/W)^k) that are needed)."""
+    T = x_u8.shape[0]
+    marks = []
+
+    def mark(name):  # optional phase timing (self.trace = True): CUDA events, read after the step
+        if self.trace and x_u8.is_cuda:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            marks.append((name, e))
+
+    mark("start")
+    if x_u8.is_cuda and self.k % 2 == 0:
+        need, slot, rows = plan_pack_cuda(x_u8, x_scale, topk_ids, topk_weights, self.experts_per_rank,
+                                          self.world)
+    else:
+        need, slot, src = plan_dispatch_fixed(topk_ids, self.experts_per_rank, self.world)
+        rows = pack_rows_fixed(x_u8, x_scale, topk_ids, topk_weights, src)      # [W*T, bytes]
+    mark("plan+pack")
+    got = torch.empty_like(rows)
+    dist.all_to_all_single(got, rows, group=self.group)
+    mark("dispatch")
+    rx_q, rx_s, rids, rw = unpack_rows(got, self.H, self.k)
+    mark("unpack")
+    partial = self.local_fn(rx_q, rx_s, rids, rw).contiguous()                  # [W*T, H]
+    mark("local experts")
+    back = torch.empty_like(partial)
+    dist.all_to_all_single(back, partial, group=self.group)
+    mark("combine a2a")
+    self.last_stats = {"sent_rows": self.world * T, "recv_rows": self.world * T,
+                       "dispatch_bytes": rows.numel(), "combine_bytes": partial.numel() * partial.element_size()}
+    out = combine_partials_fixed(back, need, slot, self.out_dtype)
+    mark("sum partials")
+    if marks:
+        torch.cuda.synchronize()
+        self.last_stats["phase_ms"] = {marks[i + 1][0]: round(marks[i][1].elapsed_time(marks[i + 1][1]), 4)
+                                       for i in range(len(marks) - 1)}
+    return out
+
+
+ExpertParallelMoE._forward_fixed = _forward_fixed
+
+
 class LocalExpertShard:
-    """The experts of one rank on its GPU: routing sort restricted by ``expert_mask``, the two GEMM
-    stages, and the masked top-k reduce that yields one partial row per received token."""
+    """The experts of one rank on its GPU: routing sort restricted by ``expert_mask``, activations
+    permuted into routing order, the two TMA-fed GEMM stages, and the masked top-k reduce that yields
+    one partial row per received token. Rows whose expert ids are all foreign (or -1) give zeros."""
 
     def __init__(self, w1, w1_scale, w2, w2_scale, *, experts: int, topk: int, rank: int, world: int,
                  tile_m: int = 128, mid_dtype=torch.float16, out_dtype=torch.bfloat16):
         from .kernels import (compile_moe_blockscale_gemm1, compile_moe_blockscale_gemm2,
                               compile_moe_reduction)
 
+        if tile_m % 8:
+            raise ValueError("LocalExpertShard uses the routing-order layout: tile_m must be a multiple of 8")
         self.E, self.k, self.rank, self.world = experts, topk, rank, world
         self.EL = experts // world
         self.w1, self.w2 = w1, w2                       # repacked local experts [EL, 2I, H], [EL, H, I]
@@ -200,38 +338,61 @@ class LocalExpertShard:
         self.H, self.I = w1.shape[2], w1.shape[1] // 2
         self.tile_m, self.mid_dtype, self.out_dtype = tile_m, mid_dtype, out_dtype
         names = {torch.float16: "f16", torch.bfloat16: "bf16"}
-        common = dict(model_dim=self.H, inter_dim=self.I, experts=self.EL, topk=topk, tile_m=tile_m,
+        # the stage kernels see the GLOBAL expert count for the length of the routing buffers
+        # (sorted length = R*k + E*tile_m - k) but only local, compacted expert ids occur in them
+        common = dict(model_dim=self.H, inter_dim=self.I, experts=experts, topk=topk, tile_m=tile_m,
                       tile_n=256, tile_k=128)
-        self.gemm1 = compile_moe_blockscale_gemm1(doweight_stage1=False, out_dtype=names[mid_dtype], **common)
+        self.gemm1 = compile_moe_blockscale_gemm1(doweight_stage1=False, out_dtype=names[mid_dtype],
+                                                  a_sorted=True, out_sorted=True, **common)
         self.gemm2 = compile_moe_blockscale_gemm2(doweight_stage2=True, out_dtype=names[out_dtype],
-                                                  accumulate=False, **common)
+                                                  accumulate=False, a_sorted=True, **common)
         self.reduce = compile_moe_reduction(topk=topk, model_dim=self.H, dtype_str=names[out_dtype],
                                             use_mask=True)
+        self._mid_code = {torch.float16: 1, torch.bfloat16: 0}[mid_dtype]
         mask = torch.zeros(experts, dtype=torch.int32, device=w1.device)
         mask[rank * self.EL:(rank + 1) * self.EL] = 1
         self.expert_mask = mask
+        self._buf = {}
+
+    def _buffers(self, R, dev):
+        b = self._buf.get(R)
+        if b is None:
+            L = R * self.k + self.E * self.tile_m - self.k
+            b = {"L": L,
+                 "x_sorted": torch.empty((L, self.H), dtype=torch.float8_e4m3fn, device=dev),
+                 "xs_sorted": torch.empty((self.H // 128, L), dtype=torch.float32, device=dev),
+                 "out1": torch.zeros((L, self.I), dtype=self.mid_dtype, device=dev),
+                 "a2_q": torch.empty((L, self.I), dtype=torch.float8_e4m3fn, device=dev),
+                 "a2_s": torch.empty((self.I // 128, L), dtype=torch.float32, device=dev),
+                 "routes": torch.empty((R * self.k, self.H), dtype=self.out_dtype, device=dev),
+                 "out": torch.empty((R, self.H), dtype=self.out_dtype, device=dev)}
+            self._buf[R] = b
+        return b
 
     def __call__(self, x_q_u8, x_scale, topk_ids, topk_weights):
-        from .utils import moe_sorting, quant_1x128
+        from . import _lib
+        from .utils import moe_gather_rows, moe_sorting
 
         R = x_q_u8.shape[0]
         dev = x_q_u8.device
-        out = torch.zeros((R, self.H), dtype=self.out_dtype, device=dev)
         if R == 0:
-            return out
+            return torch.zeros((0, self.H), dtype=self.out_dtype, device=dev)
+        b = self._buffers(R, dev)
         sid, sw, seid, npp = moe_sorting(topk_ids, topk_weights, num_experts=self.E,
                                          block_size=self.tile_m, expert_mask=self.expert_mask)
         nblk = seid.numel()
-        out1 = torch.empty((R, self.k, self.I), dtype=self.mid_dtype, device=dev)
-        # rows of non-local routes are never written by stage 1; keep them finite for the quantiser
-        out1.zero_()
         xs_t = x_scale.t().contiguous()
-        self.gemm1(out1, x_q_u8, self.w1, xs_t, self.w1_scale, sid, seid, sw, npp, R, self.I, self.H,
-                   nblk, None)
-        a2_q, a2_s = quant_1x128(out1.view(R * self.k, self.I))
-        routes = torch.empty((R * self.k, self.H), dtype=self.out_dtype, device=dev)
-        self.gemm2(routes, a2_q, self.w2, a2_s, self.w2_scale, sid, seid, sw, npp, R, self.H, self.I,
-                   nblk, None)
-        valid = self.expert_mask[topk_ids.long()].to(torch.uint8).contiguous()
-        self.reduce(routes, out, valid, R, None)
-        return out
+        moe_gather_rows(x_q_u8.view(torch.float8_e4m3fn), xs_t, sid, npp, topk=self.k,
+                        out=b["x_sorted"], scale_out=b["xs_sorted"])
+        self.gemm1(b["out1"], b["x_sorted"], self.w1, b["xs_sorted"], self.w1_scale, sid, seid, sw, npp,
+                   R, self.I, self.H, nblk, None)
+        _lib.check(_lib.load().flyb200_quant_1x128_devrows(
+            b["out1"].data_ptr(), b["a2_q"].data_ptr(), b["a2_s"].data_ptr(), npp.data_ptr(), b["L"],
+            self.I, self._mid_code, _lib.stream_handle(None)))
+        self.gemm2(b["routes"], b["a2_q"], self.w2, b["a2_s"], self.w2_scale, sid, seid, sw, npp, R,
+                   self.H, self.I, nblk, None)
+        ids = topk_ids.long()
+        valid = ((ids >= 0) & (ids < self.E))
+        valid = (valid & (self.expert_mask[ids.clamp(0, self.E - 1)] != 0)).to(torch.uint8).contiguous()
+        self.reduce(b["routes"], b["out"], valid, R, None)
+        return b["out"]

@@ -176,6 +176,17 @@ int flyb200_moe_gather_rows(const void* x, const float* scale_t, const int32_t* 
 int flyb200_quant_1x128_devrows(const void* x, void* q, float* scale_t, const int32_t* num_rows_dev,
                                 int64_t rows_alloc, int32_t cols, int32_t in_dtype, void* stream);
 
+/* Expert-parallel dispatch preparation (new multi-GPU layer, no reference counterpart). For local
+ * tokens x [T,H] fp8 with token-major scales x_scale [T,H/128], topk_ids i32 [T,k], topk_weights f32
+ * [T,k] and W ranks owning experts_per_rank consecutive experts each: need_out u8 [T,W] (token t
+ * visits rank r), slot_out i32 [T,W] (its row slot inside rank r's block), src_out i32 [W*T] (token
+ * feeding each send row, -1 = unused) and the packed send buffer send_out [W*T, H + 4*H/128 + 8*k]
+ * bytes = [fp8 row | scales | expert ids | route weights], unused rows with ids -1. k must be even. */
+int flyb200_ep_plan_pack(const void* x, const float* x_scale, const int32_t* topk_ids,
+                         const float* topk_weights, int32_t T, int32_t H, int32_t k, int32_t W,
+                         int32_t experts_per_rank, uint8_t* need_out, int32_t* slot_out,
+                         int32_t* src_out, void* send_out, void* stream);
+
 /* Reads and clears the device error word of the current device after synchronising `stream`.
  * *code_out = 0 when no kernel reported a problem. The reference only prints GPU errors
  * (lib/Runtime/FlyRocmRuntimeWrappers.cpp:22-30); this is the status-returning equivalent. */

@@ -225,6 +225,27 @@ def test_sorted_layout_matches_gathered_layout():
     assert torch.equal(ss[:, :n].cpu().t().contiguous(), want_s)
 
 
+def test_ep_plan_pack_kernel_matches_torch_logic():
+    """The fused expert-parallel dispatch preparation against the device-agnostic torch functions."""
+    from flydsl_b200 import parallel as P
+
+    g = torch.Generator().manual_seed(5)
+    T, H, k, E, W = 300, 512, 8, 64, 8
+    x = torch.randint(0, 255, (T, H), generator=g, dtype=torch.uint8)
+    xs = torch.rand(T, H // 128, generator=g)
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32)
+    w = torch.rand(T, k, generator=g)
+    need_c, slot_c, rows_c = P.plan_pack_cuda(x.to(DEV), xs.to(DEV), ids.to(DEV), w.to(DEV), E // W, W)
+    need_t, slot_t, src_t = P.plan_dispatch_fixed(ids, E // W, W)
+    rows_t = P.pack_rows_fixed(x, xs, ids, w, src_t)
+    assert torch.equal(need_c.cpu(), need_t)
+    assert torch.equal(slot_c.cpu()[need_t], slot_t[need_t])
+    used = src_t >= 0
+    assert torch.equal(rows_c.cpu()[used], rows_t[used])
+    id_lo = H + 4 * (H // 128)
+    assert torch.equal(rows_c.cpu()[~used][:, id_lo:id_lo + 4 * k], rows_t[~used][:, id_lo:id_lo + 4 * k])  # ids = -1
+
+
 def test_skewed_routing_and_empty_experts():
     """Decode-style stress: hot experts, many experts with zero tokens, tile_m larger than any count."""
     from flydsl_b200.moe import BlockscaleMoE

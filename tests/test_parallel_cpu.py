@@ -52,7 +52,7 @@ def _free_port():
     return port
 
 
-def _ep_worker(rank, world, port, case, T_local, ret):
+def _ep_worker(rank, world, port, case, T_local, exchange, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     torch.set_num_threads(2)
@@ -77,7 +77,7 @@ def _ep_worker(rank, world, port, case, T_local, ret):
             out = (per_route * (w * local).reshape(R, k, 1)).sum(1)
             return out.to(torch.bfloat16)
 
-        ep = P.ExpertParallelMoE(local_fn, experts=E, topk=k, model_dim=H, rank=rank, world=world)
+        ep = P.ExpertParallelMoE(local_fn, experts=E, topk=k, model_dim=H, rank=rank, world=world, exchange=exchange)
         sl = slice(rank * T_local, (rank + 1) * T_local)
         out = ep.forward(case["x_q"][sl].view(torch.uint8), case["x_scale"][sl], case["topk_ids"][sl],
                          case["topk_weights"][sl])
@@ -86,7 +86,8 @@ def _ep_worker(rank, world, port, case, T_local, ret):
         dist.destroy_process_group()
 
 
-def test_expert_parallel_matches_single_process_oracle():
+@pytest.mark.parametrize("exchange", ["fixed", "exact"])
+def test_expert_parallel_matches_single_process_oracle(exchange):
     world, T_local = 2, 12
     case = O.make_moe_case(T=world * T_local, H=256, I=128, E=8, topk=3, seed=7, w_std=0.05)
     ref, _, _, _ = O.torch_moe_two_stage_ref(case["x_q"], case["x_scale"], case["w1_q"], case["w1_scale"],
@@ -94,10 +95,27 @@ def test_expert_parallel_matches_single_process_oracle():
     mgr = mp.Manager()
     ret = mgr.dict()
     port = _free_port()
-    mp.spawn(_ep_worker, args=(world, port, case, T_local, ret), nprocs=world, join=True)
+    mp.spawn(_ep_worker, args=(world, port, case, T_local, exchange, ret), nprocs=world, join=True)
     out = torch.cat([ret[r][0] for r in range(world)], dim=0)
     assert O.max_rel_err(out, ref) <= 1e-2 and O.cosine(out, ref) >= 0.9999
-    # every (token, rank) pair travels exactly once
     need, _, _, _ = P.plan_dispatch(case["topk_ids"], 4, world)
-    assert sum(ret[r][1]["sent_rows"] for r in range(world)) == int(need.sum())
-    assert sum(ret[r][1]["recv_rows"] for r in range(world)) == int(need.sum())
+    if exchange == "exact":   # every (token, rank) pair travels exactly once
+        assert sum(ret[r][1]["sent_rows"] for r in range(world)) == int(need.sum())
+        assert sum(ret[r][1]["recv_rows"] for r in range(world)) == int(need.sum())
+    else:                     # fixed blocks: T_local slots per rank pair
+        assert all(ret[r][1]["sent_rows"] == world * T_local for r in range(world))
+
+
+def test_plan_dispatch_fixed_slots():
+    g = torch.Generator().manual_seed(1)
+    T, k, E, W = 23, 3, 12, 4
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32)
+    need, slot, src = P.plan_dispatch_fixed(ids, E // W, W)
+    need2, _, counts, _ = P.plan_dispatch(ids, E // W, W)
+    assert torch.equal(need, need2) and src.numel() == W * T
+    for r in range(W):
+        block = src[r * T:(r + 1) * T]
+        n = int(counts[r])
+        assert torch.equal(block[:n], torch.nonzero(need[:, r]).flatten()) and (block[n:] == -1).all()
+        for t in torch.nonzero(need[:, r]).flatten().tolist():
+            assert int(block[int(slot[t, r])]) == t
