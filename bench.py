@@ -407,35 +407,41 @@ def moe_ep_bench(rank, world, dev, peaks, quick=False):
     EL, TL = E // world, T // world
     w1, w1_s, w2, w2_s = make_moe_gpu(0, H, I, EL, topk, dev, seed=0, e_lo=rank * EL)
     shard = parallel.LocalExpertShard(w1, w1_s, w2, w2_s, experts=E, topk=topk, rank=rank, world=world)
-    ep = parallel.ExpertParallelMoE(shard, experts=E, topk=topk, model_dim=H, rank=rank, world=world)
     g = torch.Generator(device=dev).manual_seed(1000 + rank)
     x_q, x_s = quant_1x128_torch(torch.randn(TL, H, generator=g, device=dev))
     logits = torch.randn(TL, E, generator=g, device=dev)
     vals, ids = torch.topk(torch.softmax(logits, dim=1), k=topk, dim=1)
     tw = (vals / vals.sum(dim=1, keepdim=True)).float()
     ids = ids.to(torch.int32)
-    for _ in range(3):
-        ep.forward(x_q, x_s, ids, tw)
-    times = []
-    for _ in range(5 if quick else 10):
-        barrier(world)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        ep.forward(x_q, x_s, ids, tw)
-        e1.record()
-        e1.synchronize()
-        times.append(e0.elapsed_time(e1))
-    ms = max_over_ranks(statistics.median(times), world)
-    ep.trace = True
-    ep.forward(x_q, x_s, ids, tw)     # one extra, instrumented step: phase times of rank 0
-    ep.trace = False
-    stats = ep.last_stats
-    return [{"tokens": T, "tokens_per_rank": TL, "experts_per_rank": EL, "ms": round(ms, 4),
-             "tokens_per_s": round(T / (ms * 1e-3), 1), "parallelism": f"ep{world}",
-             "dispatch_bytes_per_rank": stats.get("dispatch_bytes"),
-             "combine_bytes_per_rank": stats.get("combine_bytes"),
-             "phase_ms_rank0": stats.get("phase_ms"),
-             "collective": "NCCL all_to_all_single, equal splits (T/W row slots per rank pair), no host sync"}]
+    notes = {"peer": "CUDA kernels over peer memory (NVLink): rows pushed into the destination's receive "
+                     "area, partial rows pulled and summed by the source; two flag barriers; no NCCL call",
+             "fixed": "NCCL all_to_all_single, equal splits (T/W row slots per rank pair), no host sync"}
+    out = []
+    for mode in ("peer", "fixed"):
+        ep = parallel.ExpertParallelMoE(shard, experts=E, topk=topk, model_dim=H, rank=rank, world=world,
+                                        exchange=mode)
+        for _ in range(3):
+            ep.forward(x_q, x_s, ids, tw)
+        times = []
+        for _ in range(5 if quick else 10):
+            barrier(world)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            ep.forward(x_q, x_s, ids, tw)
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1))
+        ms = max_over_ranks(statistics.median(times), world)
+        ep.trace = True
+        ep.forward(x_q, x_s, ids, tw)     # one extra, instrumented step: phase times of rank 0
+        ep.trace = False
+        stats = ep.last_stats
+        if ep.peer is not None:
+            ep.peer.close()
+        out.append({"tokens": T, "tokens_per_rank": TL, "experts_per_rank": EL, "ms": round(ms, 4),
+                    "tokens_per_s": round(T / (ms * 1e-3), 1), "parallelism": f"ep{world}",
+                    "exchange": mode, "phase_ms_rank0": stats.get("phase_ms"), "collective": notes[mode]})
+    return out
 
 
 def run_ours(args):

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_int, c_int32, c_int64, c_size_t, c_void_p, POINTER
+from ctypes import c_char_p, c_int, c_int32, c_int64, c_size_t, c_uint32, c_void_p, POINTER
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("FLYB200_LIB_PATH") or os.path.join(_PKG_DIR, "lib", "libflyb200.so")
@@ -59,6 +59,15 @@ SIGNATURES = {
     "flyb200_quant_1x128_devrows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32,
                                             c_void_p]),
     "flyb200_ep_plan_pack": (c_int, [c_void_p] * 4 + [c_int32] * 5 + [c_void_p] * 5),
+    "flyb200_ep_gather_packed": (c_int, [c_void_p] * 5 + [c_int32] * 4 + [c_void_p]),
+    "flyb200_ep_combine": (c_int, [c_void_p] * 4 + [c_int32] * 4 + [c_void_p]),
+    "flyb200_ep_buffer_create": (c_int, [c_int64, c_void_p, c_void_p]),
+    "flyb200_ep_buffer_open": (c_int, [c_void_p, c_void_p]),
+    "flyb200_ep_buffer_close": (c_int, [c_void_p]),
+    "flyb200_ep_buffer_destroy": (c_int, [c_void_p]),
+    "flyb200_ep_barrier": (c_int, [c_void_p, c_int32, c_int32, c_int64, c_uint32, c_int32, c_void_p]),
+    "flyb200_ep_push": (c_int, [c_void_p] * 4 + [c_int32] * 6 + [c_void_p, c_int64] + [c_void_p] * 4),
+    "flyb200_ep_pull_combine": (c_int, [c_void_p, c_int64] + [c_void_p] * 3 + [c_int32] * 5 + [c_void_p]),
     "flyb200_query_device_error": (c_int, [c_void_p, POINTER(c_int32)]),
     "flyb200_last_error_string": (c_char_p, []),
     "flyb200_version": (c_int, []),

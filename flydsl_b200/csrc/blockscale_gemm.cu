@@ -93,6 +93,18 @@ struct Cfg {
   // release round trip (about a thousand cycles) for the narrow tiles.
   static constexpr int kAccBufs = (512 / BN) > 8 ? 8 : (512 / BN);
   static constexpr int kTmemCols = BN * kAccBufs;
+  // Optional (compile with -DFLYB200_SPLIT_N): 256-wide tiles issue each K block as two 128-column
+  // MMA groups with a commit after each, so the epilogue drains the first half while the tensor core
+  // works on the second and the MMA -> drain -> release round trip spans four half buffers instead
+  // of two whole ones. Measured on B200 it is SLOWER (M=4096 N=7168 K=2048: 86 us against 68 us):
+  // an N=128 instruction re-reads the A tile from shared memory per 128 columns and the tensor core
+  // becomes bound by shared-memory bandwidth. Off by default.
+#ifdef FLYB200_SPLIT_N
+  static constexpr bool kSplit = (BN == 256);
+#else
+  static constexpr bool kSplit = false;
+#endif
+  static constexpr int kHalves = kSplit ? 2 : 1;
   static constexpr int kCH = BN / 4;  // columns per epilogue thread per column group
   static constexpr int kSmemBytes = kStages * kStageBytes + kCBytes + kMiscBytes + 1024;
   static_assert(kStages >= 3, "pipeline too shallow");
@@ -208,12 +220,16 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   constexpr int kDone = kStages + kAccBufs;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto done_bar = [&](uint32_t i) { return bar_base + 8u * (kStages + i); };
-  auto tempty_bar = [&](int b) { return bar_base + 8u * (kStages + kDone + b); };
-  const uint32_t epi_bar = bar_base + 8u * (kStages + kDone + kAccBufs);
-  volatile uint32_t* tmem_slot =
-      reinterpret_cast<volatile uint32_t*>(misc + 1024 + 8 * (kStages + kDone + kAccBufs + 1));
-  volatile int* abort_flag =
-      reinterpret_cast<volatile int*>(misc + 1024 + 8 * (kStages + kDone + kAccBufs + 1) + 4);
+  // half[i] (split tiles only): the first 128 columns of iteration i are in TMEM. tempty[b][h]: the
+  // epilogue has read half h of accumulator buffer b.
+  constexpr int kHalves = C::kHalves;
+  auto half_bar = [&](uint32_t i) { return bar_base + 8u * (kStages + kDone + i); };
+  auto tempty_bar = [&](int b, int h) { return bar_base + 8u * (kStages + 2 * kDone + b * 2 + h); };
+  constexpr int kNumBars = kStages + 2 * kDone + 2 * kAccBufs + 1;
+  static_assert(8 * kNumBars + 8 <= 1024, "barrier area overflows the misc block");
+  const uint32_t epi_bar = bar_base + 8u * (kNumBars - 1);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc + 1024 + 8 * kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 1024 + 8 * kNumBars + 4);
   // wait until the stage that iteration `it` is about to overwrite has been consumed
   auto wait_stage_free = [&](uint32_t it, int code) -> bool {
     if (it < static_cast<uint32_t>(kStages)) return true;
@@ -226,7 +242,9 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) mbar_init(full_bar(s), gather_a ? 3 : 1);
     for (int i = 0; i < kDone; ++i) mbar_init(done_bar(i), 1);
-    for (int b = 0; b < kAccBufs; ++b) mbar_init(tempty_bar(b), kEpiWarps);  // one arrival per warp
+    for (int i = 0; i < kDone; ++i) mbar_init(half_bar(i), 1);
+    for (int b = 0; b < kAccBufs; ++b)
+      for (int h = 0; h < 2; ++h) mbar_init(tempty_bar(b, h), kEpiWarps);  // one arrival per warp
     mbar_init(epi_bar, kEpiWarps);
     *abort_flag = 0;
     fence_proxy_async_smem();
@@ -315,7 +333,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
     } else if (warp == 1 && lane == 0) {
       // ---------------- MMA issuer ----------------
-      constexpr uint32_t idesc = umma_idesc_e4m3_f32(BM, BN);
+      constexpr uint32_t idesc = umma_idesc_e4m3_f32(BM, BN / kHalves);
       uint32_t it = 0;
       bool alive = true;
       for (int tile = walk.first(); tile < walk.total && alive; tile = walk.next(tile)) {
@@ -330,7 +348,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint32_t ph = (it / kStages) & 1;
           const int buf = it % kAccBufs;
           const uint32_t tph = (it / kAccBufs) & 1;
-          if (!mbar_wait(tempty_bar(buf), tph ^ 1, abort_flag, p.err, kErrWaitTmemEmpty) ||
+          if (!mbar_wait(tempty_bar(buf, 0), tph ^ 1, abort_flag, p.err, kErrWaitTmemEmpty) ||
               !mbar_wait(full_bar(s), ph, abort_flag, p.err, kErrWaitSmemFull)) {
             alive = false;
             break;
@@ -352,6 +370,18 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #else
             tc_mma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
 #endif
+          if constexpr (kHalves == 2) {
+            tc_commit(half_bar(it % kDone));  // columns [0, 128) of this K block are in TMEM
+            if (!mbar_wait(tempty_bar(buf, 1), tph ^ 1, abort_flag, p.err, kErrWaitTmemEmpty)) {
+              alive = false;
+              break;
+            }
+            tc_fence_after();
+            const uint64_t bdesc_hi = umma_desc_sw128(sa + kATileBytes + (BN / 2) * BK);
+#pragma unroll
+            for (int k = 0; k < BK / 32; ++k)
+              tc_mma_f8(d + BN / 2, adesc + 2 * k, bdesc_hi + 2 * k, idesc, k > 0 ? 1u : 0u);
+          }
           tc_commit(done_bar(it % kDone));  // stage reusable + partial sums of this K block in TMEM
           FLYB200_TRACE(2, it);
         }
@@ -600,39 +630,57 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             ring_a[j] = ld_sa(cur, kb + kRing);
             ring_b0[j] = ld_sb(cur.sb_idx0, kb + kRing);
             ring_b1[j] = ld_sb(cur.sb_idx1, kb + kRing);
-            // warp-uniform outcome: the tcgen05.ld below needs the whole warp
-            const bool got = mbar_wait(done_bar(it % kDone), (it / kDone) & 1, abort_flag, p.err,
-                                       kErrWaitTmemFull);
-            if (!__all_sync(0xffffffffu, got)) {
-              alive = false;
-            } else {
+            const uint32_t t0 = tmem_base + lane_base + buf * BN + half * CH;
+            // Loads of LDW columns are software-pipelined against the FMAs of the previous load (two
+            // register buffers). Measured on B200: wider single-shot loads (32/64 columns per wait)
+            // are slower -- the TMEM read port, not latency, bounds a K block at roughly 350
+            // cycles, and the extra registers spill.
+            auto taddr = [&](int q) {  // load q: q < NSUB -> group 0, else group 1
+              return t0 + (q >= NSUB ? BN / 2 : 0) + (q % NSUB) * LDW;
+            };
+            constexpr int NL = NQ / kHalves;  // loads per wait segment
+#pragma unroll
+            for (int h = 0; h < kHalves; ++h) {
+              if (!alive) break;
+              // warp-uniform outcome: the tcgen05.ld below needs the whole warp
+              const bool got = mbar_wait((kHalves == 2 && h == 0) ? half_bar(it % kDone) : done_bar(it % kDone),
+                                         (it / kDone) & 1, abort_flag, p.err, kErrWaitTmemFull);
+              if (!__all_sync(0xffffffffu, got)) {
+                alive = false;
+                break;
+              }
               if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(3, it);
               tc_fence_after();
 #ifdef FLYB200_DBG_SKIP_PROMOTE
               if (kb + 1 < KB) {
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(tempty_bar(buf));
-                ++it;
+                if (lane == 0) {
+                  mbar_arrive(tempty_bar(buf, h));
+                  if (kHalves == 1) mbar_arrive(tempty_bar(buf, 1));
+                }
                 continue;
               }
 #endif
-              const uint32_t t0 = tmem_base + lane_base + buf * BN + half * CH;
-              // Loads of LDW columns are software-pipelined against the FMAs of the previous
-              // load (two register buffers). Measured on B200: wider single-shot loads (32/64
-              // columns per wait) are slower -- the TMEM read port, not latency, bounds a K block
-              // at roughly 350 cycles, and the extra registers spill.
-              auto taddr = [&](int q) {  // load q: q < NSUB -> group 0, else group 1
-                return t0 + (q >= NSUB ? BN / 2 : 0) + (q % NSUB) * LDW;
-              };
               uint32_t va[LDW], vb[LDW];
-              tmem_ld<LDW>(taddr(0), va);
+              tmem_ld<LDW>(taddr(h * NL), va);
               tmem_wait_dep<LDW>(va);
+              auto release = [&]() {  // every load of this segment has landed: hand the columns back
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                  mbar_arrive(tempty_bar(buf, h));
+                  if (kHalves == 1) mbar_arrive(tempty_bar(buf, 1));
+                }
+                if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(4, it);
+              };
+              if (NL == 1) release();
 #pragma unroll
-              for (int q = 0; q < NQ; ++q) {
-                uint32_t* cv = (q & 1) ? vb : va;
-                uint32_t* nv = (q & 1) ? va : vb;
-                if (q + 1 < NQ) tmem_ld<LDW>(taddr(q + 1), nv);   // in flight during the FMAs
+              for (int ql = 0; ql < NL; ++ql) {
+                const int q = h * NL + ql;
+                uint32_t* cv = (ql & 1) ? vb : va;
+                uint32_t* nv = (ql & 1) ? va : vb;
+                if (ql + 1 < NL) tmem_ld<LDW>(taddr(q + 1), nv);   // in flight during the FMAs
                 const float s = (q >= NSUB) ? s1 : s0;
                 const float2 s2 = make_float2(s, s);
                 float2* a = acc + (q >= NSUB ? CH / 2 : 0) + (q % NSUB) * (LDW / 2);
@@ -640,16 +688,13 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 for (int c = 0; c < LDW / 2; ++c)
                   a[c] = __ffma2_rn(make_float2(__uint_as_float(cv[2 * c]),
                                                 __uint_as_float(cv[2 * c + 1])), s2, a[c]);
-                if (q + 1 < NQ) {
+                if (ql + 1 < NL) {
                   tmem_wait_dep<LDW>(nv);
-                  if (q + 2 == NQ) {  // every load of this buffer has landed: hand it back
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty_bar(buf));
-                    if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(4, it);
-                  }
+                  if (ql + 2 == NL) release();
                 }
               }
+            }
+            if (alive) {
               ++it;
             }
           }

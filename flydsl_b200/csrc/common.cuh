@@ -35,6 +35,7 @@ enum DeviceError : int {
   kErrWaitGather = 5,     // gather warps gave up waiting for a free stage
   kErrWaitEpilogue = 6,   // an epilogue warp gave up waiting for the other epilogue warps
   kErrWaitExchange = 7,   // decode kernel: split-K partials of a cluster neighbour never arrived
+  kErrWaitPeer = 8,       // expert-parallel barrier: a peer rank's flag never arrived
 };
 
 // ---- shared-memory address / mbarrier --------------------------------------------------------

@@ -6,52 +6,9 @@
 // Send layout: W blocks of T row slots; row = [H fp8 | H/128 f32 scales | k i32 expert ids | k f32
 // route weights]. Unused slots carry expert id -1 in every position, which the receiver's sorter drops.
 #include "common.cuh"
+#include "ep_plan.cuh"
 
 namespace flyb200 {
-
-constexpr int kPlanThreads = 1024;
-
-// One CTA per destination rank r: need[t][r], slot[t][r] (exclusive running count of needed tokens)
-// and src[r*T + slot] = t; the tail of the block is filled with -1.
-__global__ void __launch_bounds__(kPlanThreads)
-ep_plan_kernel(const int* __restrict__ topk_ids, int T, int k, int W, int experts_per_rank,
-               uint8_t* __restrict__ need, int* __restrict__ slot, int* __restrict__ src) {
-  __shared__ int warp_tot[kPlanThreads / 32];
-  __shared__ int base_s;
-  const int r = blockIdx.x;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) base_s = 0;
-  __syncthreads();
-  for (int t0 = 0; t0 < T; t0 += kPlanThreads) {
-    const int t = t0 + threadIdx.x;
-    bool nd = false;
-    if (t < T) {
-      for (int j = 0; j < k; ++j) {
-        const int id = topk_ids[t * k + j];
-        nd |= (id >= 0) && (id / experts_per_rank == r);
-      }
-    }
-    const unsigned bal = __ballot_sync(0xffffffffu, nd);
-    if (lane == 0) warp_tot[warp] = __popc(bal);
-    __syncthreads();
-    int before = base_s;
-    for (int w = 0; w < warp; ++w) before += warp_tot[w];
-    const int s = before + __popc(bal & ((1u << lane) - 1u));
-    if (t < T) {
-      need[t * W + r] = nd ? 1 : 0;
-      slot[t * W + r] = nd ? s : 0;
-      if (nd) src[r * T + s] = t;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int tot = 0;
-      for (int w = 0; w < kPlanThreads / 32; ++w) tot += warp_tot[w];
-      base_s += tot;
-    }
-    __syncthreads();
-  }
-  for (int s = base_s + threadIdx.x; s < T; s += kPlanThreads) src[r * T + s] = -1;
-}
 
 // One warp per send row.
 __global__ void __launch_bounds__(256)
@@ -109,6 +66,110 @@ extern "C" int flyb200_ep_plan_pack(const void* x, const float* x_scale, const i
   if (blocks > sms * 8) blocks = sms * 8;
   ep_pack_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint8_t*>(x), x_scale, topk_ids, topk_weights,
                                          src_out, static_cast<uint8_t*>(send_out), rows, H, k);
+  FLYB200_CUDA_CHECK(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Receiving side: activations straight from the packed receive buffer into routing order (what
+// flyb200_moe_gather_rows does for plain tensors), so the packed rows are never copied apart.
+namespace flyb200 {
+__global__ void __launch_bounds__(256)
+ep_gather_packed_kernel(const uint8_t* __restrict__ packed, const int* __restrict__ sorted_ids,
+                        const int* __restrict__ num_valid, uint4* __restrict__ x_out,
+                        float* __restrict__ scale_out_t, int rows_in, int H, int row_bytes,
+                        int rows_out) {
+  const int chunks = H / 16, nscale = H / 128;
+  const int valid = min(num_valid[0], rows_out);
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int i = warp; i < valid; i += nwarps) {
+    const int t = sorted_ids[i] & 0xFFFFFF;
+    const bool ok = t < rows_in;
+    const uint8_t* row = packed + static_cast<size_t>(ok ? t : 0) * row_bytes;
+    const uint4* s4 = reinterpret_cast<const uint4*>(row);
+    for (int c = lane; c < chunks; c += 32)
+      x_out[static_cast<size_t>(i) * chunks + c] = ok ? s4[c] : make_uint4(0u, 0u, 0u, 0u);
+    const float* sc = reinterpret_cast<const float*>(row + H);
+    for (int s = lane; s < nscale; s += 32)
+      scale_out_t[static_cast<size_t>(s) * rows_out + i] = ok ? sc[s] : 0.f;
+  }
+}
+
+// Sending side, after the combine all-to-all: out[t] = sum over ranks r (ascending) of the partial row
+// back[r*T + slot[t][r]] where need[t][r]; fp32 accumulate, one 16-byte vector per thread.
+template <typename T>
+__global__ void __launch_bounds__(256)
+ep_combine_kernel(const T* __restrict__ back, const uint8_t* __restrict__ need,
+                  const int* __restrict__ slot, T* __restrict__ out, int tokens, int W, int H) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int vec_per_row = H / VEC;
+  const long long total = static_cast<long long>(tokens) * vec_per_row;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i / vec_per_row);
+    const int v = static_cast<int>(i - static_cast<long long>(t) * vec_per_row);
+    float acc[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+    for (int r = 0; r < W; ++r) {
+      if (!need[t * W + r]) continue;
+      const long long row = static_cast<long long>(r) * tokens + slot[t * W + r];
+      const uint4 raw = *reinterpret_cast<const uint4*>(back + row * H + static_cast<long long>(v) * VEC);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) acc[j] += static_cast<float>(e[j]);
+    }
+    uint4 o;
+    T* po = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) po[j] = static_cast<T>(acc[j]);
+    *reinterpret_cast<uint4*>(out + static_cast<long long>(t) * H + static_cast<long long>(v) * VEC) = o;
+  }
+}
+}  // namespace flyb200
+
+extern "C" int flyb200_ep_gather_packed(const void* packed, const int32_t* sorted_ids,
+                                        const int32_t* num_valid_ids, void* x_out, float* scale_out_t,
+                                        int32_t rows_in, int32_t H, int32_t k, int32_t rows_out,
+                                        void* stream) {
+  if (!packed || !sorted_ids || !num_valid_ids || !x_out || !scale_out_t)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_gather_packed: NULL buffer");
+  if ((reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(x_out)) % 16)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_gather_packed: buffers must be 16-byte aligned");
+  if (rows_in < 1 || rows_out < 1 || H < 128 || H % 128 || k < 1 || (8 * k) % 16)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_gather_packed: bad sizes");
+  const int sms = sm_count();
+  if (sms <= 0) return FLYB200_ERR_CUDA;
+  const int row_bytes = H + 4 * (H / 128) + 8 * k;
+  ep_gather_packed_kernel<<<sms * 4, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(packed), sorted_ids, num_valid_ids, static_cast<uint4*>(x_out),
+      scale_out_t, rows_in, H, row_bytes, rows_out);
+  FLYB200_CUDA_CHECK(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+extern "C" int flyb200_ep_combine(const void* back, const uint8_t* need, const int32_t* slot, void* out,
+                                  int32_t T, int32_t W, int32_t H, int32_t dtype, void* stream) {
+  if (!back || !need || !slot || !out)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_combine: NULL buffer");
+  if ((reinterpret_cast<uintptr_t>(back) | reinterpret_cast<uintptr_t>(out)) % 16)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_combine: buffers must be 16-byte aligned");
+  if (T < 1 || W < 1 || H < 8 || H % 8 || (dtype != FLYB200_BF16 && dtype != FLYB200_F16))
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_combine: bad sizes or dtype");
+  const int sms = sm_count();
+  if (sms <= 0) return FLYB200_ERR_CUDA;
+  const long long total = static_cast<long long>(T) * (H / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > static_cast<long long>(sms) * 16) blocks = static_cast<long long>(sms) * 16;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == FLYB200_BF16)
+    ep_combine_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(back), need, slot, static_cast<__nv_bfloat16*>(out), T, W, H);
+  else
+    ep_combine_kernel<__half><<<static_cast<int>(blocks), 256, 0, st>>>(
+        static_cast<const __half*>(back), need, slot, static_cast<__half*>(out), T, W, H);
   FLYB200_CUDA_CHECK(cudaGetLastError());
   return FLYB200_OK;
 }

@@ -16,8 +16,13 @@ top-k reduce (``valid_mask``, kernels/moe_blockscale_2stage.py:2554-2563).
                masked reduce: one partial output row per received token;
     combine    partial rows go back the same way; the source rank adds a token's partials in a
                fixed rank order (deterministic).
-  The collectives are NCCL all-to-alls (``all_to_all_single`` with split sizes) over NVLink;
-  receive buffers are ordinary local memory, which is what the GEMM kernels read.
+  Three exchange modes (``ExpertParallelMoE(exchange=...)``):
+    "peer"   CUDA kernels over peer memory (:class:`PeerExchange`): rows are written straight into
+             the destination's receive area and partial rows are read from the rank that computed
+             them; only needed rows cross NVLink; two flag barriers per step, no NCCL call;
+    "fixed"  two equal-split NCCL all-to-alls on fixed row slots (no host sync; also the gloo path);
+    "exact"  NCCL all-to-alls with split sizes (one host sync for the counts).
+  Receive buffers are local memory in every mode, which is what the GEMM kernels read.
 """
 from __future__ import annotations
 
@@ -159,24 +164,22 @@ def plan_pack_cuda(x_u8, x_scale, topk_ids, topk_weights, experts_per_rank, worl
         x_u8.data_ptr(), x_scale.contiguous().data_ptr(), ids.contiguous().data_ptr(),
         w.contiguous().data_ptr(), T, H, k, world, experts_per_rank, need.data_ptr(), slot.data_ptr(),
         src.data_ptr(), rows.data_ptr(), _lib.stream_handle(None)))
-    return need.bool(), slot.long(), rows
+    return need, slot, rows
 
 
 def combine_partials_fixed(back, need, slot, out_dtype):
     """out[t] = sum over ranks r (ascending) of back[r*T + slot[t, r]] where needed; fp32."""
     T, W = need.shape
     if back.is_cuda and back.dtype in (torch.bfloat16, torch.float16) and back.shape[1] % 8 == 0:
-        # one gather into [T, W, H], then the masked fixed-order reduce kernel
         from . import _lib
 
-        base = torch.arange(W, device=back.device).view(1, W) * T
-        gathered = back[(base + slot.clamp(min=0)).reshape(-1)]                  # [T*W, H]
         out = torch.empty((T, back.shape[1]), dtype=back.dtype, device=back.device)
-        mask = need.to(torch.uint8).contiguous()
-        _lib.check(_lib.load().flyb200_moe_reduce(
-            gathered.data_ptr(), out.data_ptr(), mask.data_ptr(), T, W, back.shape[1],
+        _lib.check(_lib.load().flyb200_ep_combine(
+            back.data_ptr(), need.to(torch.uint8).contiguous().data_ptr(),
+            slot.to(torch.int32).contiguous().data_ptr(), out.data_ptr(), T, W, back.shape[1],
             _lib.BF16 if back.dtype == torch.bfloat16 else _lib.F16, _lib.stream_handle(None)))
         return out.to(out_dtype)
+    need, slot = need.bool(), slot.long()
     acc = torch.zeros((T, back.shape[1]), dtype=torch.float32, device=back.device)
     base = torch.arange(W, device=back.device).view(1, W) * T
     idx = (base + slot.clamp(min=0))
@@ -249,17 +252,21 @@ class ExpertParallelMoE:
         self.rank, self.world, self.group, self.out_dtype = rank, world, group, out_dtype
         self.experts_per_rank = experts // world
         self.last_stats = {}
-        if exchange not in ("fixed", "exact"):
-            raise ValueError("exchange must be 'fixed' (T row slots per rank pair, no host sync) or "
-                             "'exact' (only the needed rows travel; one host sync for the counts)")
+        if exchange not in ("fixed", "exact", "peer"):
+            raise ValueError("exchange must be 'peer' (CUDA kernels over peer memory), 'fixed' (T row "
+                             "slots per rank pair, no host sync) or 'exact' (only the needed rows "
+                             "travel; one host sync for the counts)")
         self.exchange = exchange
         self.trace = False
+        self.peer = None     # PeerExchange, created on the first "peer" step (needs T)
 
     def forward(self, x_q, x_scale, topk_ids, topk_weights):
         """x_q fp8/uint8 [T, H]; x_scale f32 [T, H/128] (token-major); ids [T, k]; weights [T, k]."""
         x_u8 = x_q.view(torch.uint8)
         if self.exchange == "fixed":
             return self._forward_fixed(x_u8, x_scale, topk_ids, topk_weights)
+        if self.exchange == "peer":
+            return self._forward_peer(x_u8, x_scale, topk_ids, topk_weights)
         need, order, counts, pos = plan_dispatch(topk_ids, self.experts_per_rank, self.world)
         recv_counts = exchange_counts(counts, self.group)
         send_l, recv_l = counts.tolist(), recv_counts.tolist()       # one host sync per step
@@ -298,9 +305,11 @@ def _forward_fixed(self, x_u8, x_scale, topk_ids, topk_weights):
     got = torch.empty_like(rows)
     dist.all_to_all_single(got, rows, group=self.group)
     mark("dispatch")
-    rx_q, rx_s, rids, rw = unpack_rows(got, self.H, self.k)
-    mark("unpack")
-    partial = self.local_fn(rx_q, rx_s, rids, rw).contiguous()                  # [W*T, H]
+    if got.is_cuda and hasattr(self.local_fn, "forward_packed"):
+        partial = self.local_fn.forward_packed(got)                             # rows read in place
+    else:
+        rx_q, rx_s, rids, rw = unpack_rows(got, self.H, self.k)
+        partial = self.local_fn(rx_q, rx_s, rids, rw).contiguous()              # [W*T, H]
     mark("local experts")
     back = torch.empty_like(partial)
     dist.all_to_all_single(back, partial, group=self.group)
@@ -317,6 +326,159 @@ def _forward_fixed(self, x_u8, x_scale, topk_ids, topk_weights):
 
 
 ExpertParallelMoE._forward_fixed = _forward_fixed
+
+
+class _RawCuda:
+    """Device memory owned by the C library, exposed to torch without a copy."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1",
+                                         "data": (int(ptr), False), "version": 2}
+
+
+class PeerExchange:
+    """The exchange buffers of one rank and its mappings of the peers' buffers.
+
+    Layout of every rank's buffer: receive area ``[W*T, row bytes]`` | partial area ``[W*T, H]``
+    (16-bit) | ``W`` barrier flags. Created collectively (every rank of ``group`` must call it with
+    the same sizes): one all-gather of the 64-byte IPC handles."""
+
+    def __init__(self, *, tokens: int, model_dim: int, topk: int, rank: int, world: int, device,
+                 group=None, limit_ms: int = 2000):
+        import ctypes
+
+        from . import _lib
+
+        self.T, self.H, self.k, self.rank, self.world = tokens, model_dim, topk, rank, world
+        self.group, self.limit_ms, self.device = group, int(limit_ms), torch.device(device)
+        self.row_bytes = model_dim + 4 * (model_dim // 128) + 8 * topk
+        al = lambda n: (n + 255) // 256 * 256
+        self.recv_off = 0
+        self.part_off = al(world * tokens * self.row_bytes)
+        self.flag_off = self.part_off + al(world * tokens * model_dim * 2)
+        self.nbytes = self.flag_off + 256
+        self._lib = _lib.load()
+        own = ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(self.device):
+            _lib.check(self._lib.flyb200_ep_buffer_create(self.nbytes, ctypes.byref(own), handle))
+            self.own = int(own.value)
+            mine = torch.tensor(list(bytes(handle)), dtype=torch.uint8, device=self.device)
+            every = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(every, mine, group=group)
+            self._opened = []
+            ptrs = []
+            for r in range(world):
+                if r == rank:
+                    ptrs.append(self.own)
+                    continue
+                raw = (ctypes.c_ubyte * 64)(*every[r].cpu().tolist())
+                q = ctypes.c_void_p()
+                _lib.check(self._lib.flyb200_ep_buffer_open(raw, ctypes.byref(q)))
+                self._opened.append(int(q.value))
+                ptrs.append(int(q.value))
+            self.peers = (ctypes.c_void_p * world)(*ptrs)
+            whole = torch.as_tensor(_RawCuda(self.own, self.nbytes), device=self.device)
+            self.recv = whole[: world * tokens * self.row_bytes].view(world * tokens, self.row_bytes)
+            self.partial_u8 = whole[self.part_off: self.part_off + world * tokens * model_dim * 2]
+            self.epoch = 0
+            dist.barrier(group=group)   # every buffer exists and is zeroed before the first push
+
+    def partial(self, dtype):
+        return self.partial_u8.view(dtype).view(self.world * self.T, self.H)
+
+    def barrier(self):
+        from . import _lib
+
+        self.epoch += 1
+        _lib.check(self._lib.flyb200_ep_barrier(self.peers, self.world, self.rank, self.flag_off,
+                                                self.epoch, self.limit_ms, _lib.stream_handle(None)))
+
+    def push(self, x_u8, x_scale, topk_ids, topk_weights, experts_per_rank):
+        """Plan + write this rank's token rows into the destinations' receive areas."""
+        from . import _lib
+
+        T, W, dev = self.T, self.world, x_u8.device
+        ids = (topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)).contiguous()
+        w = (topk_weights if topk_weights.dtype == torch.float32 else topk_weights.float()).contiguous()
+        need = torch.empty((T, W), dtype=torch.uint8, device=dev)
+        slot = torch.empty((T, W), dtype=torch.int32, device=dev)
+        src = torch.empty((W * T,), dtype=torch.int32, device=dev)
+        _lib.check(self._lib.flyb200_ep_push(
+            x_u8.data_ptr(), x_scale.contiguous().data_ptr(), ids.data_ptr(), w.data_ptr(), T, self.H,
+            self.k, W, self.rank, experts_per_rank, self.peers, self.recv_off, need.data_ptr(),
+            slot.data_ptr(), src.data_ptr(), _lib.stream_handle(None)))
+        return need, slot
+
+    def pull_combine(self, need, slot, dtype):
+        from . import _lib
+
+        out = torch.empty((self.T, self.H), dtype=dtype, device=need.device)
+        _lib.check(self._lib.flyb200_ep_pull_combine(
+            self.peers, self.part_off, need.data_ptr(), slot.data_ptr(), out.data_ptr(), self.T,
+            self.world, self.H, self.rank, _lib.BF16 if dtype == torch.bfloat16 else _lib.F16,
+            _lib.stream_handle(None)))
+        return out
+
+    def close(self):
+        """Collective: unmap the peers' buffers, then free the own one."""
+        from . import _lib
+
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        with torch.cuda.device(self.device):
+            for q in self._opened:
+                _lib.check(self._lib.flyb200_ep_buffer_close(q))
+            self._opened = []
+            dist.barrier(group=self.group)
+            if self.own:
+                self.recv = self.partial_u8 = None
+                _lib.check(self._lib.flyb200_ep_buffer_destroy(self.own))
+                self.own = 0
+
+
+def _forward_peer(self, x_u8, x_scale, topk_ids, topk_weights):
+    """Exchange by CUDA kernels over peer memory; ``local_fn`` must offer ``forward_packed``
+    (:class:`LocalExpertShard` does). The whole step is enqueued without a host sync."""
+    if not x_u8.is_cuda:
+        raise ValueError("exchange='peer' needs CUDA tensors (one GPU per rank)")
+    if self.out_dtype not in (torch.bfloat16, torch.float16):
+        raise ValueError("exchange='peer' combines 16-bit partial rows")
+    T = x_u8.shape[0]
+    if self.peer is None or self.peer.T != T:
+        if self.peer is not None:
+            self.peer.close()
+        self.peer = PeerExchange(tokens=T, model_dim=self.H, topk=self.k, rank=self.rank,
+                                 world=self.world, device=x_u8.device, group=self.group)
+    px = self.peer
+    marks = []
+
+    def mark(name):
+        if self.trace:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            marks.append((name, e))
+
+    mark("start")
+    need, slot = px.push(x_u8, x_scale, topk_ids, topk_weights, self.experts_per_rank)
+    mark("plan+push")
+    px.barrier()                                   # every rank's rows have landed here
+    mark("barrier")
+    self.local_fn.forward_packed(px.recv, out=px.partial(self.out_dtype))
+    mark("local experts")
+    px.barrier()                                   # every rank's partial rows are complete
+    mark("barrier 2")
+    out = px.pull_combine(need, slot, self.out_dtype)
+    mark("pull+sum")
+    self.last_stats = {"sent_rows": None, "recv_rows": self.world * T, "exchange": "peer"}
+    if marks:
+        torch.cuda.synchronize()
+        self.last_stats["phase_ms"] = {marks[i + 1][0]: round(marks[i][1].elapsed_time(marks[i + 1][1]), 4)
+                                       for i in range(len(marks) - 1)}
+    return out
+
+
+ExpertParallelMoE._forward_peer = _forward_peer
 
 
 class LocalExpertShard:
@@ -370,20 +532,49 @@ class LocalExpertShard:
         return b
 
     def __call__(self, x_q_u8, x_scale, topk_ids, topk_weights):
-        from . import _lib
-        from .utils import moe_gather_rows, moe_sorting
+        from .utils import moe_gather_rows
 
         R = x_q_u8.shape[0]
-        dev = x_q_u8.device
         if R == 0:
-            return torch.zeros((0, self.H), dtype=self.out_dtype, device=dev)
+            return torch.zeros((0, self.H), dtype=self.out_dtype, device=x_q_u8.device)
+        xs_t = x_scale.t().contiguous()
+
+        def gather(b, sid, npp):
+            moe_gather_rows(x_q_u8.view(torch.float8_e4m3fn), xs_t, sid, npp, topk=self.k,
+                            out=b["x_sorted"], scale_out=b["xs_sorted"])
+
+        return self._run(R, x_q_u8.device, topk_ids, topk_weights, gather, None)
+
+    def forward_packed(self, rows, out=None):
+        """Same as calling the shard on ``unpack_rows(rows)``, but the packed rows
+        ``[R, H + 4*H/128 + 8*k]`` (uint8) are read in place: only ids and weights are sliced out,
+        activations and scales go straight into routing order."""
+        from . import _lib
+
+        R = rows.shape[0]
+        H, k = self.H, self.k
+        o1 = H + 4 * (H // 128)
+        if rows.shape[1] != o1 + 8 * k or not rows.is_contiguous():
+            raise ValueError("forward_packed: rows must be contiguous [R, H + 4*H/128 + 8*k] bytes")
+        ids = rows[:, o1:o1 + 4 * k].contiguous().view(torch.int32).view(R, k)
+        w = rows[:, o1 + 4 * k:o1 + 8 * k].contiguous().view(torch.float32).view(R, k)
+
+        def gather(b, sid, npp):
+            _lib.check(_lib.load().flyb200_ep_gather_packed(
+                rows.data_ptr(), sid.data_ptr(), npp.data_ptr(), b["x_sorted"].data_ptr(),
+                b["xs_sorted"].data_ptr(), R, H, k, b["L"], _lib.stream_handle(None)))
+
+        return self._run(R, rows.device, ids, w, gather, out)
+
+    def _run(self, R, dev, topk_ids, topk_weights, gather, out):
+        from . import _lib
+        from .utils import moe_sorting
+
         b = self._buffers(R, dev)
         sid, sw, seid, npp = moe_sorting(topk_ids, topk_weights, num_experts=self.E,
                                          block_size=self.tile_m, expert_mask=self.expert_mask)
         nblk = seid.numel()
-        xs_t = x_scale.t().contiguous()
-        moe_gather_rows(x_q_u8.view(torch.float8_e4m3fn), xs_t, sid, npp, topk=self.k,
-                        out=b["x_sorted"], scale_out=b["xs_sorted"])
+        gather(b, sid, npp)
         self.gemm1(b["out1"], b["x_sorted"], self.w1, b["xs_sorted"], self.w1_scale, sid, seid, sw, npp,
                    R, self.I, self.H, nblk, None)
         _lib.check(_lib.load().flyb200_quant_1x128_devrows(
@@ -391,8 +582,9 @@ class LocalExpertShard:
             self.I, self._mid_code, _lib.stream_handle(None)))
         self.gemm2(b["routes"], b["a2_q"], self.w2, b["a2_s"], self.w2_scale, sid, seid, sw, npp, R,
                    self.H, self.I, nblk, None)
-        ids = topk_ids.long()
-        valid = ((ids >= 0) & (ids < self.E))
-        valid = (valid & (self.expert_mask[ids.clamp(0, self.E - 1)] != 0)).to(torch.uint8).contiguous()
-        self.reduce(b["routes"], b["out"], valid, R, None)
-        return b["out"]
+        # a route counts here iff its expert lives on this rank (-1 marks an unused slot)
+        valid = (torch.div(topk_ids, self.EL, rounding_mode="floor") == self.rank).to(torch.uint8)
+        if out is None:
+            out = b["out"]
+        self.reduce(b["routes"], out, valid, R, None)
+        return out

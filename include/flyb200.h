@@ -187,6 +187,48 @@ int flyb200_ep_plan_pack(const void* x, const float* x_scale, const int32_t* top
                          int32_t experts_per_rank, uint8_t* need_out, int32_t* slot_out,
                          int32_t* src_out, void* send_out, void* stream);
 
+/* Expert-parallel receive side: flyb200_moe_gather_rows reading straight from a packed receive
+ * buffer (rows_in rows in the flyb200_ep_plan_pack row format) -- x_out [rows_out, H] in routing
+ * order, scale_out_t [H/128, rows_out]. No reference counterpart. */
+int flyb200_ep_gather_packed(const void* packed, const int32_t* sorted_ids,
+                             const int32_t* num_valid_ids, void* x_out, float* scale_out_t,
+                             int32_t rows_in, int32_t H, int32_t k, int32_t rows_out, void* stream);
+
+/* Expert-parallel final sum: out[t] = sum over ranks r, ascending, of back[r*T + slot[t][r]] where
+ * need[t][r] (fp32 accumulate; back/out BF16|F16 [*, H]). No reference counterpart. */
+int flyb200_ep_combine(const void* back, const uint8_t* need, const int32_t* slot, void* out, int32_t T,
+                       int32_t W, int32_t H, int32_t dtype, void* stream);
+
+/* ---- Expert-parallel exchange over peer memory (one process per GPU, NVLink). No reference
+ * counterpart: the reference is single-GPU. Every rank creates one exchange buffer, passes the 64-byte
+ * handle to its peers (any host channel) and opens theirs; peers[r] below is rank r's buffer as mapped
+ * in THIS process (peers[rank] = the own buffer). These four calls allocate / map device memory and
+ * belong at start-up. ---- */
+int flyb200_ep_buffer_create(int64_t bytes, void** ptr_out, void* ipc_handle_out /* 64 bytes */);
+int flyb200_ep_buffer_open(const void* ipc_handle, void** ptr_out);
+int flyb200_ep_buffer_close(void* opened_ptr);
+int flyb200_ep_buffer_destroy(void* ptr);
+
+/* All-rank barrier on the stream: flags (W x u32, zero at creation) live at flag_off in every buffer;
+ * epoch must grow by one per call, the same on every rank. A rank waits at most limit_ms for each
+ * peer, then records FLYB200_ERR_DEVICE_TIMEOUT in the device error word and goes on. */
+int flyb200_ep_barrier(const void* const* peers, int32_t W, int32_t rank, int64_t flag_off,
+                       uint32_t epoch, int32_t limit_ms, void* stream);
+
+/* flyb200_ep_plan_pack whose rows go straight into the destinations' receive areas (at recv_off in
+ * each buffer; row of (source rank s, slot j) = s*T + j) instead of a send buffer. */
+int flyb200_ep_push(const void* x, const float* x_scale, const int32_t* topk_ids,
+                    const float* topk_weights, int32_t T, int32_t H, int32_t k, int32_t W, int32_t rank,
+                    int32_t experts_per_rank, const void* const* peers, int64_t recv_off,
+                    uint8_t* need_out, int32_t* slot_out, int32_t* src_out, void* stream);
+
+/* flyb200_ep_combine reading each partial row from the rank that computed it: rank r's partial area
+ * (at part_off in its buffer, [W*T, H] BF16|F16) holds the row of this rank's token t at
+ * rank*T + slot[t][r]. */
+int flyb200_ep_pull_combine(const void* const* peers, int64_t part_off, const uint8_t* need,
+                            const int32_t* slot, void* out, int32_t T, int32_t W, int32_t H, int32_t rank,
+                            int32_t dtype, void* stream);
+
 /* Reads and clears the device error word of the current device after synchronising `stream`.
  * *code_out = 0 when no kernel reported a problem. The reference only prints GPU errors
  * (lib/Runtime/FlyRocmRuntimeWrappers.cpp:22-30); this is the status-returning equivalent. */

@@ -238,12 +238,95 @@ def test_ep_plan_pack_kernel_matches_torch_logic():
     need_c, slot_c, rows_c = P.plan_pack_cuda(x.to(DEV), xs.to(DEV), ids.to(DEV), w.to(DEV), E // W, W)
     need_t, slot_t, src_t = P.plan_dispatch_fixed(ids, E // W, W)
     rows_t = P.pack_rows_fixed(x, xs, ids, w, src_t)
-    assert torch.equal(need_c.cpu(), need_t)
-    assert torch.equal(slot_c.cpu()[need_t], slot_t[need_t])
+    assert torch.equal(need_c.cpu().bool(), need_t)
+    assert torch.equal(slot_c.cpu().long()[need_t], slot_t[need_t])
     used = src_t >= 0
     assert torch.equal(rows_c.cpu()[used], rows_t[used])
     id_lo = H + 4 * (H // 128)
     assert torch.equal(rows_c.cpu()[~used][:, id_lo:id_lo + 4 * k], rows_t[~used][:, id_lo:id_lo + 4 * k])  # ids = -1
+
+
+def test_ep_peer_kernels_two_ranks_emulated_on_one_gpu():
+    """Push, packed local experts and pull+sum of the peer-memory exchange with both ranks' buffers
+    on this GPU and their kernels issued one after the other on one stream (the flag barrier is
+    left to the two-GPU test: kernels that wait for each other must not share a GPU). Against the
+    single-process oracle and, bit for bit, against the torch/NCCL-path functions."""
+    import ctypes
+
+    from flydsl_b200 import _lib, parallel as P
+    from flydsl_b200.utils import shuffle_weight
+
+    W, T, H, I, E, k = 2, 48, 512, 256, 8, 4
+    m = O.make_moe_case(T=W * T, H=H, I=I, E=E, topk=k, seed=21, w_std=0.05)
+    ref, _, _, _ = O.torch_moe_two_stage_ref(m["x_q"], m["x_scale"], m["w1_q"], m["w1_scale"], m["w2_q"],
+                                             m["w2_scale"], m["topk_ids"], m["topk_weights"], 256)
+    lib = _lib.load()
+    EL = E // W
+    row_bytes = H + 4 * (H // 128) + 8 * k
+    part_off = (W * T * row_bytes + 255) // 256 * 256
+    nbytes = part_off + W * T * H * 2
+    bufs, views = [], []
+    for r in range(W):
+        q, h = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
+        _lib.check(lib.flyb200_ep_buffer_create(nbytes, ctypes.byref(q), h))
+        bufs.append(int(q.value))
+        views.append(torch.as_tensor(P._RawCuda(int(q.value), nbytes), device=DEV))
+    peers = (ctypes.c_void_p * W)(*bufs)
+    try:
+        shards, plans = [], []
+        for r in range(W):
+            lo, hi = r * EL, (r + 1) * EL
+            shards.append(P.LocalExpertShard(
+                shuffle_weight(m["w1_q"][lo:hi].to(DEV)), m["w1_scale"][lo:hi].to(DEV),
+                shuffle_weight(m["w2_q"][lo:hi].to(DEV)), m["w2_scale"][lo:hi].to(DEV),
+                experts=E, topk=k, rank=r, world=W, tile_m=32))
+        for r in range(W):      # every rank pushes its tokens
+            sl = slice(r * T, (r + 1) * T)
+            x = m["x_q"][sl].view(torch.uint8).to(DEV)
+            xs, ids = m["x_scale"][sl].to(DEV).contiguous(), m["topk_ids"][sl].to(DEV).to(torch.int32).contiguous()
+            w = m["topk_weights"][sl].to(DEV).float().contiguous()
+            need = torch.empty((T, W), dtype=torch.uint8, device=DEV)
+            slot = torch.empty((T, W), dtype=torch.int32, device=DEV)
+            src = torch.empty((W * T,), dtype=torch.int32, device=DEV)
+            _lib.check(lib.flyb200_ep_push(x.data_ptr(), xs.data_ptr(), ids.data_ptr(), w.data_ptr(), T, H, k, W,
+                                           r, EL, peers, 0, need.data_ptr(), slot.data_ptr(), src.data_ptr(),
+                                           _lib.stream_handle(None)))
+            plans.append((need, slot))
+            # what landed in rank d's receive area is what the packed NCCL path would have sent there
+            _, _, rows = P.plan_pack_cuda(x, xs, ids, w, EL, W)
+            used = (src >= 0).cpu()
+            for d in range(W):
+                got = views[d][: W * T * row_bytes].view(W * T, row_bytes)[r * T:(r + 1) * T].cpu()
+                u = used[d * T:(d + 1) * T]
+                assert torch.equal(got[u], rows[d * T:(d + 1) * T].cpu()[u])
+                id_lo = H + 4 * (H // 128)
+                assert (got[~u][:, id_lo:id_lo + 4 * k].contiguous().view(torch.int32) == -1).all()
+        for r in range(W):      # local experts on the packed rows, partials into the own partial area
+            recv = views[r][: W * T * row_bytes].view(W * T, row_bytes)
+            part = views[r][part_off:part_off + W * T * H * 2].view(torch.bfloat16).view(W * T, H)
+            shards[r].forward_packed(recv, out=part)
+            rx = P.unpack_rows(recv, H, k)
+            assert torch.equal(shards[r](*rx).clone(), part)          # same result as the unpacked entry
+        outs = []
+        for r in range(W):      # every rank pulls and sums the partial rows of its tokens
+            need, slot = plans[r]
+            out = torch.empty((T, H), dtype=torch.bfloat16, device=DEV)
+            _lib.check(lib.flyb200_ep_pull_combine(peers, part_off, need.data_ptr(), slot.data_ptr(),
+                                                   out.data_ptr(), T, W, H, r, _lib.BF16, _lib.stream_handle(None)))
+            # the NCCL path's combine on the same partial rows: back[q*T + j] = rank q's row r*T + j
+            back = torch.cat([views[q][part_off:part_off + W * T * H * 2].view(torch.bfloat16).view(W * T, H)
+                              [r * T:(r + 1) * T] for q in range(W)], dim=0).contiguous()
+            assert torch.equal(P.combine_partials_fixed(back, need, slot, torch.bfloat16), out)
+            assert torch.equal(P.combine_partials_fixed(back.cpu(), need.cpu(), slot.cpu(), torch.bfloat16), out.cpu())
+            outs.append(out.float().cpu())
+        torch.cuda.synchronize()
+        assert _lib.query_device_error() == 0
+        assert_close_to_oracle(torch.cat(outs, dim=0), ref, "peer exchange, two ranks emulated")
+    finally:
+        torch.cuda.synchronize()
+        views.clear()
+        for q in bufs:
+            _lib.check(lib.flyb200_ep_buffer_destroy(q))
 
 
 def test_skewed_routing_and_empty_experts():

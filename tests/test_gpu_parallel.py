@@ -1,5 +1,5 @@
 """Multi-GPU layer on real GPUs (skipped with fewer than two): N-sharded dense GEMM and the
-expert-parallel MoE over NCCL, each rank a child process, against the single-process CPU oracle."""
+expert-parallel MoE (NCCL exchanges and the peer-memory exchange), each rank a child process, against the single-process CPU oracle."""
 import os
 import socket
 
@@ -43,13 +43,25 @@ def _worker(rank, world, port, dense, moe, ret):
         shard = parallel.LocalExpertShard(shuffle_weight(moe["w1_q"][lo:hi].to(dev)), moe["w1_scale"][lo:hi].to(dev),
                                           shuffle_weight(moe["w2_q"][lo:hi].to(dev)), moe["w2_scale"][lo:hi].to(dev),
                                           experts=E, topk=k, rank=rank, world=world, tile_m=32)
-        ep = parallel.ExpertParallelMoE(shard, experts=E, topk=k, model_dim=H, rank=rank, world=world)
         sl = slice(rank * TL, (rank + 1) * TL)
-        out = ep.forward(moe["x_q"][sl].to(dev), moe["x_scale"][sl].to(dev), moe["topk_ids"][sl].to(dev),
-                         moe["topk_weights"][sl].to(dev))
-        torch.cuda.synchronize()
-        assert _lib.query_device_error() == 0
-        ret[rank] = (c.float().cpu(), out.float().cpu())
+        args = (moe["x_q"][sl].to(dev), moe["x_scale"][sl].to(dev), moe["topk_ids"][sl].to(dev),
+                moe["topk_weights"][sl].to(dev))
+        outs = {}
+        for mode in ("fixed", "exact", "peer"):
+            ep = parallel.ExpertParallelMoE(shard, experts=E, topk=k, model_dim=H, rank=rank, world=world,
+                                            exchange=mode)
+            outs[mode] = ep.forward(*args).float().cpu()
+            if mode == "peer":
+                # a second and third step reuse the exchange areas and the barrier flags
+                for _ in range(2):
+                    again = ep.forward(*args).float().cpu()
+                    assert torch.equal(again, outs[mode])
+                ep.peer.close()
+            torch.cuda.synchronize()
+            assert _lib.query_device_error() == 0
+        # the three exchanges move the same rows and add partials in the same rank order
+        assert torch.equal(outs["fixed"], outs["peer"])
+        ret[rank] = (c.float().cpu(), outs["peer"], outs["exact"])
     finally:
         dist.destroy_process_group()
 
@@ -67,6 +79,7 @@ def test_two_ranks_dense_shards_and_expert_parallel_moe():
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), dense, moe, ret), nprocs=world, join=True)
     c = torch.cat([ret[r][0] for r in range(world)], dim=1)
-    out = torch.cat([ret[r][1] for r in range(world)], dim=0)
     assert O.max_rel_err(c, ref_c) <= 1e-2 and O.cosine(c, ref_c) >= 0.9999
-    assert O.max_rel_err(out, ref_o) <= 1e-2 and O.cosine(out, ref_o) >= 0.9999
+    for i in (1, 2):
+        out = torch.cat([ret[r][i] for r in range(world)], dim=0)
+        assert O.max_rel_err(out, ref_o) <= 1e-2 and O.cosine(out, ref_o) >= 0.9999
