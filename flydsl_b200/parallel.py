@@ -305,7 +305,7 @@ def _forward_fixed(self, x_u8, x_scale, topk_ids, topk_weights):
     got = torch.empty_like(rows)
     dist.all_to_all_single(got, rows, group=self.group)
     mark("dispatch")
-    if got.is_cuda and hasattr(self.local_fn, "forward_packed"):
+    if got.is_cuda and self.k % 2 == 0 and hasattr(self.local_fn, "forward_packed"):
         partial = self.local_fn.forward_packed(got)                             # rows read in place
     else:
         rx_q, rx_s, rids, rw = unpack_rows(got, self.H, self.k)
@@ -444,6 +444,8 @@ def _forward_peer(self, x_u8, x_scale, topk_ids, topk_weights):
         raise ValueError("exchange='peer' needs CUDA tensors (one GPU per rank)")
     if self.out_dtype not in (torch.bfloat16, torch.float16):
         raise ValueError("exchange='peer' combines 16-bit partial rows")
+    if self.k % 2:
+        raise ValueError("exchange='peer' needs an even top-k (packed rows must stay 16-byte aligned)")
     T = x_u8.shape[0]
     if self.peer is None or self.peer.T != T:
         if self.peer is not None:

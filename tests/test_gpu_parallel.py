@@ -73,7 +73,7 @@ def test_two_ranks_dense_shards_and_expert_parallel_moe():
     world = 2
     dense = O.make_dense_case(96, 512, 512, seed=1)
     ref_c = O.run_torch_blockscale(dense["a_q"], dense["b_q"], dense["a_scale"], dense["b_scale"], dtype=torch.float32)
-    moe = O.make_moe_case(T=64, H=512, I=256, E=8, topk=3, seed=3, w_std=0.05)
+    moe = O.make_moe_case(T=64, H=512, I=256, E=8, topk=4, seed=3, w_std=0.05)
     ref_o, _, _, _ = O.torch_moe_two_stage_ref(moe["x_q"], moe["x_scale"], moe["w1_q"], moe["w1_scale"], moe["w2_q"],
                                                moe["w2_scale"], moe["topk_ids"], moe["topk_weights"], 256)
     ret = mp.Manager().dict()
