@@ -6,13 +6,32 @@
 //
 // Every CTA rebuilds the full per-expert histogram (the id array is at most a few hundred KB and
 // comes from L2), scans the padded counts to find its own base offset, then compacts its expert's
-// routes in order: each warp owns a contiguous segment, counts its matches, and after one
-// block-level prefix writes them at base + earlier-warps + running rank.
+// routes in order. Both passes over the ids give every thread 32 CONSECUTIVE ids, fetched as eight
+// 16-byte loads that are all in flight at once (the passes are latency-bound otherwise); a thread
+// counts its matches, one block-level prefix turns the counts into positions, and the thread writes
+// its matches in order.
 #include "common.cuh"
 
 namespace flyb200 {
 
 constexpr int kSortThreads = 1024;
+constexpr int kChunk = 32;  // consecutive ids per thread per round
+
+// ids[i0 .. i0 + kChunk) into registers; -1 (matches no expert) beyond n.
+__device__ __forceinline__ void load_chunk(const int* __restrict__ ids, int i0, int n, bool vec_ok,
+                                           int (&v)[kChunk]) {
+  if (vec_ok && i0 + kChunk <= n) {
+    const int4* p4 = reinterpret_cast<const int4*>(ids + i0);
+#pragma unroll
+    for (int j = 0; j < kChunk / 4; ++j) {
+      const int4 q = __ldg(p4 + j);
+      v[4 * j] = q.x; v[4 * j + 1] = q.y; v[4 * j + 2] = q.z; v[4 * j + 3] = q.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < kChunk; ++j) v[j] = (i0 + j < n) ? __ldg(ids + i0 + j) : -1;
+  }
+}
 
 struct SortParams {
   const int* topk_ids;
@@ -48,11 +67,17 @@ moe_sort_kernel(const SortParams p) {
   const int n = p.T_eff * p.k;
   const int sentinel = (p.k << 24) | p.T;
 
+  // A masked expert owns no rows and nobody depends on its CTA (CTA 0 also writes the buffer tails).
+  if (e != 0 && p.expert_mask && p.expert_mask[e] == 0) return;
   for (int i = tid; i < p.E; i += kSortThreads) hist[i] = 0;
   __syncthreads();
-  for (int i = tid; i < n; i += kSortThreads) {
-    const int id = p.topk_ids[i];
-    if (id >= 0 && id < p.E) atomicAdd(&hist[id], 1);
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(p.topk_ids) & 15) == 0;
+  for (int r0 = 0; r0 < n; r0 += kSortThreads * kChunk) {
+    int v[kChunk];
+    load_chunk(p.topk_ids, r0 + tid * kChunk, n, vec_ok, v);
+#pragma unroll
+    for (int j = 0; j < kChunk; ++j)
+      if (v[j] >= 0 && v[j] < p.E) atomicAdd(&hist[v[j]], 1);
   }
   __syncthreads();
 
@@ -112,32 +137,45 @@ moe_sort_kernel(const SortParams p) {
   const int my_cnt = hist[e];
   const int my_padded = ((my_cnt + p.block_m - 1) / p.block_m) * p.block_m;
 
-  // Ordered compaction. Warp w owns routes [w*seg, (w+1)*seg).
-  const int seg = (((n + kSortThreads / 32 - 1) / (kSortThreads / 32)) + 31) & ~31;
-  const int lo = warp * seg;
-  const int hi = min(n, lo + seg);
-  int cnt = 0;
-  for (int i0 = lo; i0 < hi; i0 += 32) {
-    const int i = i0 + lane;
-    const bool hit = (i < hi) && (p.topk_ids[i] == e);
-    cnt += __popc(__ballot_sync(0xffffffffu, hit));
-  }
-  if (lane == 0) warp_cnt[warp] = cnt;
-  __syncthreads();
-  int rank = my_base;
-  for (int w = 0; w < warp; ++w) rank += warp_cnt[w];
-  for (int i0 = lo; i0 < hi; i0 += 32) {
-    const int i = i0 + lane;
-    const bool hit = (i < hi) && (p.topk_ids[i] == e);
-    const unsigned bal = __ballot_sync(0xffffffffu, hit);
-    if (hit) {
-      const int pos = rank + __popc(bal & ((1u << lane) - 1u));
-      const int t = i / p.k;
-      const int slot = i - t * p.k;
-      p.sorted_ids[pos] = (slot << 24) | t;
-      p.sorted_weights[pos] = p.topk_weights[i];
+  // Ordered compaction: thread t of round r owns routes [r0 + t*kChunk, r0 + (t+1)*kChunk).
+  int running = my_base;
+  for (int r0 = 0; r0 < n; r0 += kSortThreads * kChunk) {
+    int v[kChunk];
+    const int i0 = r0 + tid * kChunk;
+    load_chunk(p.topk_ids, i0, n, vec_ok, v);
+    int cnt = 0;
+#pragma unroll
+    for (int j = 0; j < kChunk; ++j) cnt += (v[j] == e) ? 1 : 0;
+    int incl = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
     }
-    rank += __popc(bal);
+    if (lane == 31) warp_cnt[warp] = incl;
+    __syncthreads();
+    int before = 0, all = 0;
+    for (int w = 0; w < kSortThreads / 32; ++w) {
+      const int c = warp_cnt[w];
+      before += (w < warp) ? c : 0;
+      all += c;
+    }
+    int pos = running + before + incl - cnt;
+    if (cnt) {
+#pragma unroll
+      for (int j = 0; j < kChunk; ++j) {
+        if (v[j] == e) {
+          const int i = i0 + j;
+          const int t = i / p.k;
+          const int slot = i - t * p.k;
+          p.sorted_ids[pos] = (slot << 24) | t;
+          p.sorted_weights[pos] = p.topk_weights[i];
+          ++pos;
+        }
+      }
+    }
+    running += all;
+    __syncthreads();
   }
   for (int i = my_cnt + tid; i < my_padded; i += kSortThreads) {
     p.sorted_ids[my_base + i] = sentinel;

@@ -529,6 +529,9 @@ class LocalExpertShard:
                  "a2_q": torch.empty((L, self.I), dtype=torch.float8_e4m3fn, device=dev),
                  "a2_s": torch.empty((self.I // 128, L), dtype=torch.float32, device=dev),
                  "routes": torch.empty((R * self.k, self.H), dtype=self.out_dtype, device=dev),
+                 "ids": torch.empty((R, self.k), dtype=torch.int32, device=dev),
+                 "w": torch.empty((R, self.k), dtype=torch.float32, device=dev),
+                 "valid": torch.empty((R, self.k), dtype=torch.uint8, device=dev),
                  "out": torch.empty((R, self.H), dtype=self.out_dtype, device=dev)}
             self._buf[R] = b
         return b
@@ -558,17 +561,20 @@ class LocalExpertShard:
         o1 = H + 4 * (H // 128)
         if rows.shape[1] != o1 + 8 * k or not rows.is_contiguous():
             raise ValueError("forward_packed: rows must be contiguous [R, H + 4*H/128 + 8*k] bytes")
-        ids = rows[:, o1:o1 + 4 * k].contiguous().view(torch.int32).view(R, k)
-        w = rows[:, o1 + 4 * k:o1 + 8 * k].contiguous().view(torch.float32).view(R, k)
+        b = self._buffers(R, rows.device)
+        ids, w, valid = b["ids"], b["w"], b["valid"]
+        _lib.check(_lib.load().flyb200_ep_unpack_meta(
+            rows.data_ptr(), R, H, k, self.EL, self.rank, ids.data_ptr(), w.data_ptr(), valid.data_ptr(),
+            _lib.stream_handle(None)))
 
         def gather(b, sid, npp):
             _lib.check(_lib.load().flyb200_ep_gather_packed(
                 rows.data_ptr(), sid.data_ptr(), npp.data_ptr(), b["x_sorted"].data_ptr(),
                 b["xs_sorted"].data_ptr(), R, H, k, b["L"], _lib.stream_handle(None)))
 
-        return self._run(R, rows.device, ids, w, gather, out)
+        return self._run(R, rows.device, ids, w, gather, out, valid)
 
-    def _run(self, R, dev, topk_ids, topk_weights, gather, out):
+    def _run(self, R, dev, topk_ids, topk_weights, gather, out, valid=None):
         from . import _lib
         from .utils import moe_sorting
 
@@ -585,7 +591,8 @@ class LocalExpertShard:
         self.gemm2(b["routes"], b["a2_q"], self.w2, b["a2_s"], self.w2_scale, sid, seid, sw, npp, R,
                    self.H, self.I, nblk, None)
         # a route counts here iff its expert lives on this rank (-1 marks an unused slot)
-        valid = (torch.div(topk_ids, self.EL, rounding_mode="floor") == self.rank).to(torch.uint8)
+        if valid is None:
+            valid = (torch.div(topk_ids, self.EL, rounding_mode="floor") == self.rank).to(torch.uint8)
         if out is None:
             out = b["out"]
         self.reduce(b["routes"], out, valid, R, None)
