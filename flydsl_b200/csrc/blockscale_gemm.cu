@@ -93,14 +93,16 @@ struct Cfg {
   // release round trip (about a thousand cycles) for the narrow tiles.
   static constexpr int kAccBufs = (512 / BN) > 8 ? 8 : (512 / BN);
   static constexpr int kTmemCols = BN * kAccBufs;
-  // Optional (compile with -DFLYB200_SPLIT_N): 256-wide tiles issue each K block as two 128-column
-  // MMA groups with a commit after each, so the epilogue drains the first half while the tensor core
-  // works on the second and the MMA -> drain -> release round trip spans four half buffers instead
-  // of two whole ones. Measured on B200 it is SLOWER (M=4096 N=7168 K=2048: 86 us against 68 us):
-  // an N=128 instruction re-reads the A tile from shared memory per 128 columns and the tensor core
-  // becomes bound by shared-memory bandwidth. Off by default.
+  // Optional (-DFLYB200_SPLIT_N), dense 256-wide tiles: every K block is issued as two 128-column
+  // MMA groups by two issuer threads (warps 1 and 2) with a commit each, so the epilogue drains the
+  // first half while the tensor core works on the second and the MMA -> drain -> release round trip
+  // spans four half buffers instead of two whole ones. Measured on B200 it is SLOWER and therefore
+  // off: M=4096 N=7168 K=2048 takes 76.6 us with two issuers (86 us with one) against 68.6 us
+  // unsplit -- an N=128 instruction re-reads the A tile from shared memory per 128 columns, and
+  // MMA-only runs (no loads, no promotion) give 1500 TFLOP/s for 128-wide against 2270-2590 for
+  // 256-wide instructions.
 #ifdef FLYB200_SPLIT_N
-  static constexpr bool kSplit = (BN == 256);
+  static constexpr bool kSplit = (BN == 256) && (MODE == 0);
 #else
   static constexpr bool kSplit = false;
 #endif
@@ -234,6 +236,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   auto wait_stage_free = [&](uint32_t it, int code) -> bool {
     if (it < static_cast<uint32_t>(kStages)) return true;
     const uint32_t j = it - kStages;
+    if (kHalves == 2 && !mbar_wait(half_bar(j % kDone), (j / kDone) & 1, abort_flag, p.err, code)) return false;
     return mbar_wait(done_bar(j % kDone), (j / kDone) & 1, abort_flag, p.err, code);
   };
 
@@ -331,8 +334,12 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
         }
       }
-    } else if (warp == 1 && lane == 0) {
+    } else if ((warp == 1 || (kHalves == 2 && warp == 2)) && lane == 0) {
       // ---------------- MMA issuer ----------------
+      // Split tiles have two issuers: warp 1 feeds columns [0, BN/2) of every K block, warp 2 the
+      // rest, each with its own commit, so that the instruction-issue cost (tens of cycles per
+      // tcgen05.mma, serial in one thread) is spread over two threads.
+      const int h = (kHalves == 2 && warp == 2) ? 1 : 0;
       constexpr uint32_t idesc = umma_idesc_e4m3_f32(BM, BN / kHalves);
       uint32_t it = 0;
       bool alive = true;
@@ -348,20 +355,20 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint32_t ph = (it / kStages) & 1;
           const int buf = it % kAccBufs;
           const uint32_t tph = (it / kAccBufs) & 1;
-          if (!mbar_wait(tempty_bar(buf, 0), tph ^ 1, abort_flag, p.err, kErrWaitTmemEmpty) ||
+          if (!mbar_wait(tempty_bar(buf, h), tph ^ 1, abort_flag, p.err, kErrWaitTmemEmpty) ||
               !mbar_wait(full_bar(s), ph, abort_flag, p.err, kErrWaitSmemFull)) {
             alive = false;
             break;
           }
-          FLYB200_TRACE(1, it);
+          if (h == 0) FLYB200_TRACE(1, it);
           tc_fence_after();
           const uint32_t sa = smem_base + s * C::kStageBytes;
           const uint64_t adesc = umma_desc_sw128(sa);
-          const uint64_t bdesc = umma_desc_sw128(sa + kATileBytes);
+          const uint64_t bdesc = umma_desc_sw128(sa + kATileBytes + h * (BN / 2) * BK);
 #ifdef FLYB200_DBG_SAMEBUF
-          const uint32_t d = tmem_base;
+          const uint32_t d = tmem_base + h * (BN / 2);
 #else
-          const uint32_t d = tmem_base + buf * BN;
+          const uint32_t d = tmem_base + buf * BN + h * (BN / 2);
 #endif
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k)
@@ -370,20 +377,9 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #else
             tc_mma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
 #endif
-          if constexpr (kHalves == 2) {
-            tc_commit(half_bar(it % kDone));  // columns [0, 128) of this K block are in TMEM
-            if (!mbar_wait(tempty_bar(buf, 1), tph ^ 1, abort_flag, p.err, kErrWaitTmemEmpty)) {
-              alive = false;
-              break;
-            }
-            tc_fence_after();
-            const uint64_t bdesc_hi = umma_desc_sw128(sa + kATileBytes + (BN / 2) * BK);
-#pragma unroll
-            for (int k = 0; k < BK / 32; ++k)
-              tc_mma_f8(d + BN / 2, adesc + 2 * k, bdesc_hi + 2 * k, idesc, k > 0 ? 1u : 0u);
-          }
-          tc_commit(done_bar(it % kDone));  // stage reusable + partial sums of this K block in TMEM
-          FLYB200_TRACE(2, it);
+          // this issuer's MMAs of the K block are done: partial sums in TMEM, operands consumed
+          tc_commit((kHalves == 2 && h == 0) ? half_bar(it % kDone) : done_bar(it % kDone));
+          if (h == 0) FLYB200_TRACE(2, it);
         }
       }
     } else if (MODE != kDense && warp >= 2 && gather_a) {
