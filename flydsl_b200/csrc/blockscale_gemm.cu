@@ -19,6 +19,8 @@
 // The computation follows kernel_gemm / compute_tile_blockscale of the reference
 // (kernels/blockscale_preshuffle_gemm.py:161-839, :509-587) and the stage kernels of
 // kernels/moe_blockscale_2stage.py (:206-1161, :1386-2387); none of its AMD data movement is kept.
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace flyb200 {
@@ -73,6 +75,10 @@ struct GemmParams {
   int out_sorted;
   int a_rows;
   int group;               // tiles a CTA processes back to back (see TileWalker)
+  // Stage 1 with the 1x128 re-quantisation fused into the epilogue (256-wide tiles, routing-order
+  // output): fp8 rows [a_rows, N] and their scales [N/128, a_rows] instead of the 16-bit `out`.
+  uint8_t* out_q;
+  float* out_scale_t;
 };
 
 template <int BN, int MODE, typename OutT>
@@ -155,6 +161,12 @@ __device__ __forceinline__ void red8<float>(float* dst, const float* v) {
                  "f"(v[4 * i]), "f"(v[4 * i + 1]), "f"(v[4 * i + 2]), "f"(v[4 * i + 3])
                  : "memory");
 }
+
+__device__ __forceinline__ float round_through(float v, __half) { return __half2float(__float2half_rn(v)); }
+__device__ __forceinline__ float round_through(float v, __nv_bfloat16) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+__device__ __forceinline__ float round_through(float v, float) { return v; }
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
   // silu(g) * u with the fast exp, as the reference does (moe_blockscale_2stage.py:239-251).
@@ -738,7 +750,82 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                        "r"(q.z), "r"(q.w)
                        : "memory");
         };
-        if constexpr (MODE == kMoe1) {
+        bool tile_stored = false;
+        if constexpr (MODE == kMoe1 && BN == 256) {
+          if (p.out_q) {
+            // Fused 1x128 re-quantisation (what flyb200_quant_1x128 does to the 16-bit stage-1
+            // output, bit for bit): the tile's 128 output columns are exactly one scale group of
+            // each row. Values are rounded through the 16-bit type first, as the unfused path
+            // stores them; the row's two threads (64 columns each) exchange their amax through
+            // shared memory. fp8 tile: 128 rows x 128 bytes in staging region 0 (16-byte chunks
+            // swizzled by row); amax/scale scratch in region 1.
+            float* amax_s = reinterpret_cast<float*>(smem_al + kStages * C::kStageBytes + kRegionBytes);
+            float* scale_s = amax_s + 2 * BM;
+            float* yq = const_cast<float*>(accf);   // y overwrites the gate half of the accumulators
+            float vmax = -3.4e38f, vmin = 3.4e38f;
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              float v = round_through(silu_mul(accf[j], accf[CH + j]) * route_w, OutT());
+              if (v != v) v = 0.f;
+              else if (isinf(v)) v = v > 0.f ? 448.f : -448.f;
+              yq[j] = v;
+              vmax = fmaxf(vmax, v);
+              vmin = fminf(vmin, v);
+            }
+            amax_s[half * BM + r] = fmaxf(vmax, -vmin);
+            if (!epi_sync()) { alive = false; break; }
+            float scale = __fdiv_rn(fmaxf(amax_s[r], amax_s[BM + r]), 448.f);
+            if (scale == 0.f) scale = 1.f;
+#pragma unroll
+            for (int j = 0; j < CH; j += 16) {
+              uint32_t w4[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint32_t w = 0;
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                  w |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(__fdiv_rn(yq[j + 4 * q + b], scale),
+                                                                   __NV_SATFINITE, __NV_E4M3)) << (8 * b);
+                w4[q] = w;
+              }
+              const int chunk = (half * CH + j) >> 4;
+              const uint32_t addr = cstage_base + r * 128 + ((chunk ^ (r & 7)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w4[0]), "r"(w4[1]),
+                           "r"(w4[2]), "r"(w4[3])
+                           : "memory");
+            }
+            if (half == 0) {
+              row_off[r] = row_ok ? static_cast<long long>(m_blk * p.tile_m + r) : -1LL;  // sorted row
+              scale_s[r] = scale;
+            }
+            if (!epi_sync()) { alive = false; break; }
+            const int rows = min(BM, p.tile_m);
+            const int ch = lane & 7;                       // 8 chunks of 16 bytes per row
+            if (n0 + 128 <= p.N) {
+              for (int r0 = ew * 4; r0 < rows; r0 += kEpiWarps * 4) {
+                const int rr = r0 + (lane >> 3);
+                if (rr < rows) {
+                  const long long srow = row_off[rr];
+                  if (srow >= 0) {
+                    const uint32_t addr = cstage_base + rr * 128 + ((ch ^ (rr & 7)) << 4);
+                    uint4 q;
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                                 : "r"(addr)
+                                 : "memory");
+                    *reinterpret_cast<uint4*>(p.out_q + srow * p.N + n0 + ch * 16) = q;
+                    if (ch == 0)
+                      p.out_scale_t[static_cast<long long>(n0 / 128) * p.a_rows + srow] = scale_s[rr];
+                  }
+                }
+              }
+            }
+            tile_stored = true;
+          }
+        }
+        if (tile_stored) {
+          // nothing left to do for this tile
+        } else if constexpr (MODE == kMoe1) {
 #pragma unroll
           for (int j = 0; j < CH; j += 8) {
             float y[8];
@@ -758,47 +845,49 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
           }
         }
-        if constexpr (MODE != kDense) {
-          if (half == 0) row_off[r] = row_ok ? static_cast<long long>(out_row) : -1LL;
-        } else {
-          fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA store
-        }
-        if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(6, it);
-        if (!epi_sync()) { alive = false; break; }
-        if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(7, it);
-        // (3) write the tile out
-        if constexpr (MODE == kDense) {
-          if (store_thread) {
-#pragma unroll
-            for (int reg = 0; reg < C::kRegions; ++reg)
-              if (n0 + reg * 64 < p.N)
-                tma_store_2d(&tmap_c, cstage_base + reg * kRegionBytes, n0 + reg * 64, m_blk * BM);
-            bulk_commit_group();
+        if (!tile_stored) {
+          if constexpr (MODE != kDense) {
+            if (half == 0) row_off[r] = row_ok ? static_cast<long long>(out_row) : -1LL;
+          } else {
+            fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA store
           }
-        } else {
-          constexpr int CPR = C::kOutCols / 8;   // 16-byte chunks per output row
-          constexpr int RPI = 32 / CPR;          // rows per warp instruction
-          const int rows = min(BM, p.tile_m);
-          const int ch = lane % CPR;
-          const int col = ch * 8;
-          if (n0 + col + 8 <= p.N) {
-            for (int r0 = ew * RPI; r0 < rows; r0 += kEpiWarps * RPI) {
-              const int rr = r0 + lane / CPR;
-              if (rr < rows) {
-                const long long off = row_off[rr];
-                if (off >= 0) {
-                  const uint32_t addr = cstage_base + (col >> 6) * kRegionBytes + rr * 128 +
-                                        ((((col & 63) >> 3) ^ (rr & 7)) << 4);
-                  uint4 q;
-                  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                               : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
-                               : "r"(addr)
-                               : "memory");
-                  OutT* dst = out + off + n0 + col;
-                  if (MODE == kMoe2 && p.accumulate)
-                    red8_packed(dst, q);
-                  else
-                    *reinterpret_cast<uint4*>(dst) = q;
+          if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(6, it);
+          if (!epi_sync()) { alive = false; break; }
+          if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(7, it);
+          // (3) write the tile out
+          if constexpr (MODE == kDense) {
+            if (store_thread) {
+#pragma unroll
+              for (int reg = 0; reg < C::kRegions; ++reg)
+                if (n0 + reg * 64 < p.N)
+                  tma_store_2d(&tmap_c, cstage_base + reg * kRegionBytes, n0 + reg * 64, m_blk * BM);
+              bulk_commit_group();
+            }
+          } else {
+            constexpr int CPR = C::kOutCols / 8;   // 16-byte chunks per output row
+            constexpr int RPI = 32 / CPR;          // rows per warp instruction
+            const int rows = min(BM, p.tile_m);
+            const int ch = lane % CPR;
+            const int col = ch * 8;
+            if (n0 + col + 8 <= p.N) {
+              for (int r0 = ew * RPI; r0 < rows; r0 += kEpiWarps * RPI) {
+                const int rr = r0 + lane / CPR;
+                if (rr < rows) {
+                  const long long off = row_off[rr];
+                  if (off >= 0) {
+                    const uint32_t addr = cstage_base + (col >> 6) * kRegionBytes + rr * 128 +
+                                          ((((col & 63) >> 3) ^ (rr & 7)) << 4);
+                    uint4 q;
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                                 : "r"(addr)
+                                 : "memory");
+                    OutT* dst = out + off + n0 + col;
+                    if (MODE == kMoe2 && p.accumulate)
+                      red8_packed(dst, q);
+                    else
+                      *reinterpret_cast<uint4*>(dst) = q;
+                  }
                 }
               }
             }
@@ -1103,14 +1192,13 @@ static int moe_sorted_layout(const flyb200_gemm_cfg* cfg, int T, int E, int k, i
   return make_tensor_map_2d(tmap, act, p->a_rows, kdim, 1, tile_m);
 }
 
-extern "C" int flyb200_moe_gemm1(void* out, const void* x, const void* w_repacked,
-                                 const float* scale_x, const float* scale_w,
-                                 const int32_t* sorted_ids, const int32_t* expert_ids,
-                                 const float* sorted_weights, const int32_t* num_valid_ids,
-                                 int32_t T, int32_t I, int32_t H, int32_t num_blocks, int32_t E,
-                                 int32_t k, int32_t tile_m, int32_t doweight, int32_t out_dtype,
-                                 const flyb200_gemm_cfg* cfg, void* stream) {
-  int rc = moe_common_checks(out, x, w_repacked, scale_x, scale_w, sorted_ids, expert_ids,
+static int moe_gemm1_impl(void* out, void* out_q, float* out_scale_t, const void* x, const void* w_repacked,
+                          const float* scale_x, const float* scale_w, const int32_t* sorted_ids,
+                          const int32_t* expert_ids, const float* sorted_weights,
+                          const int32_t* num_valid_ids, int32_t T, int32_t I, int32_t H,
+                          int32_t num_blocks, int32_t E, int32_t k, int32_t tile_m, int32_t doweight,
+                          int32_t out_dtype, const flyb200_gemm_cfg* cfg, void* stream) {
+  int rc = moe_common_checks(out_q ? out_q : out, x, w_repacked, scale_x, scale_w, sorted_ids, expert_ids,
                              sorted_weights, num_valid_ids, T, I, H, num_blocks, E, k, tile_m,
                              doweight);
   if (rc) return rc;
@@ -1121,6 +1209,17 @@ extern "C" int flyb200_moe_gemm1(void* out, const void* x, const void* w_repacke
   if (sms <= 0) return FLYB200_ERR_CUDA;
   int bn = (cfg && cfg->block_n) ? cfg->block_n : pick_block_n(num_blocks, I, sms, true);
   if (bn < 64) return set_error(FLYB200_ERR_INVALID_ARGUMENT, "stage-1 block_n must be >= 64");
+  if (out_q) {
+    if (cfg && cfg->block_n && cfg->block_n != 256)
+      return set_error(FLYB200_ERR_INVALID_ARGUMENT, "fused re-quantisation needs block_n 256");
+    bn = 256;   // 128 output columns per tile = one 1x128 scale group per row
+    if (!cfg || (cfg->path & 3) != 3)
+      return set_error(FLYB200_ERR_INVALID_ARGUMENT,
+                       "fused re-quantisation needs routing-order input and output (cfg.path bits 0 and 1)");
+    if (I % 128) return set_error(FLYB200_ERR_INVALID_ARGUMENT, "fused re-quantisation needs I %% 128 == 0");
+    if (reinterpret_cast<uintptr_t>(out_q) % 16 || !out_scale_t)
+      return set_error(FLYB200_ERR_INVALID_ARGUMENT, "out_q must be 16-byte aligned, out_scale_t non-NULL");
+  }
   int grid = sms;
   if (cfg && cfg->max_ctas > 0 && cfg->max_ctas < grid) grid = cfg->max_ctas;
   const long tiles = static_cast<long>(num_blocks) * cdiv(I, bn / 2);
@@ -1130,6 +1229,7 @@ extern "C" int flyb200_moe_gemm1(void* out, const void* x, const void* w_repacke
   p.a = reinterpret_cast<const uint8_t*>(x);
   p.b = reinterpret_cast<const uint8_t*>(w_repacked);
   p.scale_a = scale_x; p.scale_b = scale_w; p.out = out;
+  p.out_q = static_cast<uint8_t*>(out_q); p.out_scale_t = out_scale_t;
   p.err = device_error_word();
   if (!p.err) return FLYB200_ERR_CUDA;
   p.M = T; p.N = I; p.K = H; p.a_box_rows = 0;
@@ -1143,6 +1243,31 @@ extern "C" int flyb200_moe_gemm1(void* out, const void* x, const void* w_repacke
   if (out_dtype == FLYB200_BF16)
     return launch_bn<kMoe1, __nv_bfloat16>(bn, tmap, tmap, p, grid, st);
   return launch_bn<kMoe1, __half>(bn, tmap, tmap, p, grid, st);
+}
+
+extern "C" int flyb200_moe_gemm1(void* out, const void* x, const void* w_repacked,
+                                 const float* scale_x, const float* scale_w,
+                                 const int32_t* sorted_ids, const int32_t* expert_ids,
+                                 const float* sorted_weights, const int32_t* num_valid_ids,
+                                 int32_t T, int32_t I, int32_t H, int32_t num_blocks, int32_t E,
+                                 int32_t k, int32_t tile_m, int32_t doweight, int32_t out_dtype,
+                                 const flyb200_gemm_cfg* cfg, void* stream) {
+  return moe_gemm1_impl(out, nullptr, nullptr, x, w_repacked, scale_x, scale_w, sorted_ids, expert_ids,
+                        sorted_weights, num_valid_ids, T, I, H, num_blocks, E, k, tile_m, doweight,
+                        out_dtype, cfg, stream);
+}
+
+extern "C" int flyb200_moe_gemm1_q8(void* out_q, float* out_scale_t, const void* x, const void* w_repacked,
+                                    const float* scale_x, const float* scale_w,
+                                    const int32_t* sorted_ids, const int32_t* expert_ids,
+                                    const float* sorted_weights, const int32_t* num_valid_ids,
+                                    int32_t T, int32_t I, int32_t H, int32_t num_blocks, int32_t E,
+                                    int32_t k, int32_t tile_m, int32_t doweight, int32_t mid_dtype,
+                                    const flyb200_gemm_cfg* cfg, void* stream) {
+  if (!out_q || !out_scale_t) return set_error(FLYB200_ERR_INVALID_ARGUMENT, "gemm1_q8: NULL output");
+  return moe_gemm1_impl(nullptr, out_q, out_scale_t, x, w_repacked, scale_x, scale_w, sorted_ids, expert_ids,
+                        sorted_weights, num_valid_ids, T, I, H, num_blocks, E, k, tile_m, doweight,
+                        mid_dtype, cfg, stream);
 }
 
 extern "C" int flyb200_moe_gemm2(void* out, const void* a2, const void* w_repacked,

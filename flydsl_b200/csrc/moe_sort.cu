@@ -185,9 +185,78 @@ moe_sort_kernel(const SortParams p) {
     p.sorted_expert_ids[my_base / p.block_m + b] = cid;
 }
 
+// Router: top-k of a token's expert scores in descending order (= slot order) and a softmax over the
+// k selected values, as the reference's test router does with torch.topk + torch.softmax
+// (tests/kernels/test_moe_blockscale.py:228-230). One warp per token; a lane keeps every 32nd score
+// in registers; k rounds of warp arg-max (ties go to the lower expert id).
+constexpr int kRouteMaxPerLane = 32;  // experts <= 1024
+
+__global__ void __launch_bounds__(256)
+moe_route_topk_kernel(const float* __restrict__ logits, int T, int E, int k, int* __restrict__ ids_out,
+                      float* __restrict__ w_out) {
+  const int lane = threadIdx.x & 31;
+  const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (t >= T) return;
+  float v[kRouteMaxPerLane];
+#pragma unroll
+  for (int j = 0; j < kRouteMaxPerLane; ++j) {
+    const int e = j * 32 + lane;
+    v[j] = (e < E) ? logits[static_cast<size_t>(t) * E + e] : -INFINITY;
+    if (v[j] != v[j]) v[j] = -INFINITY;   // NaN scores are never selected
+  }
+  float top = 0.f, sum = 0.f, mine = 0.f;
+  int mine_id = 0;
+  for (int s = 0; s < k; ++s) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < kRouteMaxPerLane; ++j) {
+      const int e = j * 32 + lane;
+      if (e < E && (v[j] > best || (v[j] == best && e < best_e))) { best = v[j]; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    if (s == 0) top = best;
+    const float p = expf(best - top);
+    sum += p;
+    if (lane == s % 32) { mine = p; mine_id = best_e; }
+    if (s % 32 == 31 || s == k - 1) {   // flush up to 32 selections (k <= 32 in practice: one flush)
+      const int s0 = s - (s % 32);
+      if (s0 + lane <= s) {
+        ids_out[static_cast<size_t>(t) * k + s0 + lane] = mine_id;
+        w_out[static_cast<size_t>(t) * k + s0 + lane] = mine;   // normalised below
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kRouteMaxPerLane; ++j)
+      if (j * 32 + lane == best_e) v[j] = -INFINITY;
+  }
+  __syncwarp();
+  for (int s = lane; s < k; s += 32)
+    w_out[static_cast<size_t>(t) * k + s] = __fdiv_rn(w_out[static_cast<size_t>(t) * k + s], sum);
+}
+
 }  // namespace flyb200
 
 using namespace flyb200;
+
+extern "C" int flyb200_moe_route_topk(const float* logits, int32_t T, int32_t E, int32_t k,
+                                      int32_t* topk_ids, float* topk_weights, void* stream) {
+  if (!logits || !topk_ids || !topk_weights)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "route_topk: NULL buffer");
+  if (T < 1 || E < 1 || E > 32 * kRouteMaxPerLane || k < 1 || k > E)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "route_topk: bad sizes T=%d E=%d k=%d (E <= %d, k <= E)", T,
+                     E, k, 32 * kRouteMaxPerLane);
+  const int blocks = (T + 7) / 8;
+  moe_route_topk_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(logits, T, E, k, topk_ids,
+                                                                                 topk_weights);
+  FLYB200_CUDA_CHECK(cudaGetLastError());
+  return FLYB200_OK;
+}
 
 extern "C" int flyb200_moe_sort(const int32_t* topk_ids, const float* topk_weights, int32_t T,
                                 int32_t k, int32_t E, int32_t block_m, const int32_t* expert_mask,

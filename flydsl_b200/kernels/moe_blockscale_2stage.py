@@ -58,6 +58,19 @@ class MoeGemm1Launcher:
             int(size_expert_ids), self.experts, self.topk, self.tile_m, self.doweight,
             self.out_code, self._cfg_ref, _lib.stream_handle(stream)))
 
+    def quantized(self, out_q, out_scale_t, x, w, scale_x, scale_w, sorted_token_ids, expert_ids,
+                  sorted_weights, max_token_ids, tokens, size_expert_ids, stream=None):
+        """Stage 1 with the 1x128 re-quantisation fused into its epilogue (routing-order layouts
+        only): writes fp8 ``out_q [rows, inter]`` and ``out_scale_t [inter/128, rows]`` -- bit for bit
+        what ``quant_1x128`` makes of the 16-bit stage-1 output -- and no 16-bit tensor at all.
+        Rows of padding positions are left untouched."""
+        _lib.check(_lib.load().flyb200_moe_gemm1_q8(
+            out_q.data_ptr(), out_scale_t.data_ptr(), x.data_ptr(), w.data_ptr(), scale_x.data_ptr(),
+            scale_w.data_ptr(), sorted_token_ids.data_ptr(), expert_ids.data_ptr(),
+            sorted_weights.data_ptr(), max_token_ids.data_ptr(), int(tokens), self.inter_dim,
+            self.model_dim, int(size_expert_ids), self.experts, self.topk, self.tile_m, self.doweight,
+            self.out_code, self._cfg_ref, _lib.stream_handle(stream)))
+
 
 class MoeGemm2Launcher:
     """``fn(out, x, w, scale_x, scale_w, sorted_token_ids, expert_ids, sorted_weights,

@@ -42,7 +42,7 @@ class BlockscaleMoE:
     def __init__(self, w1, w1_scale, w2, w2_scale, *, topk: int, tile_m: int = 128,
                  mid_dtype=torch.float16, out_dtype=torch.bfloat16, mode: str = "reduce",
                  block_n1: Optional[int] = None, block_n2: Optional[int] = None,
-                 sorted_layout: Optional[bool] = None):
+                 sorted_layout: Optional[bool] = None, fused_quant: Optional[bool] = None):
         if mode not in ("reduce", "atomic"):
             raise ValueError(f"mode must be 'reduce' or 'atomic', got {mode!r}")
         self.E, two_i, self.H = w1.shape
@@ -61,6 +61,12 @@ class BlockscaleMoE:
         # for decode-size batches (one more launch, nothing to hide), hence the default by block size.
         self.sorted_layout = (self.tile_m >= 64 and self.tile_m % 8 == 0) if sorted_layout is None \
             else bool(sorted_layout)
+        # Re-quantisation between the stages fused into the stage-1 epilogue (routing-order layouts,
+        # 256-wide stage-1 tiles): the 16-bit intermediate is never written.
+        can_fuse = self.sorted_layout and block_n1 in (None, 0, 256)
+        self.fused_quant = can_fuse if fused_quant is None else bool(fused_quant)
+        if self.fused_quant and not can_fuse:
+            raise ValueError("fused_quant needs sorted_layout and block_n1 in (None, 256)")
         common = dict(model_dim=self.H, inter_dim=self.I, experts=self.E, topk=self.topk,
                       tile_m=self.tile_m, tile_n=256, tile_k=128)
         self.gemm1 = compile_moe_blockscale_gemm1(doweight_stage1=False, out_dtype=_DT_NAME[mid_dtype],
@@ -90,9 +96,9 @@ class BlockscaleMoE:
                 if self.sorted_layout else None,
                 "xs_sorted": torch.empty((self.H // 128, L), dtype=torch.float32, device=dev)
                 if self.sorted_layout else None,
-                "out1": torch.zeros((L, self.I), dtype=self.mid_dtype, device=dev),
-                "a2_q": torch.empty((L, self.I), dtype=torch.float8_e4m3fn, device=dev),
-                "a2_s": torch.empty((self.I // 128, L), dtype=torch.float32, device=dev),
+                "out1": None if self.fused_quant else torch.zeros((L, self.I), dtype=self.mid_dtype, device=dev),
+                "a2_q": torch.zeros((L, self.I), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn),
+                "a2_s": torch.zeros((self.I // 128, L), dtype=torch.float32, device=dev),
                 "routes": torch.empty((T * self.topk, self.H), dtype=self.out_dtype, device=dev)
                 if self.mode == "reduce" else None,
             }
@@ -124,11 +130,15 @@ class BlockscaleMoE:
                 raise ValueError("routing buffers do not match this layer's experts/tile_m/topk")
             moe_gather_rows(x_q, x_scale_t, sid, npp, topk=self.topk, out=b["x_sorted"],
                             scale_out=b["xs_sorted"])
-            self.gemm1(b["out1"], b["x_sorted"], self.w1, b["xs_sorted"], self.w1_scale, sid, seid, sw,
-                       npp, T, self.I, self.H, nblk, None)
-            _lib.check(_lib.load().flyb200_quant_1x128_devrows(
-                b["out1"].data_ptr(), b["a2_q"].data_ptr(), b["a2_s"].data_ptr(), npp.data_ptr(),
-                b["rows"], self.I, mid_code, _lib.stream_handle(None)))
+            if self.fused_quant:
+                self.gemm1.quantized(b["a2_q"], b["a2_s"], b["x_sorted"], self.w1, b["xs_sorted"],
+                                     self.w1_scale, sid, seid, sw, npp, T, nblk, None)
+            else:
+                self.gemm1(b["out1"], b["x_sorted"], self.w1, b["xs_sorted"], self.w1_scale, sid, seid, sw,
+                           npp, T, self.I, self.H, nblk, None)
+                _lib.check(_lib.load().flyb200_quant_1x128_devrows(
+                    b["out1"].data_ptr(), b["a2_q"].data_ptr(), b["a2_s"].data_ptr(), npp.data_ptr(),
+                    b["rows"], self.I, mid_code, _lib.stream_handle(None)))
         else:
             self.gemm1(b["out1"], x_q, self.w1, x_scale_t, self.w1_scale, sid, seid, sw, npp, T, self.I,
                        self.H, nblk, None)
@@ -150,5 +160,5 @@ class BlockscaleMoE:
     #: kernels one forward() launches (sort, [gather], gemm1, quant, gemm2, reduce | memset+gemm2)
     @property
     def launches_per_step(self) -> int:
-        return 6 if self.sorted_layout else 5
+        return (5 if self.fused_quant else 6) if self.sorted_layout else 5
 

@@ -489,7 +489,7 @@ class LocalExpertShard:
     one partial row per received token. Rows whose expert ids are all foreign (or -1) give zeros."""
 
     def __init__(self, w1, w1_scale, w2, w2_scale, *, experts: int, topk: int, rank: int, world: int,
-                 tile_m: int = 128, mid_dtype=torch.float16, out_dtype=torch.bfloat16):
+                 tile_m: int = 128, mid_dtype=torch.float16, out_dtype=torch.bfloat16, fused_quant: bool = True):
         from .kernels import (compile_moe_blockscale_gemm1, compile_moe_blockscale_gemm2,
                               compile_moe_reduction)
 
@@ -513,6 +513,7 @@ class LocalExpertShard:
         self.reduce = compile_moe_reduction(topk=topk, model_dim=self.H, dtype_str=names[out_dtype],
                                             use_mask=True)
         self._mid_code = {torch.float16: 1, torch.bfloat16: 0}[mid_dtype]
+        self.fused_quant = bool(fused_quant)   # re-quantisation inside the stage-1 epilogue
         mask = torch.zeros(experts, dtype=torch.int32, device=w1.device)
         mask[rank * self.EL:(rank + 1) * self.EL] = 1
         self.expert_mask = mask
@@ -525,9 +526,9 @@ class LocalExpertShard:
             b = {"L": L,
                  "x_sorted": torch.empty((L, self.H), dtype=torch.float8_e4m3fn, device=dev),
                  "xs_sorted": torch.empty((self.H // 128, L), dtype=torch.float32, device=dev),
-                 "out1": torch.zeros((L, self.I), dtype=self.mid_dtype, device=dev),
-                 "a2_q": torch.empty((L, self.I), dtype=torch.float8_e4m3fn, device=dev),
-                 "a2_s": torch.empty((self.I // 128, L), dtype=torch.float32, device=dev),
+                 "out1": None if self.fused_quant else torch.zeros((L, self.I), dtype=self.mid_dtype, device=dev),
+                 "a2_q": torch.zeros((L, self.I), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn),
+                 "a2_s": torch.zeros((self.I // 128, L), dtype=torch.float32, device=dev),
                  "routes": torch.empty((R * self.k, self.H), dtype=self.out_dtype, device=dev),
                  "ids": torch.empty((R, self.k), dtype=torch.int32, device=dev),
                  "w": torch.empty((R, self.k), dtype=torch.float32, device=dev),
@@ -583,11 +584,15 @@ class LocalExpertShard:
                                          block_size=self.tile_m, expert_mask=self.expert_mask)
         nblk = seid.numel()
         gather(b, sid, npp)
-        self.gemm1(b["out1"], b["x_sorted"], self.w1, b["xs_sorted"], self.w1_scale, sid, seid, sw, npp,
-                   R, self.I, self.H, nblk, None)
-        _lib.check(_lib.load().flyb200_quant_1x128_devrows(
-            b["out1"].data_ptr(), b["a2_q"].data_ptr(), b["a2_s"].data_ptr(), npp.data_ptr(), b["L"],
-            self.I, self._mid_code, _lib.stream_handle(None)))
+        if self.fused_quant:
+            self.gemm1.quantized(b["a2_q"], b["a2_s"], b["x_sorted"], self.w1, b["xs_sorted"], self.w1_scale,
+                                 sid, seid, sw, npp, R, nblk, None)
+        else:
+            self.gemm1(b["out1"], b["x_sorted"], self.w1, b["xs_sorted"], self.w1_scale, sid, seid, sw, npp,
+                       R, self.I, self.H, nblk, None)
+            _lib.check(_lib.load().flyb200_quant_1x128_devrows(
+                b["out1"].data_ptr(), b["a2_q"].data_ptr(), b["a2_s"].data_ptr(), npp.data_ptr(), b["L"],
+                self.I, self._mid_code, _lib.stream_handle(None)))
         self.gemm2(b["routes"], b["a2_q"], self.w2, b["a2_s"], self.w2_scale, sid, seid, sw, npp, R,
                    self.H, self.I, nblk, None)
         # a route counts here iff its expert lives on this rank (-1 marks an unused slot)

@@ -6,6 +6,7 @@ pertoken_quant        amax/dtype-max quantiser (torch ops) (reference: tests/uti
 quant_1x128           1x128 group quantiser, CUDA          (reference: tests/kernels/test_moe_blockscale.py:346-361)
 moe_sorting           routing sort, CUDA                   (reference: tests/kernels/test_moe_gemm.py:97-161)
 build_routing_buffers sorter wrapper                       (reference: tests/kernels/test_moe_gemm.py:223-295)
+route_topk            router top-k + softmax, CUDA         (reference: tests/kernels/test_moe_blockscale.py:228-230)
 get_topk_valid_mask   EP slot mask                         (reference: tests/kernels/test_moe_gemm.py:211-220)
 """
 from __future__ import annotations
@@ -144,6 +145,25 @@ def moe_sorting(topk_ids: torch.Tensor, topk_weights: torch.Tensor, *, num_exper
             int(block_size), mask_ptr, nlt, sorted_ids.data_ptr(), sorted_weights.data_ptr(),
             sorted_expert_ids.data_ptr(), num_post_pad.data_ptr(), _lib.stream_handle(stream)))
     return sorted_ids, sorted_weights, sorted_expert_ids, num_post_pad
+
+
+def route_topk(logits: torch.Tensor, topk: int, stream=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """CUDA router of the reference's MoE test (tests/kernels/test_moe_blockscale.py:228-230):
+    ``vals, ids = topk(logits)``; ``weights = softmax(vals)``. Returns (ids i32 [T, k], weights f32
+    [T, k]); slot order = descending score."""
+    _require_cuda(logits, "logits")
+    if logits.dim() != 2:
+        raise ValueError("route_topk expects [tokens, experts]")
+    if logits.dtype != torch.float32:
+        logits = logits.float()
+    T, E = logits.shape
+    ids = torch.empty((T, int(topk)), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, int(topk)), dtype=torch.float32, device=logits.device)
+    if T:
+        with torch.cuda.device(logits.device):
+            _lib.check(_lib.load().flyb200_moe_route_topk(logits.data_ptr(), T, E, int(topk), ids.data_ptr(),
+                                                          w.data_ptr(), _lib.stream_handle(stream)))
+    return ids, w
 
 
 def get_topk_valid_mask(topk_ids: torch.Tensor, expert_mask: Optional[torch.Tensor] = None):

@@ -83,6 +83,13 @@ int flyb200_moe_sort(const int32_t* topk_ids, const float* topk_weights, int32_t
                      int32_t num_local_tokens, int32_t* sorted_ids, float* sorted_weights,
                      int32_t* sorted_expert_ids, int32_t* num_valid_ids, void* stream);
 
+/* Router: topk_ids[t] = the k experts with the largest logits[t] in descending order (slot order),
+ * topk_weights[t] = softmax over those k values. Replaces the reference test's
+ * torch.topk + torch.softmax (tests/kernels/test_moe_blockscale.py:228-230). logits f32 [T, E],
+ * E <= 1024; ties go to the lower expert id; NaN scores are never selected. */
+int flyb200_moe_route_topk(const float* logits, int32_t T, int32_t E, int32_t k, int32_t* topk_ids,
+                           float* topk_weights, void* stream);
+
 /* MoE stage 1: gather rows by sorted id, X * W1^T (gate rows [0,I), up rows [I,2I) per expert),
  * out[(t*k+s), col] = silu(gate) * up [* route weight]. Replaces
  * launch_moe_blockscale_gemm1 (kernels/moe_blockscale_2stage.py:1165-1214; factory :74-89).
@@ -94,6 +101,20 @@ int flyb200_moe_gemm1(void* out, const void* x, const void* w_repacked, const fl
                       int32_t I, int32_t H, int32_t num_blocks, int32_t E, int32_t k,
                       int32_t tile_m, int32_t doweight, int32_t out_dtype,
                       const flyb200_gemm_cfg* cfg, void* stream);
+
+/* flyb200_moe_gemm1 with the re-quantisation between the stages fused into its epilogue: instead of
+ * the 16-bit out it writes out_q fp8 e4m3fn [rows, I] and out_scale_t f32 [I/128, rows] in routing
+ * order (rows = T*k + E*tile_m - k sorted positions) -- bit for bit what flyb200_quant_1x128 makes of
+ * the stage-1 output rounded to mid_dtype (F16|BF16), i.e. the reference's host re-quantisation
+ * (tests/kernels/test_moe_blockscale.py:346-361) without the intermediate tensor. Needs cfg.path
+ * bits 0 and 1 (routing-order input and output); uses 256-wide tiles (128 output columns = one scale
+ * group per row). Rows of padding positions are not written. */
+int flyb200_moe_gemm1_q8(void* out_q, float* out_scale_t, const void* x, const void* w_repacked,
+                         const float* scale_x, const float* scale_w, const int32_t* sorted_ids,
+                         const int32_t* expert_ids, const float* sorted_weights,
+                         const int32_t* num_valid_ids, int32_t T, int32_t I, int32_t H,
+                         int32_t num_blocks, int32_t E, int32_t k, int32_t tile_m, int32_t doweight,
+                         int32_t mid_dtype, const flyb200_gemm_cfg* cfg, void* stream);
 
 /* MoE stage 2: gather rows (t*k+s) of a2, A2 * W2^T, [* route weight], then either atomically add
  * into out[t, col] (accumulate != 0; caller zeroes out) or store to out[(t*k+s), col]. Replaces

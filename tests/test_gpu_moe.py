@@ -225,6 +225,55 @@ def test_sorted_layout_matches_gathered_layout():
     assert torch.equal(ss[:, :n].cpu().t().contiguous(), want_s)
 
 
+@pytest.mark.parametrize("mid", [torch.float16, torch.bfloat16])
+def test_stage1_fused_requant_is_bit_identical_to_separate_quantiser(mid):
+    """Stage 1 with the 1x128 re-quantisation in its epilogue against stage 1 + the stand-alone
+    quantiser: same fp8 bytes and scales on every real route row, same layer output."""
+    from flydsl_b200.moe import BlockscaleMoE
+    from flydsl_b200.utils import moe_sorting
+
+    T, H, I, E, k = 200, 1024, 512, 8, 4
+    m = O.make_moe_case(T=T, H=H, I=I, E=E, topk=k, seed=31, x_std=1.0, w_std=0.05)
+    args = (m["x_q"].to(DEV), m["x_scale"].to(DEV).t().contiguous(), m["topk_ids"].to(DEV), m["topk_weights"].to(DEV))
+    got = {}
+    for fused in (False, True):
+        layer = BlockscaleMoE.from_unpacked(m["w1_q"].to(DEV), m["w1_scale"].to(DEV), m["w2_q"].to(DEV),
+                                            m["w2_scale"].to(DEV), topk=k, tile_m=64, mid_dtype=mid,
+                                            sorted_layout=True, fused_quant=fused)
+        out = layer.forward(*args)
+        b = layer._buffers(T, args[0].device)
+        got[fused] = (out.clone(), b["a2_q"].view(torch.uint8).clone(), b["a2_s"].clone())
+    torch.cuda.synchronize()
+    sid, _, _, npp = moe_sorting(args[2], args[3], num_experts=E, block_size=64)
+    n = int(npp[0])
+    real = ((sid[:n] & 0xFFFFFF) < T).cpu()
+    assert real.sum() == T * k
+    assert torch.equal(got[True][1][:n].cpu()[real], got[False][1][:n].cpu()[real])
+    assert torch.equal(got[True][2][:, :n].cpu()[:, real], got[False][2][:, :n].cpu()[:, real])
+    assert torch.equal(got[True][0], got[False][0])
+    ref, _, _, _ = O.torch_moe_two_stage_ref(m["x_q"], m["x_scale"], m["w1_q"], m["w1_scale"], m["w2_q"],
+                                             m["w2_scale"], m["topk_ids"], m["topk_weights"], I)
+    if mid == torch.float16:   # the oracle's intermediate is fp16
+        assert_close_to_oracle(got[True][0], ref, "fused re-quantisation")
+
+
+@pytest.mark.parametrize("T,E,k", [(1, 8, 2), (37, 64, 6), (512, 256, 8), (5, 1000, 33)])
+def test_router_matches_oracle(T, E, k):
+    """Router kernel against the oracle's torch.topk + softmax: same experts in the same slot order,
+    weights to fp32 rounding of the exponentials."""
+    from flydsl_b200.utils import route_topk
+
+    g = torch.Generator().manual_seed(T * 1000 + E)
+    logits = torch.randn(T, E, generator=g)
+    if E >= 64:
+        logits[:, :16] += 2.0     # hot experts, as the decode stress config biases them
+    ids_ref, w_ref = O.route_topk(logits, k)
+    ids, w = route_topk(logits.to(DEV), k)
+    assert torch.equal(ids.cpu(), ids_ref)
+    torch.testing.assert_close(w.cpu(), w_ref, rtol=2e-6, atol=1e-7)
+    torch.testing.assert_close(w.sum(1).cpu(), torch.ones(T), rtol=1e-5, atol=1e-6)
+
+
 def test_ep_plan_pack_kernel_matches_torch_logic():
     """The fused expert-parallel dispatch preparation against the device-agnostic torch functions."""
     from flydsl_b200 import parallel as P
