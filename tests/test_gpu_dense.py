@@ -133,3 +133,25 @@ def test_dense_bad_arguments_raise():
     z = torch.zeros(8 * 256, dtype=torch.uint8, device="cuda")
     with pytest.raises(ValueError):  # misaligned output pointer is rejected by the C ABI, nothing launches
         fn(z[1:], z, z, z.view(torch.float32), z.view(torch.float32), 8, 128, None)
+
+
+def test_autotuner_picks_a_valid_configuration(tmp_path):
+    """The tuner benchmarks its candidates on the GPU, caches the winner and the tuned launcher
+    still matches the oracle."""
+    from flydsl_b200.autotune import GemmAutotuner
+    from flydsl_b200.utils import shuffle_weight
+
+    DEV = torch.device("cuda")
+    M, N, K = 48, 1536, 1024
+    tuner = GemmAutotuner(cache_dir=str(tmp_path), warmup=2, rep=5)
+    cfg = tuner.tune(M, N, K)
+    assert len(tuner.timings[tuner.key(M, N, K)]) >= 4          # several candidates really ran
+    assert (tmp_path / "blockscale_gemm.json").exists()
+    d = O.make_dense_case(M, N, K, seed=5)
+    ref = O.run_torch_blockscale(d["a_q"], d["b_q"], d["a_scale"], d["b_scale"], dtype=torch.float32)
+    fn = tuner.tuned_gemm(M=M, N=N, K=K)
+    c = torch.empty((M, N), dtype=torch.bfloat16, device=DEV)
+    fn(c, d["a_q"].to(DEV), shuffle_weight(d["b_q"].to(DEV)), d["a_scale"].to(DEV).t().contiguous(),
+       d["b_scale"].to(DEV), M, N, None)
+    torch.cuda.synchronize()
+    assert_close_to_oracle(c, ref, f"tuned {cfg}")

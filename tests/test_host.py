@@ -78,3 +78,34 @@ def test_stream_handle_forms():
     assert _lib.stream_handle(1234) == 1234
     with pytest.raises(TypeError):
         _lib.stream_handle("nope")
+
+
+def test_autotuner_keys_cache_and_persistence(tmp_path):
+    """Autotuner host logic without a GPU: a fake benchmark decides, the choice is cached per
+    (device, M bucket, N, K, dtype) and survives a new tuner object through the JSON file."""
+    from flydsl_b200.autotune import Config, GemmAutotuner, default_configs, m_bucket
+
+    assert [m_bucket(m) for m in (1, 2, 3, 32, 33, 4096)] == [1, 2, 4, 32, 64, 4096]
+    calls = []
+
+    def fake_bench(call, warmup, rep):
+        return call()
+
+    def make_call(cfg):
+        if cfg.block_n == 32:
+            raise ValueError("not valid for this shape")
+        calls.append(cfg)
+        cost = {None: 5.0, 256: 2.0, 128: 3.0, 64: 4.0}[cfg.block_n]
+        return lambda: cost
+
+    t = GemmAutotuner(cache_dir=str(tmp_path), do_bench_fn=fake_bench, device_name="fake")
+    best = t.tune(4096, 7168, 2048, make_call=make_call)
+    assert best == Config(block_n=256, path="tiled")
+    n = len(calls)
+    assert t.tune(3000, 7168, 2048, make_call=make_call) == best and len(calls) == n   # same bucket: cached
+    t.tune(100, 7168, 2048, make_call=make_call)
+    assert len(calls) > n                                                              # other bucket: tuned
+    t2 = GemmAutotuner(cache_dir=str(tmp_path), do_bench_fn=fake_bench, device_name="fake")
+    assert t2.tune(4096, 7168, 2048, make_call=lambda cfg: (_ for _ in ()).throw(AssertionError)) == best
+    assert any(c.path == "decode" for c in default_configs(16, 7168, 2048))
+    assert all(c.path != "decode" for c in default_configs(4096, 7168, 2048))
