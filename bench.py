@@ -323,6 +323,40 @@ def dense_sweep(dev, peaks, quick=False):
     return rows
 
 
+def int4_sweep(dev, peaks, quick=False):
+    """Weight-only int4 x bf16 decode GEMM (N = K = 8192, M in {1, 16, 64}): cold-L2 kernel time over
+    rotating copies of the packed weights; GB/s on the algorithmic bytes (N*K/2 packed weights +
+    scales + activations + output) against the measured copy peak."""
+    from flydsl_b200.kernels import compile_int4_weight_only_gemm, pack_int4_weight
+
+    N = K = 8192
+    copies = 8                      # 8 x 34.6 MB of weights + scales > 2 x L2
+    g = torch.Generator(device=dev).manual_seed(4)
+    sets = []
+    for _ in range(copies):
+        q = torch.randint(-8, 8, (N, K), generator=g, device=dev, dtype=torch.int8)
+        sc = (torch.rand(N, K // 128, generator=g, device=dev) * 0.01 + 0.001).to(torch.bfloat16)
+        sets.append(pack_int4_weight(q, sc))
+        del q, sc
+    fn = compile_int4_weight_only_gemm(N=N, K=K)
+    rows = []
+    for M in ([16] if quick else [1, 16, 64]):
+        a = [torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16) for _ in range(copies)]
+        c = [torch.empty(M, N, dtype=torch.bfloat16, device=dev) for _ in range(copies)]
+
+        def make_call(i):
+            wq, st = sets[i]
+            return lambda: fn(c[i], a[i], wq, st, M, None)
+
+        us = time_graph_rotating(make_call, copies)
+        byts = N * K // 2 + 2 * N * (K // 128) + 2 * M * K + 2 * M * N
+        gbs = byts / us / 1e3
+        rows.append({"M": M, "N": N, "K": K, "us": round(us, 2), "gbs": round(gbs, 1),
+                     "frac_hbm_peak": round(gbs / peaks["hbm_gbs"], 4),
+                     "tflops": round(2.0 * M * N * K / us / 1e6, 1), "copies": copies})
+    return rows
+
+
 def make_moe_gpu(T, H, I, E_local, topk, dev, seed, e_lo=0):
     """Expert weights generated expert by expert on the GPU (N(0,0.02), 128x128 block-quantised,
     seed derived from the global expert id) and repacked in place into the final buffers."""
@@ -529,6 +563,7 @@ def run_ours(args):
         del w, c, a_dev, sa_dev
         if world == 1:
             out["sweep"] = dense_sweep(dev, peaks, quick=args.quick)
+            out["int4"] = int4_sweep(dev, peaks, quick=args.quick)
         out["moe"] = moe_layer_bench(rank, world, dev, peaks, quick=args.quick)
     if world > 1:
         import torch.distributed as dist

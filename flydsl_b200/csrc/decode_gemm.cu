@@ -19,6 +19,7 @@
 // products are summed in fp32 by the tensor core, then acc += partial * (sa[kb,m] * sb[n/128,kb]).
 // Reference: kernels/blockscale_preshuffle_gemm.py:161-839 (small-M tiles of its select_tile_config).
 #include "common.cuh"
+#include "cluster.cuh"
 
 namespace flyb200 {
 
@@ -37,32 +38,6 @@ struct DecodeParams {
   int kbps;                // K blocks per split
   int stages;              // ring depth used (<= kDecMaxStages)
 };
-
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::
-                   : "memory");
-}
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  return remote;
-}
-// Bulk copy from this CTA's shared memory into the shared memory of a CTA of the cluster; the bytes
-// are counted on an mbarrier of the destination CTA. (A copy engine transfer: no per-thread DSMEM
-// stores, whose throughput is a few cycles per 4-byte access.)
-__device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_cluster, uint32_t src_local,
-                                                 uint32_t bytes, uint32_t bar_cluster) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
-          "r"(dst_cluster),
-      "r"(src_local), "r"(bytes), "r"(bar_cluster)
-      : "memory");
-}
 
 #ifdef FLYB200_DBG_TRACE
 __device__ long long g_dec_trace[16];

@@ -7,3 +7,8 @@ from .moe_blockscale_2stage import (  # noqa: F401
     compile_moe_blockscale_gemm2_ex,
     compile_moe_reduction,
 )
+from .int4_gemm import (  # noqa: F401
+    compile_int4_weight_only_gemm,
+    pack_int4_weight,
+    quantize_int4_groupwise,
+)

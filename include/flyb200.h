@@ -258,6 +258,22 @@ int flyb200_ep_pull_combine(const void* const* peers, int64_t part_off, const ui
                             const int32_t* slot, void* out, int32_t T, int32_t W, int32_t H, int32_t rank,
                             int32_t dtype, void* stream);
 
+/* ---- Weight-only int4 x bf16 GEMM for decode-size M (the "dequantise, then matmul" contract; the
+ * reference has no kernel of this exact format -- nearest: the W4A16 path of
+ * kernels/moe_gemm_2stage.py:607-630 and the int4 unpack of kernels/mfma_preshuffle_pipeline.py:202-222). ---- */
+
+/* q int8 [N, K] with values in [-8, 7] and scales bf16 [N, K/128] -> wq_out uint8 [K/128][N][64]
+ * (nibble = q + 8; the eight nibbles of a 32-bit word hold K elements e0 e2 e4 e6 e1 e3 e5 e7) and
+ * scales_t_out bf16 [K/128][N]. K % 128 == 0. */
+int flyb200_int4_repack(const int8_t* q, const void* scales, int32_t N, int32_t K, void* wq_out,
+                        void* scales_t_out, void* stream);
+
+/* c bf16 [M, N] = a bf16 [M, K] * dequant(W)^T, W as produced by flyb200_int4_repack; fp32
+ * accumulation, the group scale applied per 128-K group in fp32. 1 <= M <= 64; N, K % 128 == 0.
+ * cfg (optional): split_k forces the split-K factor (cluster size, 1..8). */
+int flyb200_int4_gemm(void* c, const void* a, const void* wq, const void* scales_t, int32_t M, int32_t N,
+                      int32_t K, const flyb200_gemm_cfg* cfg, void* stream);
+
 /* Reads and clears the device error word of the current device after synchronising `stream`.
  * *code_out = 0 when no kernel reported a problem. The reference only prints GPU errors
  * (lib/Runtime/FlyRocmRuntimeWrappers.cpp:22-30); this is the status-returning equivalent. */
