@@ -4,6 +4,10 @@
 //
 //   * swap-AB like the fp8 decode kernel: the 128-row weight tile is the MMA "A" operand
 //     (accumulator lane = output column n), the tokens are the MMA "B" operand (NT = 16/32/64).
+//   * the packed weights (8 KB per 128-row x 128-K group, contiguous) are fetched by bulk copies into
+//     a ring of eight shared-memory slots that runs well ahead of the consumers: 64 KB in flight per
+//     CTA keeps the HBM queue full (prefetching one group ahead in registers was latency-bound at
+//     1.2 TB/s).
 //   * four dequantiser warps turn each packed 128-row x 128-K group (8 KB) into EXACT integer-valued
 //     bf16 (-8..7) in the 128-byte-swizzled K-major image the tensor core reads (two 64-K sub-tiles):
 //     nibble n = q + 8; (n | 0x4300) is bf16 128 + n; minus 136 gives q. Three integer/half2
@@ -30,7 +34,11 @@
 
 namespace flyb200 {
 
-constexpr int kI4Threads = 320;     // warp 0 token TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-9 dequantise
+constexpr int kI4DqWarps = 8;       // dequantiser warps (two per SM sub-partition)
+constexpr int kI4Threads = 192 + 32 * kI4DqWarps + 32;   // warp 0 token TMA, warp 1 MMA, warps 2-5 epilogue,
+                                    // warps 6-13 dequantise, warp 14 packed-weight and scale copies
+constexpr int kI4PackedSlots = 8;   // ring of packed 8 KB groups
+constexpr int kI4PackedBytes = 128 * 64;
 constexpr int kI4MaxStages = 6;
 constexpr int kI4WBytes = 2 * 128 * 128;   // two 64-K bf16 sub-tiles of 128 rows
 
@@ -68,7 +76,10 @@ struct I4Cfg {
   static constexpr int kTmemCols = NT * kAccBufs < 32 ? 32 : NT * kAccBufs;
   static constexpr int kPartialBytes = (NT + 8) * 128 * 4;   // [sender][local column][128] fp32
   static constexpr int kMiscBytes = 1024;
-  static int smem_bytes(int stages) { return stages * kStageBytes + kPartialBytes + kMiscBytes + 1024; }
+  // + the group scales of the CTA's K range: [kbps][128] bf16
+  static int smem_bytes(int stages, int kbps) {
+    return stages * kStageBytes + kI4PackedSlots * kI4PackedBytes + kPartialBytes + kbps * 256 + kMiscBytes + 1024;
+  }
 };
 
 template <int NT>
@@ -84,18 +95,24 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const Int4Params p)
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t recv_base = smem_base + stages * C::kStageBytes;
-  float* recv = reinterpret_cast<float*>(smem_al + stages * C::kStageBytes);
-  const uint32_t misc_off = stages * C::kStageBytes + C::kPartialBytes;
+  const uint32_t packed_off = stages * C::kStageBytes;                       // ring of packed groups
+  const uint32_t recv_off = packed_off + kI4PackedSlots * kI4PackedBytes;
+  const uint32_t recv_base = smem_base + recv_off;
+  float* recv = reinterpret_cast<float*>(smem_al + recv_off);
+  const uint32_t scale_off = recv_off + C::kPartialBytes;                    // [kbps][128] bf16
+  const __nv_bfloat16* sc_s = reinterpret_cast<const __nv_bfloat16*>(smem_al + scale_off);
+  const uint32_t misc_off = scale_off + static_cast<uint32_t>(p.kbps) * 256u;
   const uint32_t bar_base = smem_base + misc_off;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto done_bar = [&](uint32_t i) { return bar_base + 8u * (kI4MaxStages + i); };               // < 6 + 8
   auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kI4MaxStages + 8 + b); };
   const uint32_t recv_bar = bar_base + 8u * (2 * kI4MaxStages + 16);
-  volatile uint32_t* tmem_slot =
-      reinterpret_cast<volatile uint32_t*>(smem_al + misc_off + 8 * (2 * kI4MaxStages + 17));
-  volatile int* abort_flag =
-      reinterpret_cast<volatile int*>(smem_al + misc_off + 8 * (2 * kI4MaxStages + 17) + 4);
+  auto pk_full_bar = [&](int s) { return bar_base + 8u * (2 * kI4MaxStages + 17 + s); };
+  auto pk_empty_bar = [&](int s) { return bar_base + 8u * (2 * kI4MaxStages + 17 + kI4PackedSlots + s); };
+  const uint32_t scale_bar = bar_base + 8u * (2 * kI4MaxStages + 17 + 2 * kI4PackedSlots);
+  constexpr int kBars = 2 * kI4MaxStages + 18 + 2 * kI4PackedSlots;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_al + misc_off + 8 * kBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_al + misc_off + 8 * kBars + 4);
 
   const int split = static_cast<int>(cluster_ctarank());
   const int n_tile = blockIdx.x / p.splits;
@@ -107,11 +124,16 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const Int4Params p)
 
   if (warp == 0) {
     // operands of a stage: the token TMA (one arrival + bytes) and the four dequantiser warps
-    if (lane < stages) mbar_init(full_bar(lane), 5);
+    if (lane < stages) mbar_init(full_bar(lane), 1 + kI4DqWarps);
     if (lane < kDone) mbar_init(done_bar(lane), 1);
     if (lane < kAccBufs) mbar_init(tempty_bar(lane), 4);
+    if (lane < kI4PackedSlots) {
+      mbar_init(pk_full_bar(lane), 1);
+      mbar_init(pk_empty_bar(lane), kI4DqWarps);   // one arrival per dequantiser warp
+    }
     if (lane == 0) {
       mbar_init(recv_bar, 1);
+      mbar_init(scale_bar, 1);
       *abort_flag = 0;
       prefetch_tensormap(&tmap_x);
     }
@@ -179,29 +201,56 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const Int4Params p)
         tc_commit(done_bar(i % kDone));
       }
     }
+  } else if (warp == 6 + kI4DqWarps) {
+    if (lane == 0) {
+      // ---------------- group scales of the whole K range (256 bytes per group), all in flight at
+      // once: read one by one in the promotion loop they cost a DRAM latency per group ----------------
+      if (count > 0) {
+        mbar_arrive_expect_tx(scale_bar, static_cast<uint32_t>(count) * 256u);
+        for (int i = 0; i < count; ++i)
+          bulk_load(smem_base + scale_off + i * 256,
+                    p.scales_t + static_cast<size_t>(kb_begin + i) * p.N + n0, 256, scale_bar);
+      }
+      // ---------------- packed weights: bulk copies, up to eight groups ahead ----------------
+      for (int i = 0; i < count; ++i) {
+        const int ps = i % kI4PackedSlots;
+        if (i >= kI4PackedSlots &&
+            !mbar_wait(pk_empty_bar(ps), ((i / kI4PackedSlots) & 1) ^ 1, abort_flag, p.err, kErrWaitSmemEmpty))
+          break;
+        mbar_arrive_expect_tx(pk_full_bar(ps), kI4PackedBytes);
+        bulk_load(smem_base + packed_off + ps * kI4PackedBytes,
+                  p.wq + (static_cast<size_t>(kb_begin + i) * p.N + n0) * 64, kI4PackedBytes, pk_full_bar(ps));
+      }
+    }
   } else if (warp >= 6) {
     // ---------------- dequantiser: packed int4 -> integer-valued bf16, swizzled K-major ----------
     // The group's packed tile is 512 16-byte vectors (row = v / 4, K quarter = v % 4); thread t takes
-    // vectors t, t+128, t+256, t+384, so that every load instruction of a warp reads 512 contiguous
-    // bytes. One vector = 32 weights = four 16-byte chunks of the bf16 image.
-    const int dt = threadIdx.x - 192;   // 0..127
-    auto load_group = [&](int i, uint4 (&v)[4]) {
-      const uint4* src = reinterpret_cast<const uint4*>(
-          p.wq + (static_cast<size_t>(kb_begin + i) * p.N + n0) * 64);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) v[j] = __ldg(src + j * 128 + dt);
-    };
-    uint4 cur[4], nxt[4];
-    if (count > 0) load_group(0, cur);
+    // vectors t, t+256 (eight warps) of the shared-memory slot (conflict-free: a warp reads 512
+    // contiguous bytes per instruction). One vector = 32 weights = four 16-byte chunks of the bf16 image.
+    constexpr int kDqThreads = 32 * kI4DqWarps;
+    constexpr int kVecs = 512 / kDqThreads;          // 16-byte vectors per thread per group
+    const int dt = threadIdx.x - 192;   // 0..kDqThreads-1
     for (int i = 0; i < count; ++i) {
-      if (i + 1 < count) load_group(i + 1, nxt);
+      const int ps = i % kI4PackedSlots;
+      const bool have = mbar_wait(pk_full_bar(ps), (i / kI4PackedSlots) & 1, abort_flag, p.err, kErrWaitSmemFull);
+      if (!__all_sync(0xffffffffu, have)) break;
+      uint4 cur[kVecs];
+      const uint32_t pk = smem_base + packed_off + ps * kI4PackedBytes + dt * 16;
+#pragma unroll
+      for (int j = 0; j < kVecs; ++j)
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(cur[j].x), "=r"(cur[j].y), "=r"(cur[j].z), "=r"(cur[j].w)
+                     : "r"(pk + j * (kDqThreads * 16))
+                     : "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pk_empty_bar(ps));   // the slot may be refilled
       const int s = i % stages;
       const bool ok = wait_stage_free(i, kErrWaitGather);
       if (!__all_sync(0xffffffffu, ok)) break;
       const uint32_t sw = smem_base + s * C::kStageBytes;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int vec = j * 128 + dt;
+      for (int j = 0; j < kVecs; ++j) {
+        const int vec = j * kDqThreads + dt;
         const int r = vec >> 2, part = vec & 3;
         const uint32_t row_base = sw + (part >> 1) * (128 * 128) + r * 128;
         const uint32_t w[4] = {cur[j].x, cur[j].y, cur[j].z, cur[j].w};
@@ -226,8 +275,6 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const Int4Params p)
       fence_proxy_async_smem();   // generic-proxy writes -> visible to the tensor core's reads
       __syncwarp();
       if (lane == 0) mbar_arrive(full_bar(s));
-#pragma unroll
-      for (int j = 0; j < 4; ++j) cur[j] = nxt[j];
     }
   } else {
     // ---------------- epilogue: thread = output column n (accumulator lane) ----------------
@@ -235,15 +282,16 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const Int4Params p)
     const int quad = warp & 3;                  // TMEM lane quadrant this warp may read
     const int n_loc = quad * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-    const __nv_bfloat16* sc = p.scales_t + n0 + n_loc;
     float acc[NT];
 #pragma unroll
     for (int j = 0; j < NT; ++j) acc[j] = 0.f;
     bool alive = true;
-    float s_next = count > 0 ? __bfloat162float(sc[static_cast<size_t>(kb_begin) * p.N]) : 0.f;
+    if (count > 0) {
+      const bool have = mbar_wait(scale_bar, 0, abort_flag, p.err, kErrWaitSmemFull);
+      alive = __all_sync(0xffffffffu, have);
+    }
     for (int i = 0; i < count && alive; ++i) {
-      const float sg = s_next;
-      if (i + 1 < count) s_next = __bfloat162float(sc[static_cast<size_t>(kb_begin + i + 1) * p.N]);
+      const float sg = __bfloat162float(sc_s[i * 128 + n_loc]);
       const int buf = i % kAccBufs;
       const bool got = mbar_wait(done_bar(i % kDone), (i / kDone) & 1, abort_flag, p.err, kErrWaitTmemFull);
       if (!__all_sync(0xffffffffu, got)) {
@@ -373,7 +421,7 @@ static I4Plan plan_int4(int M, int N, int K, int sms, int force_splits) {
     if (s_eff != s && force_splits <= 0) continue;
     int stages = kbps < kI4MaxStages ? kbps : kI4MaxStages;
     if (stages < 2) stages = 2;   // the stage area doubles as the send buffer of the exchange
-    const int fixed = (nt + 8) * 512 + 2048;
+    const int fixed = (nt + 8) * 512 + 2048 + kI4PackedSlots * kI4PackedBytes + kbps * 256;
     while (stages > 2 && stages * stage_bytes + fixed > 232448) --stages;
     if (stages * stage_bytes + fixed > 232448) continue;
     const long ctas = static_cast<long>(n_tiles) * s_eff;
@@ -391,7 +439,7 @@ static I4Plan plan_int4(int M, int N, int K, int sms, int force_splits) {
 template <int NT>
 static int launch_int4(const CUtensorMap& tmap, const Int4Params& p, cudaStream_t stream) {
   auto kern = int4_gemm_kernel<NT>;
-  const int smem = I4Cfg<NT>::smem_bytes(p.stages);
+  const int smem = I4Cfg<NT>::smem_bytes(p.stages, p.kbps);
   if (smem > 232448) return set_error(FLYB200_ERR_UNSUPPORTED, "int4 plan needs %d bytes of shared memory", smem);
   static thread_local int configured_dev = -1;
   int dev = 0;
