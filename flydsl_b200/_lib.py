@@ -71,6 +71,7 @@ SIGNATURES = {
     "flyb200_ep_barrier": (c_int, [c_void_p, c_int32, c_int32, c_int64, c_uint32, c_int32, c_void_p]),
     "flyb200_ep_push": (c_int, [c_void_p] * 4 + [c_int32] * 6 + [c_void_p, c_int64] + [c_void_p] * 4),
     "flyb200_ep_pull_combine": (c_int, [c_void_p, c_int64] + [c_void_p] * 3 + [c_int32] * 5 + [c_void_p]),
+    "flyb200_ep_reduce_push": (c_int, [c_void_p, c_void_p, c_void_p, c_int64] + [c_int32] * 6 + [c_void_p]),
     "flyb200_int4_repack": (c_int, [c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
     "flyb200_int4_gemm": (c_int, [c_void_p] * 4 + [c_int32] * 3 + [POINTER(GemmCfg), c_void_p]),
     "flyb200_query_device_error": (c_int, [c_void_p, POINTER(c_int32)]),

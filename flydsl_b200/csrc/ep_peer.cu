@@ -6,11 +6,13 @@
 //   plan + push    each source rank writes its token rows STRAIGHT into the destination's receive
 //                  area (plain 16-byte peer stores); only rows that are needed travel
 //   barrier        flag exchange, bounded spin
-//   local experts  sort / gather / two GEMM stages / top-k reduce on local memory, partial rows
-//                  written into this rank's partial area
+//   local experts  sort / gather / two GEMM stages on local memory; the top-k reduce writes each
+//                  partial row straight into the back area of the rank that owns the token (peer
+//                  stores, issued as soon as this rank is done)
 //   barrier
-//   pull + sum     each source rank reads the partial rows of its tokens from the ranks that own
-//                  its experts (peer loads) and adds them in rank order, fp32
+//   sum            each source rank adds its tokens' partial rows from its own back area in rank
+//                  order, fp32 (flyb200_ep_combine)
+//   (variant: partial rows stay local and the source ranks pull them, flyb200_ep_pull_combine)
 //
 // so there is no packed send buffer, no receive-side copy and no gathered intermediate, and only the
 // rows that are needed cross NVLink. Loads and stores to peer memory are ordinary ld/st; nothing here
@@ -132,6 +134,48 @@ ep_pull_kernel(PeerPtrs peers, long long part_off, const uint8_t* __restrict__ n
   }
 }
 
+// Top-k reduce of the local experts' route rows, written STRAIGHT into the memory of the rank that
+// owns the token: row i of this rank's received rows came from source rank i / T, slot i % T; its
+// partial sum (the valid routes in slot order, fp32 -- the arithmetic of the masked moe_reduce
+// kernel) goes to that rank's back area at row rank*T + slot. Rows without a local route are not
+// sent. The source rank then sums its back area locally (flyb200_ep_combine), so the only NVLink
+// traffic of the combine is this kernel's stores, issued as soon as a rank finishes its experts.
+template <typename T_>
+__global__ void __launch_bounds__(256)
+ep_reduce_push_kernel(const T_* __restrict__ routes, const uint8_t* __restrict__ valid, PeerPtrs peers,
+                      long long back_off, int R, int T, int k, int H, int rank) {
+  constexpr int VEC = 16 / sizeof(T_);
+  const int vec_per_row = H / VEC;
+  const long long total = static_cast<long long>(R) * vec_per_row;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int i = static_cast<int>(idx / vec_per_row);
+    const int v = static_cast<int>(idx - static_cast<long long>(i) * vec_per_row);
+    float acc[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+    bool any = false;
+    for (int s = 0; s < k; ++s) {
+      if (valid[i * k + s] == 0) continue;
+      any = true;
+      const uint4 raw = *reinterpret_cast<const uint4*>(
+          routes + (static_cast<long long>(i) * k + s) * H + static_cast<long long>(v) * VEC);
+      const T_* e = reinterpret_cast<const T_*>(&raw);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) acc[j] += static_cast<float>(e[j]);
+    }
+    if (!any) continue;
+    uint4 o;
+    T_* po = reinterpret_cast<T_*>(&o);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) po[j] = static_cast<T_>(acc[j]);
+    const int src = i / T, slot = i - src * T;
+    T_* dst = reinterpret_cast<T_*>(peers.p[src] + back_off) +
+              (static_cast<long long>(rank) * T + slot) * H + static_cast<long long>(v) * VEC;
+    *reinterpret_cast<uint4*>(dst) = o;
+  }
+}
+
 static bool load_peers(const void* const* peers, int W, PeerPtrs& pp) {
   if (!peers || W < 1 || W > kMaxPeers) return false;
   for (int i = 0; i < kMaxPeers; ++i) pp.p[i] = nullptr;
@@ -250,6 +294,33 @@ extern "C" int flyb200_ep_pull_combine(const void* const* peers, int64_t part_of
   else
     ep_pull_kernel<__half><<<static_cast<int>(blocks), 256, 0, st>>>(
         pp, part_off, need, slot, static_cast<__half*>(out), T, W, H, rank);
+  FLYB200_CUDA_CHECK(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+extern "C" int flyb200_ep_reduce_push(const void* routes, const uint8_t* valid, const void* const* peers,
+                                      int64_t back_off, int32_t T, int32_t W, int32_t k, int32_t H,
+                                      int32_t rank, int32_t dtype, void* stream) {
+  PeerPtrs pp;
+  if (!routes || !valid || !load_peers(peers, W, pp))
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_reduce_push: NULL buffer or more than %d ranks", kMaxPeers);
+  if (reinterpret_cast<uintptr_t>(routes) % 16 || back_off < 0 || back_off % 16)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_reduce_push: buffers must be 16-byte aligned");
+  if (T < 1 || k < 1 || H < 8 || H % 8 || rank < 0 || rank >= W || (dtype != FLYB200_BF16 && dtype != FLYB200_F16))
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_reduce_push: bad sizes or dtype");
+  const int sms = sm_count();
+  if (sms <= 0) return FLYB200_ERR_CUDA;
+  const int R = W * T;
+  const long long total = static_cast<long long>(R) * (H / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > static_cast<long long>(sms) * 16) blocks = static_cast<long long>(sms) * 16;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == FLYB200_BF16)
+    ep_reduce_push_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(routes), valid, pp, back_off, R, T, k, H, rank);
+  else
+    ep_reduce_push_kernel<__half><<<static_cast<int>(blocks), 256, 0, st>>>(
+        static_cast<const __half*>(routes), valid, pp, back_off, R, T, k, H, rank);
   FLYB200_CUDA_CHECK(cudaGetLastError());
   return FLYB200_OK;
 }

@@ -259,6 +259,7 @@ class ExpertParallelMoE:
         self.exchange = exchange
         self.trace = False
         self.peer = None     # PeerExchange, created on the first "peer" step (needs T)
+        self.peer_combine = "push"   # "push": owners receive partial rows; "pull": they fetch them
 
     def forward(self, x_q, x_scale, topk_ids, topk_weights):
         """x_q fp8/uint8 [T, H]; x_scale f32 [T, H/128] (token-major); ids [T, k]; weights [T, k]."""
@@ -410,6 +411,25 @@ class PeerExchange:
             slot.data_ptr(), src.data_ptr(), _lib.stream_handle(None)))
         return need, slot
 
+    def reduce_push(self, routes, valid, dtype):
+        """Masked top-k reduce of this rank's route rows, written into the owners' back areas (the
+        partial area of every buffer doubles as its back area)."""
+        from . import _lib
+
+        _lib.check(self._lib.flyb200_ep_reduce_push(
+            routes.data_ptr(), valid.data_ptr(), self.peers, self.part_off, self.T, self.world, self.k,
+            self.H, self.rank, _lib.BF16 if dtype == torch.bfloat16 else _lib.F16, _lib.stream_handle(None)))
+
+    def combine_local(self, need, slot, dtype):
+        """Sum of this rank's tokens over the rows that the owners pushed into the own back area."""
+        from . import _lib
+
+        out = torch.empty((self.T, self.H), dtype=dtype, device=need.device)
+        _lib.check(self._lib.flyb200_ep_combine(
+            self.own + self.part_off, need.data_ptr(), slot.data_ptr(), out.data_ptr(), self.T, self.world,
+            self.H, _lib.BF16 if dtype == torch.bfloat16 else _lib.F16, _lib.stream_handle(None)))
+        return out
+
     def pull_combine(self, need, slot, dtype):
         from . import _lib
 
@@ -466,12 +486,22 @@ def _forward_peer(self, x_u8, x_scale, topk_ids, topk_weights):
     mark("plan+push")
     px.barrier()                                   # every rank's rows have landed here
     mark("barrier")
-    self.local_fn.forward_packed(px.recv, out=px.partial(self.out_dtype))
-    mark("local experts")
-    px.barrier()                                   # every rank's partial rows are complete
-    mark("barrier 2")
-    out = px.pull_combine(need, slot, self.out_dtype)
-    mark("pull+sum")
+    if self.peer_combine == "push":
+        # the top-k reduce stores each partial row straight into the owner's back area
+        self.local_fn.forward_packed(
+            px.recv, reducer=lambda routes, valid: px.reduce_push(routes, valid, self.out_dtype))
+        mark("local experts+push")
+        px.barrier()                               # every rank's partial rows have landed here
+        mark("barrier 2")
+        out = px.combine_local(need, slot, self.out_dtype)
+        mark("sum")
+    else:
+        self.local_fn.forward_packed(px.recv, out=px.partial(self.out_dtype))
+        mark("local experts")
+        px.barrier()                               # every rank's partial rows are complete
+        mark("barrier 2")
+        out = px.pull_combine(need, slot, self.out_dtype)
+        mark("pull+sum")
     self.last_stats = {"sent_rows": None, "recv_rows": self.world * T, "exchange": "peer"}
     if marks:
         torch.cuda.synchronize()
@@ -551,10 +581,11 @@ class LocalExpertShard:
 
         return self._run(R, x_q_u8.device, topk_ids, topk_weights, gather, None)
 
-    def forward_packed(self, rows, out=None):
+    def forward_packed(self, rows, out=None, reducer=None):
         """Same as calling the shard on ``unpack_rows(rows)``, but the packed rows
         ``[R, H + 4*H/128 + 8*k]`` (uint8) are read in place: only ids and weights are sliced out,
-        activations and scales go straight into routing order."""
+        activations and scales go straight into routing order. ``reducer(routes [R*k, H], valid
+        [R, k])`` replaces the final masked top-k reduce (nothing is returned then)."""
         from . import _lib
 
         R = rows.shape[0]
@@ -573,9 +604,9 @@ class LocalExpertShard:
                 rows.data_ptr(), sid.data_ptr(), npp.data_ptr(), b["x_sorted"].data_ptr(),
                 b["xs_sorted"].data_ptr(), R, H, k, b["L"], _lib.stream_handle(None)))
 
-        return self._run(R, rows.device, ids, w, gather, out, valid)
+        return self._run(R, rows.device, ids, w, gather, out, valid, reducer)
 
-    def _run(self, R, dev, topk_ids, topk_weights, gather, out, valid=None):
+    def _run(self, R, dev, topk_ids, topk_weights, gather, out, valid=None, reducer=None):
         from . import _lib
         from .utils import moe_sorting
 
@@ -598,6 +629,9 @@ class LocalExpertShard:
         # a route counts here iff its expert lives on this rank (-1 marks an unused slot)
         if valid is None:
             valid = (torch.div(topk_ids, self.EL, rounding_mode="floor") == self.rank).to(torch.uint8)
+        if reducer is not None:            # e.g. PeerExchange.reduce_push: rows leave this GPU
+            reducer(b["routes"], valid)
+            return None
         if out is None:
             out = b["out"]
         self.reduce(b["routes"], out, valid, R, None)

@@ -274,6 +274,15 @@ int flyb200_int4_repack(const int8_t* q, const void* scales, int32_t N, int32_t 
 int flyb200_int4_gemm(void* c, const void* a, const void* wq, const void* scales_t, int32_t M, int32_t N,
                       int32_t K, const flyb200_gemm_cfg* cfg, void* stream);
 
+/* Masked top-k reduce of the local experts' route rows (the arithmetic of flyb200_moe_reduce with a
+ * valid_mask) whose result rows go straight into the owners' memory: row i of routes' [W*T, k, H]
+ * belongs to source rank i / T, slot i % T and is stored at row rank*T + slot of that rank's back area
+ * (back_off in its buffer, [W*T, H]). Rows without a valid route are not sent. The owner then calls
+ * flyb200_ep_combine on its own back area. */
+int flyb200_ep_reduce_push(const void* routes, const uint8_t* valid, const void* const* peers,
+                           int64_t back_off, int32_t T, int32_t W, int32_t k, int32_t H, int32_t rank,
+                           int32_t dtype, void* stream);
+
 /* Reads and clears the device error word of the current device after synchronising `stream`.
  * *code_out = 0 when no kernel reported a problem. The reference only prints GPU errors
  * (lib/Runtime/FlyRocmRuntimeWrappers.cpp:22-30); this is the status-returning equivalent. */

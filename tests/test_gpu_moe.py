@@ -368,6 +368,19 @@ def test_ep_peer_kernels_two_ranks_emulated_on_one_gpu():
             assert torch.equal(P.combine_partials_fixed(back, need, slot, torch.bfloat16), out)
             assert torch.equal(P.combine_partials_fixed(back.cpu(), need.cpu(), slot.cpu(), torch.bfloat16), out.cpu())
             outs.append(out.float().cpu())
+        # push variant: the reduce writes each partial row into the owner's back area (= partial
+        # area, free again by now), the owner sums its own memory -- same bits as the pull variant
+        for r in range(W):
+            recv = views[r][: W * T * row_bytes].view(W * T, row_bytes)
+            shards[r].forward_packed(recv, reducer=lambda routes, valid, r=r: _lib.check(
+                lib.flyb200_ep_reduce_push(routes.data_ptr(), valid.data_ptr(), peers, part_off, T, W, k, H, r,
+                                           _lib.BF16, _lib.stream_handle(None))))
+        for r in range(W):
+            need, slot = plans[r]
+            out = torch.empty((T, H), dtype=torch.bfloat16, device=DEV)
+            _lib.check(lib.flyb200_ep_combine(bufs[r] + part_off, need.data_ptr(), slot.data_ptr(), out.data_ptr(),
+                                              T, W, H, _lib.BF16, _lib.stream_handle(None)))
+            assert torch.equal(out.float().cpu(), outs[r])
         torch.cuda.synchronize()
         assert _lib.query_device_error() == 0
         assert_close_to_oracle(torch.cat(outs, dim=0), ref, "peer exchange, two ranks emulated")

@@ -52,10 +52,12 @@ def _worker(rank, world, port, dense, moe, ret):
                                             exchange=mode)
             outs[mode] = ep.forward(*args).float().cpu()
             if mode == "peer":
-                # a second and third step reuse the exchange areas and the barrier flags
-                for _ in range(2):
+                # further steps reuse the exchange areas and the barrier flags; both combine variants
+                # (partial rows pushed to the owner / pulled by the owner) give the same bits
+                for variant in ("push", "pull", "push"):
+                    ep.peer_combine = variant
                     again = ep.forward(*args).float().cpu()
-                    assert torch.equal(again, outs[mode])
+                    assert torch.equal(again, outs[mode]), variant
                 ep.peer.close()
             torch.cuda.synchronize()
             assert _lib.query_device_error() == 0
