@@ -198,10 +198,25 @@ struct TileWalker {
     }
     total = num_m * num_n;
   }
-  // tile -> (m block, n tile); consecutive CTAs share the weight tile and differ in rows.
+  // tile -> (m block, n tile). Dense: consecutive CTAs share the weight tile and differ in rows.
+  // MoE: every row block has its own expert's weights, so that order shares nothing and re-reads
+  // the whole routing-ordered activation tensor once per column tile (350 MB at 4096 tokens x top-8,
+  // more than L2); instead consecutive CTAs take the column tiles of ONE row block: its activation
+  // tile is fetched once and shared through L2, and the second row block of an expert follows its
+  // first closely enough to find the expert's weights (29 MB) still in L2.
+#ifdef FLYB200_MOE_N_MAJOR
+  static constexpr bool kRowBlockMajor = false;
+#else
+  static constexpr bool kRowBlockMajor = (MODE != kDense);
+#endif
   __device__ __forceinline__ void decode(int tile, int& m_blk, int& n_tile) const {
-    n_tile = tile / num_m;
-    m_blk = tile - n_tile * num_m;
+    if constexpr (kRowBlockMajor) {
+      m_blk = tile / num_n;
+      n_tile = tile - m_blk * num_n;
+    } else {
+      n_tile = tile / num_m;
+      m_blk = tile - n_tile * num_m;
+    }
   }
 };
 

@@ -6,30 +6,39 @@
 //
 // Every CTA rebuilds the full per-expert histogram (the id array is at most a few hundred KB and
 // comes from L2), scans the padded counts to find its own base offset, then compacts its expert's
-// routes in order. Both passes over the ids give every thread 32 CONSECUTIVE ids, fetched as eight
-// 16-byte loads that are all in flight at once (the passes are latency-bound otherwise); a thread
-// counts its matches, one block-level prefix turns the counts into positions, and the thread writes
-// its matches in order.
+// routes in order. Both passes over the ids work in rounds of 32 768 ids: a warp takes 1 024
+// consecutive ids as eight fully coalesced 16-byte loads per lane, all in flight at once (the passes
+// are latency-bound otherwise); a lane holds ids (j*32 + lane)*4 .. +3 of the warp's span for
+// j = 0..7. Positions follow the global id order (warp, j, lane, element): per-j warp prefix sums
+// (packed four to a register), one block-level prefix over the warps, then each lane writes its
+// matches.
 #include "common.cuh"
 
 namespace flyb200 {
 
 constexpr int kSortThreads = 1024;
-constexpr int kChunk = 32;  // consecutive ids per thread per round
+constexpr int kChunk = 32;                       // ids per thread per round (eight 16-byte loads)
+constexpr int kWarpSpan = 32 * kChunk;           // consecutive ids a warp covers per round
 
-// ids[i0 .. i0 + kChunk) into registers; -1 (matches no expert) beyond n.
-__device__ __forceinline__ void load_chunk(const int* __restrict__ ids, int i0, int n, bool vec_ok,
-                                           int (&v)[kChunk]) {
-  if (vec_ok && i0 + kChunk <= n) {
-    const int4* p4 = reinterpret_cast<const int4*>(ids + i0);
+// Element q of group j of this lane = ids[warp_base + (j*32 + lane)*4 + q]; -1 (matches no expert)
+// beyond n.
+__device__ __forceinline__ void load_chunk(const int* __restrict__ ids, int warp_base, int lane, int n,
+                                           bool vec_ok, int (&v)[kChunk]) {
+  if (vec_ok && warp_base + kWarpSpan <= n) {
+    const int4* p4 = reinterpret_cast<const int4*>(ids + warp_base);
 #pragma unroll
     for (int j = 0; j < kChunk / 4; ++j) {
-      const int4 q = __ldg(p4 + j);
+      const int4 q = __ldg(p4 + j * 32 + lane);
       v[4 * j] = q.x; v[4 * j + 1] = q.y; v[4 * j + 2] = q.z; v[4 * j + 3] = q.w;
     }
   } else {
 #pragma unroll
-    for (int j = 0; j < kChunk; ++j) v[j] = (i0 + j < n) ? __ldg(ids + i0 + j) : -1;
+    for (int j = 0; j < kChunk / 4; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int i = warp_base + (j * 32 + lane) * 4 + q;
+        v[4 * j + q] = (i < n) ? __ldg(ids + i) : -1;
+      }
   }
 }
 
@@ -74,7 +83,7 @@ moe_sort_kernel(const SortParams p) {
   const bool vec_ok = (reinterpret_cast<uintptr_t>(p.topk_ids) & 15) == 0;
   for (int r0 = 0; r0 < n; r0 += kSortThreads * kChunk) {
     int v[kChunk];
-    load_chunk(p.topk_ids, r0 + tid * kChunk, n, vec_ok, v);
+    load_chunk(p.topk_ids, r0 + warp * kWarpSpan, lane, n, vec_ok, v);
 #pragma unroll
     for (int j = 0; j < kChunk; ++j)
       if (v[j] >= 0 && v[j] < p.E) atomicAdd(&hist[v[j]], 1);
@@ -137,22 +146,35 @@ moe_sort_kernel(const SortParams p) {
   const int my_cnt = hist[e];
   const int my_padded = ((my_cnt + p.block_m - 1) / p.block_m) * p.block_m;
 
-  // Ordered compaction: thread t of round r owns routes [r0 + t*kChunk, r0 + (t+1)*kChunk).
+  // Ordered compaction.
   int running = my_base;
   for (int r0 = 0; r0 < n; r0 += kSortThreads * kChunk) {
     int v[kChunk];
-    const int i0 = r0 + tid * kChunk;
-    load_chunk(p.topk_ids, i0, n, vec_ok, v);
-    int cnt = 0;
+    const int warp_base = r0 + warp * kWarpSpan;
+    load_chunk(p.topk_ids, warp_base, lane, n, vec_ok, v);
+    // matches per group j (0..4), four groups to a register, 8 bits each (a warp-wide inclusive sum
+    // is at most 128)
+    unsigned cnt[2] = {0u, 0u};
 #pragma unroll
-    for (int j = 0; j < kChunk; ++j) cnt += (v[j] == e) ? 1 : 0;
-    int incl = cnt;
+    for (int j = 0; j < kChunk / 4; ++j) {
+      int c = 0;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) c += (v[4 * j + q] == e) ? 1 : 0;
+      cnt[j >> 2] |= static_cast<unsigned>(c) << (8 * (j & 3));
+    }
+    unsigned incl[2] = {cnt[0], cnt[1]};
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const int up = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += up;
+      const unsigned u0 = __shfl_up_sync(0xffffffffu, incl[0], o);
+      const unsigned u1 = __shfl_up_sync(0xffffffffu, incl[1], o);
+      if (lane >= o) { incl[0] += u0; incl[1] += u1; }
     }
-    if (lane == 31) warp_cnt[warp] = incl;
+    const unsigned tot0 = __shfl_sync(0xffffffffu, incl[0], 31);   // per-group totals of the warp
+    const unsigned tot1 = __shfl_sync(0xffffffffu, incl[1], 31);
+    int warp_total = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) warp_total += ((tot0 >> (8 * j)) & 0xFF) + ((tot1 >> (8 * j)) & 0xFF);
+    if (lane == 0) warp_cnt[warp] = warp_total;
     __syncthreads();
     int before = 0, all = 0;
     for (int w = 0; w < kSortThreads / 32; ++w) {
@@ -160,18 +182,28 @@ moe_sort_kernel(const SortParams p) {
       before += (w < warp) ? c : 0;
       all += c;
     }
-    int pos = running + before + incl - cnt;
-    if (cnt) {
+    if (warp_total) {
+      int group_base = running + before;     // first position of group j of this warp
 #pragma unroll
-      for (int j = 0; j < kChunk; ++j) {
-        if (v[j] == e) {
-          const int i = i0 + j;
-          const int t = i / p.k;
-          const int slot = i - t * p.k;
-          p.sorted_ids[pos] = (slot << 24) | t;
-          p.sorted_weights[pos] = p.topk_weights[i];
-          ++pos;
+      for (int j = 0; j < kChunk / 4; ++j) {
+        const unsigned tj = ((j < 4 ? tot0 : tot1) >> (8 * (j & 3))) & 0xFF;
+        const unsigned ij = ((j < 4 ? incl[0] : incl[1]) >> (8 * (j & 3))) & 0xFF;
+        const unsigned cj = ((j < 4 ? cnt[0] : cnt[1]) >> (8 * (j & 3))) & 0xFF;
+        if (cj) {
+          int pos = group_base + static_cast<int>(ij - cj);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if (v[4 * j + q] == e) {
+              const int i = warp_base + (j * 32 + lane) * 4 + q;
+              const int t = i / p.k;
+              const int slot = i - t * p.k;
+              p.sorted_ids[pos] = (slot << 24) | t;
+              p.sorted_weights[pos] = p.topk_weights[i];
+              ++pos;
+            }
+          }
         }
+        group_base += static_cast<int>(tj);
       }
     }
     running += all;

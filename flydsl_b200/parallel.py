@@ -519,7 +519,7 @@ class LocalExpertShard:
     one partial row per received token. Rows whose expert ids are all foreign (or -1) give zeros."""
 
     def __init__(self, w1, w1_scale, w2, w2_scale, *, experts: int, topk: int, rank: int, world: int,
-                 tile_m: int = 128, mid_dtype=torch.float16, out_dtype=torch.bfloat16, fused_quant: bool = True):
+                 tile_m: int = 128, mid_dtype=torch.float16, out_dtype=torch.bfloat16, fused_quant: bool = False):
         from .kernels import (compile_moe_blockscale_gemm1, compile_moe_blockscale_gemm2,
                               compile_moe_reduction)
 
