@@ -57,21 +57,15 @@ moe_reduce_kernel(const T* __restrict__ x, T* __restrict__ y, const uint8_t* __r
 }
 
 // 16-bit inputs: half a warp per 128-wide group (16 lanes x 16 bytes), so a warp moves 512 bytes per
-// load instruction; the amax reduction stays inside the half-warp. Returns through q / scale_t.
+// load instruction; the amax reduction stays inside the half-warp. `raw` holds the lane's 8 values.
 template <typename T>
-__device__ __forceinline__ void quant_group16(const T* __restrict__ x, uint8_t* __restrict__ q,
+__device__ __forceinline__ void quant_group16(const uint4& raw, uint8_t* __restrict__ q,
                                               float* __restrict__ scale_t, int64_t row, int g,
                                               int cols, int64_t scale_stride, bool active, int sub) {
   float v[8];
-  if (active) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(x + row * cols + g * 128 + sub * 8);
-    const T* e = reinterpret_cast<const T*>(&raw);
+  const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = to_f32<T>(e[j]);
-  } else {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = 0.f;
-  }
+  for (int j = 0; j < 8; ++j) v[j] = active ? to_f32<T>(e[j]) : 0.f;
   float vmax = -3.4e38f, vmin = 3.4e38f;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
@@ -88,34 +82,60 @@ __device__ __forceinline__ void quant_group16(const T* __restrict__ x, uint8_t* 
   float scale = __fdiv_rn(fmaxf(vmax, -vmin), 448.f);
   if (scale == 0.f) scale = 1.f;
   if (active) {
-    uint32_t lo = 0, hi = 0;
+    // v / scale, correctly rounded, from one reciprocal: q0 = v*rc, q = fma(fma(-scale, q0, v), rc, q0)
+    // is the IEEE quotient when rc is the correctly rounded reciprocal and the mantissa of scale is
+    // not all ones (Markstein); that rare scale takes the true division. Eight IEEE divisions per
+    // lane made this kernel compute-bound at a quarter of the copy bandwidth.
+    const float rc = __frcp_rn(scale);
+    const bool exact_div = (__float_as_uint(scale) & 0x7fffffu) == 0x7fffffu;
+    float qv[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      lo |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(__fdiv_rn(v[j], scale), __NV_SATFINITE, __NV_E4M3)) << (8 * j);
-      hi |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(__fdiv_rn(v[j + 4], scale), __NV_SATFINITE, __NV_E4M3)) << (8 * j);
+    for (int j = 0; j < 8; ++j) {
+      const float q0 = v[j] * rc;
+      qv[j] = exact_div ? __fdiv_rn(v[j], scale) : __fmaf_rn(__fmaf_rn(-scale, q0, v[j]), rc, q0);
     }
+    const uint32_t lo = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qv[0], qv[1]), __NV_SATFINITE, __NV_E4M3)) |
+                        (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qv[2], qv[3]), __NV_SATFINITE, __NV_E4M3)) << 16);
+    const uint32_t hi = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qv[4], qv[5]), __NV_SATFINITE, __NV_E4M3)) |
+                        (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qv[6], qv[7]), __NV_SATFINITE, __NV_E4M3)) << 16);
     *reinterpret_cast<uint2*>(q + row * cols + g * 128 + sub * 8) = make_uint2(lo, hi);
     if (sub == 0) scale_t[static_cast<int64_t>(g) * scale_stride + row] = scale;
   }
 }
 
-// rows x (cols/128) groups, two groups per warp per step (one per half-warp)
+// rows x (cols/128) groups, two groups per warp per step (one per half-warp), four steps' loads in
+// flight at once: the kernel is a dependent load -> reduce -> divide -> store chain per group and was
+// latency-bound at a quarter of the copy bandwidth with one group per thread in flight.
 template <typename T>
 __device__ __forceinline__ void quant_rows16(const T* __restrict__ x, uint8_t* __restrict__ q,
                                              float* __restrict__ scale_t, int64_t rows,
                                              int64_t scale_stride, int cols) {
+  constexpr int kInFlight = 4;
   const int groups = cols / 128;
   const int64_t total = rows * groups;
   const int lane = threadIdx.x & 31;
   const int sub = lane & 15;
   const int64_t hw0 = ((blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5) * 2 + (lane >> 4);
   const int64_t nhw = ((static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5) * 2;
-  for (int64_t w = hw0 - (lane >> 4); w < total; w += nhw) {  // warp-uniform trip count
-    const int64_t idx = w + (lane >> 4);
-    const bool active = idx < total;
-    const int64_t row = active ? idx / groups : 0;
-    const int g = active ? static_cast<int>(idx - row * groups) : 0;
-    quant_group16<T>(x, q, scale_t, row, g, cols, scale_stride, active, sub);
+  for (int64_t w = hw0 - (lane >> 4); w < total; w += nhw * kInFlight) {  // warp-uniform trip count
+    uint4 raw[kInFlight];
+    int64_t row[kInFlight];
+    int g[kInFlight];
+    bool active[kInFlight];
+#pragma unroll
+    for (int u = 0; u < kInFlight; ++u) {
+      const int64_t idx = w + u * nhw + (lane >> 4);
+      active[u] = idx < total;
+      // rows fastest: neighbouring half-warps write neighbouring entries of the transposed scales
+      g[u] = active[u] ? static_cast<int>(idx / rows) : 0;
+      row[u] = active[u] ? idx - static_cast<int64_t>(g[u]) * rows : 0;
+      raw[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (active[u]) raw[u] = *reinterpret_cast<const uint4*>(x + row[u] * cols + g[u] * 128 + sub * 8);
+    }
+#pragma unroll
+    for (int u = 0; u < kInFlight; ++u)
+      if (w + u * nhw < total)   // warp-uniform: the shuffles inside need the whole warp
+        quant_group16<T>(raw[u], q, scale_t, row[u], g[u], cols, scale_stride, active[u], sub);
   }
 }
 
