@@ -639,6 +639,31 @@ def run_probe(args):
             if i >= args.warmup:
                 times.append(e0.elapsed_time(e1))
         print(json.dumps({"probe": "moe", "experts": E, "tokens": T, "ms": statistics.median(times)}))
+    elif args.probe == "int4":
+        from flydsl_b200.kernels import compile_int4_weight_only_gemm, pack_int4_weight
+
+        M, N, K, copies = 16, 8192, 8192, 6
+        g = torch.Generator(device=dev).manual_seed(0)
+        sets = []
+        for _ in range(copies):
+            q = torch.randint(-8, 8, (N, K), generator=g, device=dev, dtype=torch.int8)
+            sc = (torch.rand(N, K // 128, generator=g, device=dev) * 0.01 + 0.001).to(torch.bfloat16)
+            sets.append(pack_int4_weight(q, sc))
+            del q, sc
+        a = torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
+        c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        fn = compile_int4_weight_only_gemm(N=N, K=K)
+        times = []
+        for i in range(args.warmup + args.steps):
+            wq, st = sets[i % copies]
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn(c, a, wq, st, M, None)
+            e1.record()
+            e1.synchronize()
+            if i >= args.warmup:
+                times.append(e0.elapsed_time(e1))
+        print(json.dumps({"probe": "int4", "M": M, "N": N, "K": K, "us": statistics.median(times) * 1e3}))
     else:
         M, N, K = 32, 7168, 2048
         copies = 18
@@ -659,7 +684,7 @@ def run_probe(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--probe", default=None, choices=["moe", "decode"], help="small profiling run (see run_probe)")
+    ap.add_argument("--probe", default=None, choices=["moe", "decode", "int4"], help="small profiling run (see run_probe)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
