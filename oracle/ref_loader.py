@@ -16,7 +16,9 @@ from typing import Optional, Tuple
 import torch
 import torch.nn.functional as F
 
-DEFAULT_ROOT = os.environ.get("FLYDSL_REFERENCE_ROOT", "/root/reference")
+# a FlyDSL checkout: $FLYDSL_REFERENCE_ROOT, else a directory "reference" beside this repository
+DEFAULT_ROOT = os.environ.get("FLYDSL_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 
 _WANTED = {
     "tests/kernels/test_blockscale_preshuffle_gemm.py": ["select_tile_config", "run_torch_blockscale"],
