@@ -126,9 +126,17 @@ __device__ __forceinline__ void quant_rows16(const T* __restrict__ x, uint8_t* _
     for (int u = 0; u < kInFlight; ++u) {
       const int64_t idx = w + u * nhw + (lane >> 4);
       active[u] = idx < total;
-      // rows fastest: neighbouring half-warps write neighbouring entries of the transposed scales
-      g[u] = active[u] ? static_cast<int>(idx / rows) : 0;
-      row[u] = active[u] ? idx - static_cast<int64_t>(g[u]) * rows : 0;
+      // rows fastest: neighbouring half-warps write neighbouring entries of the transposed scales.
+      // 32-bit division when the group count allows it (a 64-bit one costs more than the rest of
+      // the group's arithmetic).
+      if (total <= 0x7fffffffLL) {
+        const unsigned gi = active[u] ? static_cast<unsigned>(idx) / static_cast<unsigned>(rows) : 0u;
+        g[u] = static_cast<int>(gi);
+        row[u] = active[u] ? static_cast<int64_t>(static_cast<unsigned>(idx) - gi * static_cast<unsigned>(rows)) : 0;
+      } else {
+        g[u] = active[u] ? static_cast<int>(idx / rows) : 0;
+        row[u] = active[u] ? idx - static_cast<int64_t>(g[u]) * rows : 0;
+      }
       raw[u] = make_uint4(0u, 0u, 0u, 0u);
       if (active[u]) raw[u] = *reinterpret_cast<const uint4*>(x + row[u] * cols + g[u] * 128 + sub * 8);
     }
