@@ -307,12 +307,37 @@ moe_gather_rows_kernel(const uint4* __restrict__ x, const float* __restrict__ sc
     // source row: the token (stage 1) or the (token, slot) route (stage 2 style inputs)
     const long long src = by_slot ? static_cast<long long>(t) * topk + slot : t;
     const bool ok = by_slot ? (slot < topk && src < rows_in) : (t < rows_in);
-    for (int c = lane; c < chunks; c += 32)
-      x_out[static_cast<long long>(i) * chunks + c] =
-          ok ? x[src * chunks + c] : make_uint4(0u, 0u, 0u, 0u);
-    for (int s = lane; s < nscale; s += 32)
-      scale_out_t[static_cast<long long>(s) * rows_out + i] =
-          ok ? scale_t[static_cast<long long>(s) * rows_in + src] : 0.f;
+    // four 16-byte loads per lane in flight (the copy is latency-bound otherwise)
+    const uint4* srow = x + src * chunks;
+    uint4* drow = x_out + static_cast<long long>(i) * chunks;
+    for (int c0 = lane; c0 < chunks; c0 += 128) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + 32 * u;
+        v[u] = (ok && c < chunks) ? __ldg(srow + c) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + 32 * u;
+        if (c < chunks) drow[c] = v[u];
+      }
+    }
+  }
+  // scales: one thread per (scale row s, sorted position i), i fastest, so that the stores to the
+  // transposed output are coalesced (the reads are 4-byte gathers inside one row of scale_t)
+  const long long total = static_cast<long long>(nscale) * valid;
+  for (long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; j < total;
+       j += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int s = static_cast<int>(j / valid);
+    const int i = static_cast<int>(j - static_cast<long long>(s) * valid);
+    const int id = sorted_ids[i];
+    const int t = id & 0xFFFFFF;
+    const int slot = static_cast<unsigned>(id) >> 24;
+    const long long src = by_slot ? static_cast<long long>(t) * topk + slot : t;
+    const bool ok = by_slot ? (slot < topk && src < rows_in) : (t < rows_in);
+    scale_out_t[static_cast<long long>(s) * rows_out + i] =
+        ok ? __ldg(scale_t + static_cast<long long>(s) * rows_in + src) : 0.f;
   }
 }
 }  // namespace flyb200
@@ -329,7 +354,7 @@ extern "C" int flyb200_moe_gather_rows(const void* x, const float* scale_t, cons
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "moe_gather_rows: bad sizes");
   const int sms = sm_count();
   if (sms <= 0) return FLYB200_ERR_CUDA;
-  moe_gather_rows_kernel<<<sms * 4, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  moe_gather_rows_kernel<<<sms * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), scale_t, sorted_ids, num_valid_ids, static_cast<uint4*>(x_out),
       scale_out_t, rows_in, K, topk, rows_out, by_slot ? 1 : 0);
   FLYB200_CUDA_CHECK(cudaGetLastError());
