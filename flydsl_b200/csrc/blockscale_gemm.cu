@@ -1182,8 +1182,8 @@ static int moe_common_checks(const void* out, const void* x, const void* w, cons
       (rc = check_ptr(num_valid_ids, 4, "num_valid_ids")))
     return rc;
   if (doweight && (rc = check_ptr(sorted_weights, 4, "sorted_weights"))) return rc;
-  if (T < 1 || T >= (1 << 24) || E < 1 || k < 1 || k > 255 || num_blocks < 0)
-    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "bad MoE sizes T=%d E=%d k=%d blocks=%d", T, E, k,
+  if (T < 1 || T >= (1 << 24) || E < 1 || k < 1 || k > 255 || k > E || num_blocks < 0)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "bad MoE sizes T=%d E=%d k=%d blocks=%d (k <= E)", T, E, k,
                      num_blocks);
   if (tile_m < 1 || tile_m > BM)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "tile_m (%d) must be in [1,128]", tile_m);
@@ -1210,6 +1210,8 @@ static int moe_sorted_layout(const flyb200_gemm_cfg* cfg, int T, int E, int k, i
   p->a_sorted = bits & 1;
   p->out_sorted = (bits >> 1) & 1;
   const long long rows = static_cast<long long>(T) * k + static_cast<long long>(E) * tile_m - k;
+  if (rows <= 0 || rows > 0x7fffffffLL)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "T*k + E*tile_m - k = %lld rows is out of range", rows);
   p->a_rows = static_cast<int>(rows);
   if (!p->a_sorted) return FLYB200_OK;
   if (tile_m % 8)

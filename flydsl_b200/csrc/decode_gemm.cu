@@ -39,13 +39,6 @@ struct DecodeParams {
   int stages;              // ring depth used (<= kDecMaxStages)
 };
 
-#ifdef FLYB200_DBG_TRACE
-__device__ long long g_dec_trace[16];
-#define DEC_TRACE(i) do { if (blockIdx.x == 0 && threadIdx.x == 64) g_dec_trace[i] = clock64(); } while (0)
-#else
-#define DEC_TRACE(i)
-#endif
-
 template <int NT>
 struct DecCfg {
   static constexpr int kXTileBytes = NT * 128;
@@ -187,7 +180,6 @@ bs_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecodePa
     for (int kbl = et; kbl < count; kbl += 128)
       sb_s[kbl] = __ldg(p.scale_b + static_cast<size_t>(n_tile) * KBt + kb_begin + kbl);
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    DEC_TRACE(0);
 
     float acc[NT];
 #pragma unroll
@@ -231,14 +223,12 @@ bs_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecodePa
     // column j = j / cpc). Partials go to this CTA's own shared memory as [j][n] (the pipeline
     // stages are free by now: every MMA of this CTA has completed), then one bulk copy per owner
     // moves that owner's column slice into its receive area, slot [sender][local column][n].
-    DEC_TRACE(1);
     float* send = reinterpret_cast<float*>(smem_al);
 #pragma unroll
     for (int j = 0; j < NT; ++j)
       if (j < p.M) send[j * 128 + n_loc] = acc[j];
     fence_proxy_async_smem();
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    DEC_TRACE(2);
     const int cpc = (p.M + p.splits - 1) / p.splits;
     if (et == 0 && alive) {
       for (int o = 0; o < p.splits; ++o) {
@@ -255,7 +245,6 @@ bs_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecodePa
     const int j_hi = min(p.M, j_lo + cpc);
     if (j_hi > j_lo && alive) {
       const bool got = mbar_wait(recv_bar, 0, abort_flag, p.err, kErrWaitExchange);
-      DEC_TRACE(3);
       if (__all_sync(0xffffffffu, got)) {
         OutT* const out = reinterpret_cast<OutT*>(p.out);
         // eight columns at a time so that their shared-memory loads are in flight together
@@ -286,13 +275,10 @@ bs_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecodePa
       }
     }
   }
-
-  DEC_TRACE(4);
   // Nobody leaves before every bulk copy that reads its shared memory has been consumed: the owners
   // arrive here only after their receive barrier completed.
   __syncwarp();
   cluster_sync_all();
-  DEC_TRACE(5);
 
   // ---------------- teardown ----------------
   tc_fence_before();
@@ -383,12 +369,6 @@ static int launch_decode(const CUtensorMap& tmap, const DecodeParams& p, int n_t
   FLYB200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmap, p));
   return FLYB200_OK;
 }
-
-#ifdef FLYB200_DBG_TRACE
-extern "C" int flyb200_debug_read_dec_trace(long long* host) {
-  return cudaMemcpyFromSymbol(host, g_dec_trace, sizeof(long long) * 16) == cudaSuccess ? 0 : -3;
-}
-#endif
 
 // Whether the automatic dispatch should take the decode kernel (measured on B200): it wins when all
 // of its CTAs are resident at once (one wave) -- with more than 32 tokens only if K is deep enough

@@ -53,7 +53,8 @@ extern "C" int flyb200_ep_plan_pack(const void* x, const float* x_scale, const i
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_plan_pack: NULL buffer");
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(send_out)) % 16)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_plan_pack: x and send_out must be 16-byte aligned");
-  if (T < 1 || H < 128 || H % 128 || k < 1 || W < 1 || experts_per_rank < 1 || (8 * k) % 16)
+  if (T < 1 || H < 128 || H % 128 || k < 1 || W < 1 || experts_per_rank < 1 || (8 * k) % 16 ||
+      (H + 4 * (H / 128) + 8 * k) % 16)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT,
                      "ep_plan_pack: bad sizes (H %% 128 == 0, k even so that rows stay 16-byte aligned)");
   const int sms = sm_count();
@@ -156,7 +157,8 @@ extern "C" int flyb200_ep_gather_packed(const void* packed, const int32_t* sorte
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_gather_packed: NULL buffer");
   if ((reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(x_out)) % 16)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_gather_packed: buffers must be 16-byte aligned");
-  if (rows_in < 1 || rows_out < 1 || H < 128 || H % 128 || k < 1 || (8 * k) % 16)
+  if (rows_in < 1 || rows_out < 1 || H < 128 || H % 128 || k < 1 || (8 * k) % 16 ||
+      (H + 4 * (H / 128) + 8 * k) % 16)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_gather_packed: bad sizes");
   const int sms = sm_count();
   if (sms <= 0) return FLYB200_ERR_CUDA;

@@ -255,8 +255,10 @@ extern "C" int flyb200_ep_push(const void* x, const float* x_scale, const int32_
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_push: NULL buffer or more than %d ranks", kMaxPeers);
   if (reinterpret_cast<uintptr_t>(x) % 16 || recv_off < 0 || recv_off % 16)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_push: x and the receive area must be 16-byte aligned");
-  if (T < 1 || H < 128 || H % 128 || k < 1 || (8 * k) % 16 || rank < 0 || rank >= W || experts_per_rank < 1)
-    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_push: bad sizes (H %% 128 == 0, k even)");
+  if (T < 1 || H < 128 || H % 128 || k < 1 || (8 * k) % 16 || rank < 0 || rank >= W || experts_per_rank < 1 ||
+      (H + 4 * (H / 128) + 8 * k) % 16)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT,
+                     "ep_push: bad sizes (H %% 128 == 0, k even, packed row H + 4*(H/128) + 8*k a multiple of 16)");
   const int sms = sm_count();
   if (sms <= 0) return FLYB200_ERR_CUDA;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

@@ -190,11 +190,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const Int4Params p)
         tc_fence_after();
         const uint32_t sw = smem_base + s * C::kStageBytes;
         const uint32_t d = tmem_base + buf * NT;
-#ifdef FLYB200_DBG_I4_HALF_MMA    // timing experiment only: half of the MMAs, wrong results
-        constexpr int kSubTiles = 1;
-#else
         constexpr int kSubTiles = 2;
-#endif
 #pragma unroll
         for (int h = 0; h < kSubTiles; ++h) {
           const uint64_t wdesc = umma_desc_sw128(sw + h * (128 * 128));
@@ -253,13 +249,8 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const Int4Params p)
       const bool ok = wait_stage_free(i, kErrWaitGather);
       if (!__all_sync(0xffffffffu, ok)) break;
       const uint32_t sw = smem_base + s * C::kStageBytes;
-#ifdef FLYB200_DBG_I4_NO_CONVERT   // timing experiment only: nothing is dequantised, wrong results
-      constexpr int kVecsDone = 0;
-#else
-      constexpr int kVecsDone = kVecs;
-#endif
 #pragma unroll
-      for (int j = 0; j < kVecsDone; ++j) {
+      for (int j = 0; j < kVecs; ++j) {
         const int vec = j * kDqThreads + dt;
         const int r = vec >> 2, part = vec & 3;
         const uint32_t row_base = sw + (part >> 1) * (128 * 128) + r * 128;
@@ -282,9 +273,7 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const Int4Params p)
                        : "memory");
         }
       }
-#ifndef FLYB200_DBG_I4_NO_FENCE   // timing experiment only: results are wrong without the fence
       fence_proxy_async_smem();   // generic-proxy writes -> visible to the tensor core's reads
-#endif
       __syncwarp();
       if (lane == 0) mbar_arrive(full_bar(s));
     }

@@ -251,8 +251,8 @@ extern "C" int flyb200_moe_reduce(const void* x, void* y, const uint8_t* valid_m
 extern "C" int flyb200_quant_1x128(const void* x, void* q, float* scale_t, int64_t rows,
                                    int32_t cols, int32_t in_dtype, void* stream) {
   if (!x || !q || !scale_t) return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant: NULL buffer");
-  if ((reinterpret_cast<uintptr_t>(x) % 16) || (reinterpret_cast<uintptr_t>(q) % 4))
-    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant: x must be 16-byte, q 4-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(x) % 16) || (reinterpret_cast<uintptr_t>(q) % 8))
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant: x must be 16-byte, q 8-byte aligned");
   if (rows < 0 || cols < 128 || cols % 128)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant: cols (%d) must be a multiple of 128", cols);
   if (rows == 0) return FLYB200_OK;
@@ -378,8 +378,8 @@ extern "C" int flyb200_quant_1x128_devrows(const void* x, void* q, float* scale_
                                            int32_t cols, int32_t in_dtype, void* stream) {
   if (!x || !q || !scale_t || !num_rows_dev)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant_devrows: NULL buffer");
-  if ((reinterpret_cast<uintptr_t>(x) % 16) || (reinterpret_cast<uintptr_t>(q) % 4))
-    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant_devrows: x must be 16-byte, q 4-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(x) % 16) || (reinterpret_cast<uintptr_t>(q) % 8))
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant_devrows: x must be 16-byte, q 8-byte aligned");
   if (rows_alloc < 1 || cols < 128 || cols % 128)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant_devrows: bad sizes");
   if (in_dtype != FLYB200_BF16 && in_dtype != FLYB200_F16)

@@ -298,9 +298,11 @@ extern "C" int flyb200_moe_sort(const int32_t* topk_ids, const float* topk_weigh
   if (!topk_ids || !topk_weights || !sorted_ids || !sorted_weights || !sorted_expert_ids ||
       !num_valid_ids)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "moe_sort: NULL buffer");
-  if (T < 0 || T >= (1 << 24) || k < 1 || k > 255 || E < 1 || E > 8192 || block_m < 1)
+  // k <= E: the buffers are sized T*k + E*block_m - k (the reference's formula), which bounds the
+  // padded total T*k + E*(block_m - 1) only then.
+  if (T < 0 || T >= (1 << 24) || k < 1 || k > 255 || E < 1 || E > 8192 || block_m < 1 || k > E)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT,
-                     "moe_sort: bad sizes T=%d k=%d E=%d block_m=%d (T < 2^24, k <= 255, E <= 8192)",
+                     "moe_sort: bad sizes T=%d k=%d E=%d block_m=%d (T < 2^24, k <= 255, k <= E <= 8192)",
                      T, k, E, block_m);
   const long long max_len = static_cast<long long>(T) * k + static_cast<long long>(E) * block_m - k;
   if (max_len <= 0 || max_len > 0x7fffffffLL)

@@ -154,6 +154,11 @@ class BlockscaleMoE:
             self.gemm2(out, b["a2_q"], self.w2, b["a2_s"], self.w2_scale, sid, seid, sw, npp, T,
                        self.H, self.I, nblk, None)
         else:
+            if routing is not None:
+                # A caller's routing may drop routes (expert_mask, ids outside the local experts):
+                # their rows are never written by stage 2, so they must read as zero in the sum
+                # (the reference wrapper zero-fills its intermediate, :2714-2715).
+                b["routes"].zero_()
             self.gemm2(b["routes"], b["a2_q"], self.w2, b["a2_s"], self.w2_scale, sid, seid, sw, npp,
                        T, self.H, self.I, nblk, None)
             self.reduce(b["routes"], out, None, T, None)

@@ -51,8 +51,8 @@ def test_dense_vs_golden(tag, block_n):
     assert_close_to_oracle(c, bf16_from_bits(g[f"{tag}_c_bf16_bits"]), f"golden {tag} bn={block_n}")
 
 
-# The reference's own test grid (tests/kernels/test_blockscale_preshuffle_gemm.py:121-142), trimmed to
-# what the CPU oracle finishes in seconds, plus BASELINE config 1.
+# The reference's own test grid (tests/kernels/test_blockscale_preshuffle_gemm.py:121-142): its three
+# (N, K) pairs at every small M; the M=1024 rows follow in test_dense_reference_large_rows.
 @pytest.mark.parametrize("M", [1, 7, 16, 33, 64, 256])
 @pytest.mark.parametrize("N,K", [(7168, 2304), (2112, 7168), (3072, 1536)])
 @pytest.mark.parametrize("out_dtype", ["bf16", "fp16"])
@@ -77,6 +77,66 @@ def test_decode_path_split_k(M, N, K, split_k):
     assert torch.equal(c, c2)  # fixed reduction order: bitwise repeatable
     t = _run_dense(case["a_q"], case["a_scale"], case["b_q"], case["b_scale"], path="tiled")
     assert_close_to_oracle(t, ref, f"tiled M={M} N={N} K={K}")
+
+
+@pytest.mark.parametrize("N,K", [(7168, 2304), (2112, 7168), (3072, 1536)])
+def test_dense_reference_large_rows(N, K):
+    """The M=1024 rows of the reference grid (its `large_shape` marks)."""
+    case = O.make_dense_case(1024, N, K, seed=1024 + N)
+    ref = O.run_torch_blockscale(case["a_q"], case["b_q"], case["a_scale"], case["b_scale"], dtype=torch.float32)
+    c = _run_dense(case["a_q"], case["a_scale"], case["b_q"], case["b_scale"])
+    assert_close_to_oracle(c, ref, f"M=1024 N={N} K={K}")
+
+
+# The shapes the benchmark sweeps: M in {1, 32, 256, 4096, 16384} x three (N, K) pairs. At M >= 4096
+# there are several times more tiles than SMs, so every persistent CTA walks 6-30 tiles back to back
+# (staging-tile reuse, accumulator rotation across tile boundaries, next-tile scale prefetch).
+SWEEP_NK = [(7168, 2048), (4096, 7168), (24576, 1536)]
+
+
+@pytest.mark.parametrize("N,K", SWEEP_NK)
+@pytest.mark.parametrize("M", [1, 32, 256, 4096])
+def test_dense_sweep_shapes_default_heuristic(M, N, K):
+    case = O.make_dense_case(M, N, K, seed=M + N + K)
+    ref = O.run_torch_blockscale(case["a_q"], case["b_q"], case["a_scale"], case["b_scale"], dtype=torch.float32)
+    c = _run_dense(case["a_q"], case["a_scale"], case["b_q"], case["b_scale"])
+    assert_close_to_oracle(c, ref, f"sweep M={M} N={N} K={K}")
+    if M <= 32:   # the same shape through the tiled kernel
+        t = _run_dense(case["a_q"], case["a_scale"], case["b_q"], case["b_scale"], path="tiled")
+        assert_close_to_oracle(t, ref, f"sweep tiled M={M} N={N} K={K}")
+
+
+@pytest.mark.parametrize("M,N,K,block_n", [(4096, 7168, 2048, 256), (4096, 7168, 2048, 128), (4096, 4096, 7168, 256),
+                                           (16384, 7168, 2048, None), (16384, 7168, 2048, 256),
+                                           (4096 + 77, 7168, 2048, 256), (4096, 7168 - 48, 2048, None)])
+def test_dense_many_tiles_per_cta(M, N, K, block_n):
+    """Headline shape and its neighbours with the tile width forced, plus ragged M and N: every CTA
+    processes many tiles; run twice, results must be bitwise repeatable."""
+    case = O.make_dense_case(M, N, K, seed=3)
+    ref = O.run_torch_blockscale(case["a_q"], case["b_q"], case["a_scale"], case["b_scale"], dtype=torch.float32)
+    c = _run_dense(case["a_q"], case["a_scale"], case["b_q"], case["b_scale"], block_n=block_n)
+    assert_close_to_oracle(c, ref, f"M={M} N={N} K={K} bn={block_n}")
+    c2 = _run_dense(case["a_q"], case["a_scale"], case["b_q"], case["b_scale"], block_n=block_n)
+    assert torch.equal(c, c2)
+
+
+def test_dense_accepts_parameter_tensors():
+    """Tensor subclasses such as nn.Parameter are taken like plain tensors (the reference's
+    tests/unit/test_jit_stream_param.py:101-175 passes them to its launchers)."""
+    from flydsl_b200.kernels import compile_blockscale_preshuffle_gemm
+    from flydsl_b200.utils import shuffle_weight
+
+    M, N, K = 48, 512, 1024
+    case = O.make_dense_case(M, N, K, seed=8)
+    ref = O.run_torch_blockscale(case["a_q"], case["b_q"], case["a_scale"], case["b_scale"], dtype=torch.float32)
+    dev = torch.device("cuda")
+    w = torch.nn.Parameter(shuffle_weight(case["b_q"].to(dev)), requires_grad=False)
+    sb = torch.nn.Parameter(case["b_scale"].to(dev).contiguous().view(-1), requires_grad=False)
+    fn = compile_blockscale_preshuffle_gemm(M=M, N=N, K=K, tile_m=64, tile_n=128, tile_k=128)
+    c = torch.zeros((M, N), dtype=torch.bfloat16, device=dev)
+    fn(c, case["a_q"].to(dev), w, case["a_scale"].to(dev).t().contiguous().view(-1), sb, M, N, None)
+    torch.cuda.synchronize()
+    assert_close_to_oracle(c, ref, "nn.Parameter operands")
 
 
 def test_dense_config1_and_m_tail():

@@ -1,5 +1,7 @@
 """MoE path on the GPU: routing sort (bit-exact), 1x128 quantiser (bit-exact), top-k reduce, the two
 stage GEMMs and the chained layer, against golden vectors and the CPU oracle."""
+import functools
+
 import numpy as np
 import pytest
 import torch
@@ -165,8 +167,8 @@ def test_gemm2_ex_reduce_mode_matches_atomic():
                                max_rel=MAX_REL_ATOMIC16 if mode == MoeGemm2Mode.ATOMIC else MAX_REL)
 
 
-# The reference's own shape grid (tests/kernels/test_moe_blockscale.py:195-210): tile 16x256x128; the
-# 256-expert rows are run with 64 experts so the CPU oracle's weight generation stays within seconds.
+# The reference's own shape grid (tests/kernels/test_moe_blockscale.py:195-210), tile 16x256x128; its
+# two 256-expert rows follow in test_layer_256_experts.
 @pytest.mark.parametrize("T,H,I,E,k", [(16, 7168, 256, 8, 2), (32, 7168, 256, 8, 2), (32, 7168, 256, 64, 8),
                                        (128, 1024, 512, 16, 4)])
 @pytest.mark.parametrize("mode", ["reduce", "atomic"])
@@ -189,6 +191,172 @@ def test_layer_vs_oracle(T, H, I, E, k, mode):
         out2 = layer.forward(m["x_q"].to(DEV), xs_t, m["topk_ids"].to(DEV), m["topk_weights"].to(DEV))
         torch.cuda.synchronize()
         assert torch.equal(out, out2)
+
+
+@functools.lru_cache(maxsize=2)
+def _big_case(T, H, I, E, k, seed, hot):
+    m = O.make_moe_case(T=T, H=H, I=I, E=E, topk=k, seed=seed, x_std=1.0, w_std=0.02, hot_experts=hot, hot_bias=2.0)
+    dev = {n: m[n].to(DEV) for n in ("w1_q", "w1_scale", "w2_q", "w2_scale")}
+    return m, dev
+
+
+def _layer_against_oracle(m, dev, T, I, k, what, **layer_kw):
+    """First T tokens of case `m` through BlockscaleMoE and through the two-stage oracle."""
+    from flydsl_b200 import _lib
+    from flydsl_b200.moe import BlockscaleMoE
+
+    x_q, x_s = m["x_q"][:T], m["x_scale"][:T]
+    ids, w = m["topk_ids"][:T], m["topk_weights"][:T]
+    ref, _, _, _ = O.torch_moe_two_stage_ref(x_q, x_s, m["w1_q"], m["w1_scale"], m["w2_q"], m["w2_scale"], ids, w, I)
+    layer = BlockscaleMoE.from_unpacked(dev["w1_q"], dev["w1_scale"], dev["w2_q"], dev["w2_scale"], topk=k, **layer_kw)
+    args = (x_q.to(DEV), x_s.to(DEV).t().contiguous(), ids.to(DEV), w.to(DEV))
+    out = layer.forward(*args)
+    torch.cuda.synchronize()
+    assert _lib.query_device_error() == 0
+    assert_close_to_oracle(out, ref, what)
+    out2 = layer.forward(*args)     # reduce mode: fixed summation order, bitwise repeatable
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)
+    return layer
+
+
+def test_layer_benchmark_dims_many_row_blocks():
+    """Hidden 7168 / intermediate 2048 as benchmarked: 1024 tokens on 8 experts with 128-row blocks
+    give ~8 row blocks per expert and 16 + 28..56 column tiles per block, so every persistent CTA
+    walks many tiles in both stages (K loops of 56 and 16 blocks)."""
+    T, H, I, E, k = 1024, 7168, 2048, 8, 8
+    m, dev = _big_case(T, H, I, E, k, 3, 0)
+    counts = torch.bincount(m["topk_ids"].flatten().long(), minlength=E)
+    assert counts.min() > 2 * 128
+    _layer_against_oracle(m, dev, T, I, k, "layer 1024x7168x2048 E8", tile_m=128)
+    _layer_against_oracle(m, dev, 200, I, k, "layer 200x7168x2048 E8 gathered", tile_m=128, sorted_layout=False)
+
+
+def test_layer_benchmark_dims_skewed_decode():
+    """Decode-regime stress at the benchmarked dims: 256 and 32 tokens, half of the 16 experts hot
+    (+2 on their logits), 32-row and 16-row blocks."""
+    H, I, E, k = 7168, 2048, 16, 8
+    m, dev = _big_case(256, H, I, E, k, 5, 8)
+    counts = torch.bincount(m["topk_ids"].flatten().long(), minlength=E)
+    assert counts.max() > 3 * counts.min()
+    _layer_against_oracle(m, dev, 256, I, k, "skewed 256 tokens", tile_m=32)
+    _layer_against_oracle(m, dev, 32, I, k, "skewed 32 tokens", tile_m=16)
+
+
+@pytest.mark.parametrize("T", [32, 128])
+def test_layer_256_experts(T):
+    """The reference grid's two 256-expert rows (tests/kernels/test_moe_blockscale.py:206-209):
+    model_dim 7168, inter_dim 256, top-8, tile 16; most experts get zero or one route."""
+    H, I, E, k = 7168, 256, 256, 8
+    m, dev = _big_case(128, H, I, E, k, 7, 0)
+    _layer_against_oracle(m, dev, T, I, k, f"256 experts T={T}", tile_m=16)
+
+
+def test_stage_weighting_variants():
+    """doweight_stage1=True with doweight_stage2=False (the route weight multiplies the stage-1
+    output, reference kernels/moe_blockscale_2stage.py:1051-1066, :1129-1146) against the oracle with
+    the weight applied at the same place."""
+    from flydsl_b200.kernels import compile_moe_blockscale_gemm1, compile_moe_blockscale_gemm2
+    from flydsl_b200.utils import build_routing_buffers, quant_1x128, shuffle_weight
+
+    (T, H, I, E, k), t = _golden_moe()
+    tile_m = 32
+    sid, sw, seid, nv, _, blocks = build_routing_buffers(topk_ids=t["topk_ids"].to(DEV), topk_weights=t["topk_w"].to(DEV),
+                                                         experts=E, model_dim=H, tile_m=tile_m)
+    common = dict(model_dim=H, inter_dim=I, experts=E, topk=k, tile_m=tile_m, tile_n=256, tile_k=128)
+    g1 = compile_moe_blockscale_gemm1(doweight_stage1=True, out_dtype="f16", **common)
+    out1 = torch.zeros(T, k, I, dtype=torch.float16, device=DEV)
+    g1(out1.view(-1), t["x_q"].to(DEV).view(-1), shuffle_weight(t["w1_q"].to(DEV)).view(-1),
+       t["x_scale"].to(DEV).t().contiguous().view(-1), t["w1_scale"].to(DEV).view(-1), sid, seid, sw, nv, T, I, H,
+       blocks, None)
+    torch.cuda.synchronize()
+    want1 = t["out1"] * t["topk_w"].view(T, k, 1)
+    assert_close_to_oracle(out1, want1, "stage 1 with route weights")
+    # stage 2 without weights on the re-quantised weighted intermediate
+    a2_q, a2_s = O.quant_1x128(want1.to(torch.float16).float().reshape(-1, I))
+    want2 = O.torch_stage2_blockscale_ref(a2_q, t["w2_q"], t["topk_ids"], torch.ones_like(t["topk_w"]), a2_s,
+                                          t["w2_scale"], T, H, I, k)
+    q_dev, s_dev = quant_1x128(out1.view(-1, I))
+    g2 = compile_moe_blockscale_gemm2(doweight_stage2=False, out_dtype="f32", accumulate=True, **common)
+    out2 = torch.zeros(T, H, dtype=torch.float32, device=DEV)
+    g2(out2.view(-1), q_dev.view(-1), shuffle_weight(t["w2_q"].to(DEV)).view(-1), s_dev.view(-1),
+       t["w2_scale"].to(DEV).view(-1), sid, seid, sw, nv, T, H, I, blocks, None)
+    torch.cuda.synchronize()
+    assert_close_to_oracle(out2, want2, "stage 2 without route weights")
+
+
+def test_gemm2_ex_reduce_mode_with_valid_mask():
+    """compile_moe_blockscale_gemm2_ex(mode="reduce", valid_mask=...) through the Python wrapper: masked
+    routes contribute nothing, whatever the per-route scratch rows held before."""
+    from flydsl_b200.kernels import MoeGemm2Mode, compile_moe_blockscale_gemm2_ex
+    from flydsl_b200.utils import build_routing_buffers, shuffle_weight
+
+    (T, H, I, E, k), t = _golden_moe()
+    sid, sw, seid, nv, _, blocks = build_routing_buffers(topk_ids=t["topk_ids"].to(DEV), topk_weights=t["topk_w"].to(DEV),
+                                                         experts=E, model_dim=H, tile_m=32)
+    gen = torch.Generator().manual_seed(2)
+    mask = (torch.rand(T, k, generator=gen) > 0.3).to(torch.uint8)
+    exe = compile_moe_blockscale_gemm2_ex(model_dim=H, inter_dim=I, experts=E, topk=k, tile_m=32, tile_n=256,
+                                          tile_k=128, doweight_stage2=True, out_dtype="bf16",
+                                          mode=MoeGemm2Mode.REDUCE, valid_mask=mask.to(DEV))
+    out = torch.zeros(T, H, dtype=torch.bfloat16, device=DEV)
+    exe(out, t["a2_q"].to(DEV), torch.nn.Parameter(shuffle_weight(t["w2_q"].to(DEV)), requires_grad=False),
+        t["a2_scale"].to(DEV).t().contiguous(), t["w2_scale"].to(DEV), sid, seid, sw, nv, T, H, I, blocks,
+        valid_mask=mask.to(DEV))
+    torch.cuda.synchronize()
+    per_route = O.torch_stage2_blockscale_ref(t["a2_q"], t["w2_q"], t["topk_ids"], t["topk_w"], t["a2_scale"],
+                                              t["w2_scale"], T, H, I, k, per_route=True)
+    want = (per_route * (t["topk_w"] * mask.float()).view(T, k, 1)).sum(1)
+    assert_close_to_oracle(out, want, "gemm2_ex reduce + valid_mask")
+
+
+@pytest.mark.parametrize("sorted_layout", [False, True])
+def test_layer_bf16_intermediate(sorted_layout):
+    """Stage 1 in bf16 through the unfused pipeline (the reference allows bf16 with its direct epilogue,
+    kernels/moe_blockscale_2stage.py:182-183): the oracle rounds its intermediate to bf16 as well."""
+    from flydsl_b200.moe import BlockscaleMoE
+
+    T, H, I, E, k = 150, 1024, 512, 8, 4
+    m = O.make_moe_case(T=T, H=H, I=I, E=E, topk=k, seed=17, w_std=0.05)
+    ref, _, _, _ = O.torch_moe_two_stage_ref(m["x_q"], m["x_scale"], m["w1_q"], m["w1_scale"], m["w2_q"], m["w2_scale"],
+                                             m["topk_ids"], m["topk_weights"], I, mid_dtype=torch.bfloat16)
+    layer = BlockscaleMoE.from_unpacked(m["w1_q"].to(DEV), m["w1_scale"].to(DEV), m["w2_q"].to(DEV),
+                                        m["w2_scale"].to(DEV), topk=k, tile_m=64, mid_dtype=torch.bfloat16,
+                                        sorted_layout=sorted_layout)
+    out = layer.forward(m["x_q"].to(DEV), m["x_scale"].to(DEV).t().contiguous(), m["topk_ids"].to(DEV),
+                        m["topk_weights"].to(DEV))
+    torch.cuda.synchronize()
+    assert_close_to_oracle(out, ref, f"bf16 intermediate sorted={sorted_layout}")
+
+
+def test_layer_with_masked_routing_ignores_stale_rows():
+    """A caller-supplied routing that drops experts (expert_mask) leaves some (token, slot) rows of
+    the per-route scratch unwritten; they must not leak into the sum. The scratch is poisoned first."""
+    from flydsl_b200.moe import BlockscaleMoE
+    from flydsl_b200.utils import moe_sorting
+
+    T, H, I, E, k = 64, 512, 256, 8, 4
+    m = O.make_moe_case(T=T, H=H, I=I, E=E, topk=k, seed=23, w_std=0.05)
+    emask = torch.tensor([1, 0, 1, 1, 0, 1, 1, 1], dtype=torch.int32)
+    keep = emask[m["topk_ids"].long()].bool()
+    per_route_w = m["topk_weights"] * keep.float()
+    ref, _, _, _ = O.torch_moe_two_stage_ref(m["x_q"], m["x_scale"], m["w1_q"], m["w1_scale"], m["w2_q"], m["w2_scale"],
+                                             m["topk_ids"], per_route_w, I)
+    # local weights = the kept experts only, ids compacted by the sorter as the reference's expert_mask does
+    sel = emask.bool()
+    for sorted_layout in (False, True):
+        layer = BlockscaleMoE.from_unpacked(m["w1_q"][sel].to(DEV), m["w1_scale"][sel].to(DEV), m["w2_q"][sel].to(DEV),
+                                            m["w2_scale"][sel].to(DEV), topk=k, tile_m=32, sorted_layout=sorted_layout)
+        ids, w = m["topk_ids"].to(DEV), m["topk_weights"].to(DEV)
+        routing = moe_sorting(ids, w, num_experts=E, block_size=32, expert_mask=emask.to(DEV))
+        b = layer._buffers(T, torch.device(DEV, torch.cuda.current_device()))
+        b["routes"].fill_(float("nan"))
+        n_local = int(sel.sum())
+        rows = T * k + n_local * 32 - k
+        routing = tuple(r[:rows] if i < 2 else r for i, r in enumerate(routing))
+        out = layer.forward(m["x_q"].to(DEV), m["x_scale"].to(DEV).t().contiguous(), ids, w, routing=routing)
+        torch.cuda.synchronize()
+        assert_close_to_oracle(out, ref, f"masked routing sorted={sorted_layout}")
 
 
 def test_sorted_layout_matches_gathered_layout():
@@ -389,6 +557,48 @@ def test_ep_peer_kernels_two_ranks_emulated_on_one_gpu():
         views.clear()
         for q in bufs:
             _lib.check(lib.flyb200_ep_buffer_destroy(q))
+
+
+def test_bounded_wait_runs_out_and_the_context_stays_usable():
+    """Failure path of the device waits, made to happen without faulting anything: a two-rank flag
+    barrier on ONE GPU whose second rank never arrives (both peer pointers name this process's own
+    buffer, nothing writes flag word 1). The kernel gives up after the limit, the device error word
+    carries the wait code and the peer index, the query reports a time-out and clears the word, and
+    an ordinary GEMM on the same context still passes. (The reference only prints runtime errors,
+    lib/Runtime/FlyRocmRuntimeWrappers.cpp:22-30; this library returns them.)"""
+    import ctypes
+    import time
+
+    from flydsl_b200 import _lib
+
+    lib = _lib.load()
+    q, h = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
+    _lib.check(lib.flyb200_ep_buffer_create(4096, ctypes.byref(q), h))
+    try:
+        peers = (ctypes.c_void_p * 2)(q.value, q.value)
+        torch.cuda.synchronize()
+        assert _lib.query_device_error() == 0
+        t0 = time.time()
+        _lib.check(lib.flyb200_ep_barrier(peers, 2, 0, 0, 1, 5, _lib.stream_handle(None)))
+        code = ctypes.c_int32(0)
+        status = lib.flyb200_query_device_error(_lib.stream_handle(None), ctypes.byref(code))
+        assert time.time() - t0 < 5.0                      # returned after ~5 ms, nothing hung
+        assert status == _lib.ERR_DEVICE_TIMEOUT
+        assert code.value & 0xFF == 8 and code.value >> 8 == 1   # kErrWaitPeer, peer 1
+        assert b"bounded wait" in lib.flyb200_last_error_string()
+        assert _lib.query_device_error() == 0              # cleared by the query
+        # the flag of the rank that did arrive is in place; a complete barrier passes
+        peers1 = (ctypes.c_void_p * 1)(q.value)
+        _lib.check(lib.flyb200_ep_barrier(peers1, 1, 0, 0, 2, 5, _lib.stream_handle(None)))
+        assert _lib.query_device_error() == 0
+    finally:
+        torch.cuda.synchronize()
+        _lib.check(lib.flyb200_ep_buffer_destroy(q))
+    case = O.make_dense_case(64, 256, 256, seed=2)
+    from tests.test_gpu_dense import _run_dense
+    c = _run_dense(case["a_q"], case["a_scale"], case["b_q"], case["b_scale"], path="tiled")
+    ref = O.run_torch_blockscale(case["a_q"], case["b_q"], case["a_scale"], case["b_scale"], dtype=torch.float32)
+    assert_close_to_oracle(c, ref, "GEMM after a timed-out wait")
 
 
 def test_skewed_routing_and_empty_experts():

@@ -109,3 +109,28 @@ def test_autotuner_keys_cache_and_persistence(tmp_path):
     assert t2.tune(4096, 7168, 2048, make_call=lambda cfg: (_ for _ in ()).throw(AssertionError)) == best
     assert any(c.path == "decode" for c in default_configs(16, 7168, 2048))
     assert all(c.path != "decode" for c in default_configs(4096, 7168, 2048))
+
+
+def test_c_abi_refuses_bad_sizes_before_any_launch():
+    """Argument checks that protect vector accesses run on the host before anything is launched, so
+    they can be exercised without a GPU: a non-NULL dummy pointer is enough."""
+    from flydsl_b200 import _lib
+
+    lib = _lib.load()
+    buf = (ctypes.c_ubyte * 4096)()
+    base = ctypes.addressof(buf)
+    p16 = (base + 15) // 16 * 16
+    peers = (ctypes.c_void_p * 2)(p16, p16)
+    inval = _lib.ERR_INVALID_ARGUMENT
+    # packed expert-parallel row = H + 4*(H/128) + 8*k bytes, copied as 16-byte vectors: H=640 gives
+    # 640 + 20 + 32 = 692 bytes, not a multiple of 16
+    assert lib.flyb200_ep_push(p16, p16, p16, p16, 4, 640, 4, 2, 0, 4, peers, 0, p16, p16, p16, None) == inval
+    assert b"multiple of 16" in lib.flyb200_last_error_string()
+    assert lib.flyb200_ep_plan_pack(p16, p16, p16, p16, 4, 640, 4, 2, 4, p16, p16, p16, p16, None) == inval
+    assert lib.flyb200_ep_gather_packed(p16, p16, p16, p16, p16, 4, 4, 640, 4, None) == inval
+    # the 16-bit quantiser stores 8 bytes at a time: q at 8k+4 is refused
+    assert lib.flyb200_quant_1x128(p16, p16 + 4, p16, 2, 128, _lib.BF16, None) == inval
+    assert lib.flyb200_quant_1x128_devrows(p16, p16 + 4, p16, p16, 2, 128, _lib.BF16, None) == inval
+    # more routes per token than experts would overrun the reference-sized sort buffers
+    assert lib.flyb200_moe_sort(p16, p16, 4, 9, 8, 16, None, -1, p16, p16, p16, p16, None) == inval
+    assert b"k <= E" in lib.flyb200_last_error_string()
