@@ -35,17 +35,6 @@ constexpr int kRegionBytes = BM * 128;  // one 64-column (16-bit) slab of the st
 
 enum Mode : int { kDense = 0, kMoe1 = 1, kMoe2 = 2 };
 
-#ifdef FLYB200_DBG_TRACE
-// Debug build only: per-event timestamps of CTA 0 (event type, iteration, clock64).
-__device__ long long g_trace[8 * 512];
-__device__ __forceinline__ void trace(int type, unsigned it) {
-  if (blockIdx.x == 0 && it < 512) g_trace[type * 512 + it] = clock64();
-}
-#define FLYB200_TRACE(type, it) trace(type, it)
-#else
-#define FLYB200_TRACE(type, it)
-#endif
-
 struct GemmParams {
   const uint8_t* a;        // MoE: activation rows to gather from (dense uses the tensor map)
   const uint8_t* b;        // repacked weights
@@ -74,7 +63,6 @@ struct GemmParams {
   int a_sorted;
   int out_sorted;
   int a_rows;
-  int group;               // tiles a CTA processes back to back (see TileWalker)
   // Stage 1 with the 1x128 re-quantisation fused into the epilogue (256-wide tiles, routing-order
   // output): fp8 rows [a_rows, N] and their scales [N/128, a_rows] instead of the 16-bit `out`.
   uint8_t* out_q;
@@ -99,20 +87,6 @@ struct Cfg {
   // release round trip (about a thousand cycles) for the narrow tiles.
   static constexpr int kAccBufs = (512 / BN) > 8 ? 8 : (512 / BN);
   static constexpr int kTmemCols = BN * kAccBufs;
-  // Optional (-DFLYB200_SPLIT_N), dense 256-wide tiles: every K block is issued as two 128-column
-  // MMA groups by two issuer threads (warps 1 and 2) with a commit each, so the epilogue drains the
-  // first half while the tensor core works on the second and the MMA -> drain -> release round trip
-  // spans four half buffers instead of two whole ones. Measured on B200 it is SLOWER and therefore
-  // off: M=4096 N=7168 K=2048 takes 76.6 us with two issuers (86 us with one) against 68.6 us
-  // unsplit -- an N=128 instruction re-reads the A tile from shared memory per 128 columns, and
-  // MMA-only runs (no loads, no promotion) give 1500 TFLOP/s for 128-wide against 2270-2590 for
-  // 256-wide instructions.
-#ifdef FLYB200_SPLIT_N
-  static constexpr bool kSplit = (BN == 256) && (MODE == 0);
-#else
-  static constexpr bool kSplit = false;
-#endif
-  static constexpr int kHalves = kSplit ? 2 : 1;
   static constexpr int kCH = BN / 4;  // columns per epilogue thread per column group
   static constexpr int kSmemBytes = kStages * kStageBytes + kCBytes + kMiscBytes + 1024;
   static_assert(kStages >= 3, "pipeline too shallow");
@@ -173,18 +147,24 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
-// Tile bookkeeping shared by every role so that all of them walk the same sequence.
+// Tile bookkeeping shared by every role so that all of them walk the same sequence: tile
+// blockIdx.x, then one grid further, and so on. A position carries (m block, n tile) and is advanced
+// with additions only (the integer division happens once, in start()).
+struct TilePos {
+  int tile, m_blk, n_tile;
+};
 template <int BN, int MODE>
 struct TileWalker {
   int num_m, num_n, total;
-  int group;  // consecutive tiles (same weight tile, adjacent row blocks) a CTA takes back to back
-  // A CTA's sequence: tiles [cta*G, cta*G + G), then the same offsets one grid*G further, ...
-  __device__ __forceinline__ int first() const { return static_cast<int>(blockIdx.x) * group; }
-  __device__ __forceinline__ int next(int tile) const {
-    return (tile % group != group - 1) ? tile + 1 : tile + 1 - group + static_cast<int>(gridDim.x) * group;
-  }
+  int step_major, step_minor;  // gridDim.x split by the minor dimension's extent
+  // tile -> (m block, n tile). Dense: consecutive CTAs share the weight tile and differ in rows
+  // (minor = m). MoE: every row block has its own expert's weights, so that order shares nothing and
+  // re-reads the whole routing-ordered activation tensor once per column tile (350 MB at 4096 tokens
+  // x top-8, more than L2); instead consecutive CTAs take the column tiles of ONE row block (minor =
+  // n): its activation tile is fetched once and shared through L2, and the second row block of an
+  // expert follows its first closely enough to find the expert's weights (29 MB) still in L2.
+  static constexpr bool kRowBlockMajor = (MODE != kDense);
   __device__ __forceinline__ TileWalker(const GemmParams& p) {
-    group = p.group > 0 ? p.group : 1;
     if constexpr (MODE == kDense) {
       num_m = (p.M + BM - 1) / BM;
       num_n = (p.N + BN - 1) / BN;
@@ -197,25 +177,32 @@ struct TileWalker {
       num_n = (p.N + kColsPerTile - 1) / kColsPerTile;
     }
     total = num_m * num_n;
+    const int minor = kRowBlockMajor ? num_n : num_m;
+    const int g = static_cast<int>(gridDim.x);
+    step_major = minor > 0 ? g / minor : 0;
+    step_minor = minor > 0 ? g - step_major * minor : 0;
   }
-  // tile -> (m block, n tile). Dense: consecutive CTAs share the weight tile and differ in rows.
-  // MoE: every row block has its own expert's weights, so that order shares nothing and re-reads
-  // the whole routing-ordered activation tensor once per column tile (350 MB at 4096 tokens x top-8,
-  // more than L2); instead consecutive CTAs take the column tiles of ONE row block: its activation
-  // tile is fetched once and shared through L2, and the second row block of an expert follows its
-  // first closely enough to find the expert's weights (29 MB) still in L2.
-#ifdef FLYB200_MOE_N_MAJOR
-  static constexpr bool kRowBlockMajor = false;
-#else
-  static constexpr bool kRowBlockMajor = (MODE != kDense);
-#endif
-  __device__ __forceinline__ void decode(int tile, int& m_blk, int& n_tile) const {
-    if constexpr (kRowBlockMajor) {
-      m_blk = tile / num_n;
-      n_tile = tile - m_blk * num_n;
-    } else {
-      n_tile = tile / num_m;
-      m_blk = tile - n_tile * num_m;
+  __device__ __forceinline__ TilePos start() const {
+    TilePos t;
+    t.tile = static_cast<int>(blockIdx.x);
+    const int minor = kRowBlockMajor ? num_n : num_m;
+    const int hi = minor > 0 ? t.tile / minor : 0;
+    const int lo = t.tile - hi * minor;
+    t.m_blk = kRowBlockMajor ? hi : lo;
+    t.n_tile = kRowBlockMajor ? lo : hi;
+    return t;
+  }
+  __device__ __forceinline__ bool valid(const TilePos& t) const { return t.tile < total; }
+  __device__ __forceinline__ void advance(TilePos& t) const {
+    t.tile += static_cast<int>(gridDim.x);
+    int& lo = kRowBlockMajor ? t.n_tile : t.m_blk;
+    int& hi = kRowBlockMajor ? t.m_blk : t.n_tile;
+    const int minor = kRowBlockMajor ? num_n : num_m;
+    lo += step_minor;
+    hi += step_major;
+    if (lo >= minor) {
+      lo -= minor;
+      ++hi;
     }
   }
 };
@@ -244,26 +231,25 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   // (stage it % kStages may be refilled once iteration it - kStages is done) and the epilogue
   // (partials of iteration it are in TMEM). kDone > kStages and >= kAccBufs, so a barrier is never
   // re-armed before every waiter of its previous phase has passed. tempty[b]: the epilogue has read
-  // accumulator buffer b.
+  // accumulator buffer b (one barrier per buffer: every wait costs the single issuing thread about a
+  // hundred cycles). Dense tiles: cfull = the 8 epilogue warps have staged a tile; cfree = the store
+  // warp's TMA store has read the staging tile, which may be overwritten.
   constexpr int kAccBufs = C::kAccBufs;
   constexpr int kDone = kStages + kAccBufs;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto done_bar = [&](uint32_t i) { return bar_base + 8u * (kStages + i); };
-  // half[i] (split tiles only): the first 128 columns of iteration i are in TMEM. tempty[b][h]: the
-  // epilogue has read half h of accumulator buffer b.
-  constexpr int kHalves = C::kHalves;
-  auto half_bar = [&](uint32_t i) { return bar_base + 8u * (kStages + kDone + i); };
-  auto tempty_bar = [&](int b, int h) { return bar_base + 8u * (kStages + 2 * kDone + b * 2 + h); };
-  constexpr int kNumBars = kStages + 2 * kDone + 2 * kAccBufs + 1;
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (kStages + kDone + b); };
+  constexpr int kNumBars = kStages + kDone + kAccBufs + 3;
   static_assert(8 * kNumBars + 8 <= 1024, "barrier area overflows the misc block");
-  const uint32_t epi_bar = bar_base + 8u * (kNumBars - 1);
+  const uint32_t epi_bar = bar_base + 8u * (kNumBars - 3);
+  const uint32_t cfull_bar = bar_base + 8u * (kNumBars - 2);
+  const uint32_t cfree_bar = bar_base + 8u * (kNumBars - 1);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc + 1024 + 8 * kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 1024 + 8 * kNumBars + 4);
   // wait until the stage that iteration `it` is about to overwrite has been consumed
   auto wait_stage_free = [&](uint32_t it, int code) -> bool {
     if (it < static_cast<uint32_t>(kStages)) return true;
     const uint32_t j = it - kStages;
-    if (kHalves == 2 && !mbar_wait(half_bar(j % kDone), (j / kDone) & 1, abort_flag, p.err, code)) return false;
     return mbar_wait(done_bar(j % kDone), (j / kDone) & 1, abort_flag, p.err, code);
   };
 
@@ -272,10 +258,10 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) mbar_init(full_bar(s), gather_a ? 3 : 1);
     for (int i = 0; i < kDone; ++i) mbar_init(done_bar(i), 1);
-    for (int i = 0; i < kDone; ++i) mbar_init(half_bar(i), 1);
-    for (int b = 0; b < kAccBufs; ++b)
-      for (int h = 0; h < 2; ++h) mbar_init(tempty_bar(b, h), kEpiWarps);  // one arrival per warp
+    for (int b = 0; b < kAccBufs; ++b) mbar_init(tempty_bar(b), kEpiWarps);  // one arrival per warp
     mbar_init(epi_bar, kEpiWarps);
+    mbar_init(cfull_bar, kEpiWarps);
+    mbar_init(cfree_bar, 1);
     *abort_flag = 0;
     fence_proxy_async_smem();
     fence_barrier_init();
@@ -291,6 +277,12 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Everything above touched no global memory, so it may overlap the tail of the previous kernel in
+  // the stream (programmatic dependent launch); nothing below starts before that kernel's results
+  // are visible. The next kernel may begin its own set-up as soon as SMs become free.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
   const TileWalker<BN, MODE> walk(p);
   const int KB = p.K / BK;
 
@@ -303,9 +295,8 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // ---------------- producer: weights (and dense A) via TMA ----------------
       uint32_t it = 0;
       bool alive = true;
-      for (int tile = walk.first(); tile < walk.total && alive; tile = walk.next(tile)) {
-        int m_blk, n_tile;
-        walk.decode(tile, m_blk, n_tile);
+      for (TilePos pos = walk.start(); walk.valid(pos) && alive; walk.advance(pos)) {
+        const int m_blk = pos.m_blk, n_tile = pos.n_tile;
         const uint8_t* wbase = p.b;
         int rows_b;  // weight rows this tile brings per column group
         size_t row_stride_kb;  // bytes between consecutive K blocks of the repacked weight
@@ -338,12 +329,6 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint32_t sa = smem_base + s * C::kStageBytes;
           const uint32_t sb = sa + kATileBytes;
           const uint8_t* src = wbase + kb * row_stride_kb + static_cast<size_t>(n0) * BK;
-#ifdef FLYB200_DBG_NO_LOAD
-          if (it >= static_cast<uint32_t>(kStages)) {  // experiment: MMAs re-read stale stages
-            mbar_arrive(full_bar(s));
-            continue;
-          }
-#endif
           if constexpr (MODE == kDense) {
             mbar_arrive_expect_tx(full_bar(s), p.a_box_rows * BK + rows_b * BK);
             tma_load_2d(sa, &tmap_a, kb * BK, m_blk * BM, full_bar(s));
@@ -361,20 +346,18 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
         }
       }
-    } else if ((warp == 1 || (kHalves == 2 && warp == 2)) && lane == 0) {
+    } else if (warp == 1 && lane == 0) {
       // ---------------- MMA issuer ----------------
-      // Split tiles have two issuers: warp 1 feeds columns [0, BN/2) of every K block, warp 2 the
-      // rest, each with its own commit, so that the instruction-issue cost (tens of cycles per
-      // tcgen05.mma, serial in one thread) is spread over two threads.
-      const int h = (kHalves == 2 && warp == 2) ? 1 : 0;
-      constexpr uint32_t idesc = umma_idesc_e4m3_f32(BM, BN / kHalves);
+      // One thread issues every MMA of the CTA. (Per K block it spends ~60-100 cycles in each barrier
+      // wait, ~64 per tcgen05.mma and ~50-100 in the commit, less than the 512 cycles the tensor core
+      // needs; a second issuing thread taking alternate K blocks was measured to change nothing,
+      // the epilogue being the slower side.)
+      constexpr uint32_t idesc = umma_idesc_e4m3_f32(BM, BN);
       uint32_t it = 0;
       bool alive = true;
-      for (int tile = walk.first(); tile < walk.total && alive; tile = walk.next(tile)) {
+      for (TilePos pos = walk.start(); walk.valid(pos) && alive; walk.advance(pos)) {
         if constexpr (MODE != kDense) {
-          int m_blk, n_tile;
-          walk.decode(tile, m_blk, n_tile);
-          const int e = p.expert_ids[m_blk];
+          const int e = p.expert_ids[pos.m_blk];
           if (e < 0 || e >= p.experts) continue;
         }
         for (int kb = 0; kb < KB; ++kb, ++it) {
@@ -382,33 +365,44 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint32_t ph = (it / kStages) & 1;
           const int buf = it % kAccBufs;
           const uint32_t tph = (it / kAccBufs) & 1;
-          if (!mbar_wait(tempty_bar(buf, h), tph ^ 1, abort_flag, p.err, kErrWaitTmemEmpty) ||
-              !mbar_wait(full_bar(s), ph, abort_flag, p.err, kErrWaitSmemFull)) {
+          const uint32_t sa = smem_base + s * C::kStageBytes;
+          const uint64_t adesc = umma_desc_sw128(sa);
+          const uint64_t bdesc = umma_desc_sw128(sa + kATileBytes);
+          const uint32_t d = tmem_base + buf * BN;
+          // The operands normally landed long ago; the accumulator buffer is what the issuer really
+          // waits for, so that wait comes last and nothing but the fence separates it from the MMAs.
+          if (!mbar_wait(full_bar(s), ph, abort_flag, p.err, kErrWaitSmemFull) ||
+              !mbar_wait(tempty_bar(buf), tph ^ 1, abort_flag, p.err, kErrWaitTmemEmpty)) {
             alive = false;
             break;
           }
-          if (h == 0) FLYB200_TRACE(1, it);
           tc_fence_after();
-          const uint32_t sa = smem_base + s * C::kStageBytes;
-          const uint64_t adesc = umma_desc_sw128(sa);
-          const uint64_t bdesc = umma_desc_sw128(sa + kATileBytes + h * (BN / 2) * BK);
-#ifdef FLYB200_DBG_SAMEBUF
-          const uint32_t d = tmem_base + h * (BN / 2);
-#else
-          const uint32_t d = tmem_base + buf * BN + h * (BN / 2);
-#endif
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k)
-#ifdef FLYB200_DBG_ACC1
-            tc_mma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, 1u);
-#else
             tc_mma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
-#endif
-          // this issuer's MMAs of the K block are done: partial sums in TMEM, operands consumed
-          tc_commit((kHalves == 2 && h == 0) ? half_bar(it % kDone) : done_bar(it % kDone));
-          if (h == 0) FLYB200_TRACE(2, it);
+          // the MMAs of the K block are done: partial sums in TMEM, operands consumed
+          tc_commit(done_bar(it % kDone));
         }
       }
+    } else if (MODE == kDense && C::kStaged && warp == 2 && lane == 0) {
+      // ---------------- dense: output store ----------------
+      // One thread turns every staged tile into TMA stores, so the epilogue warps neither wait for
+      // one another nor for the store engine at a tile boundary: they signal cfull and go on to the
+      // next tile's first K block; cfree tells them when the staging tile may be overwritten.
+      uint32_t n = 0;
+      for (TilePos pos = walk.start(); walk.valid(pos); walk.advance(pos), ++n) {
+        const int m_blk = pos.m_blk;
+        if (!mbar_wait(cfull_bar, n & 1, abort_flag, p.err, kErrWaitEpilogue)) break;
+        const int n0 = pos.n_tile * BN;
+#pragma unroll
+        for (int reg = 0; reg < C::kRegions; ++reg)
+          if (n0 + reg * 64 < p.N)
+            tma_store_2d(&tmap_c, cstage_base + reg * kRegionBytes, n0 + reg * 64, m_blk * BM);
+        bulk_commit_group();
+        bulk_wait_group_read0();
+        mbar_arrive(cfree_bar);
+      }
+      bulk_wait_group0();  // every store has been written before the CTA exits
     } else if (MODE != kDense && warp >= 2 && gather_a) {
       // ---------------- MoE: gather activation rows with cp.async ----------------
       // Thread g owns rows g and g+64 of the tile; row r, 16-byte chunk c lands at
@@ -419,9 +413,8 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t it = 0, published = 0;
       bool alive = true;
       const size_t row_bytes = static_cast<size_t>(p.K);
-      for (int tile = walk.first(); tile < walk.total && alive; tile = walk.next(tile)) {
-        int m_blk, n_tile;
-        walk.decode(tile, m_blk, n_tile);
+      for (TilePos pos = walk.start(); walk.valid(pos) && alive; walk.advance(pos)) {
+        const int m_blk = pos.m_blk;
         const int e = p.expert_ids[m_blk];
         if (e < 0 || e >= p.experts) continue;
         const uint8_t* src_row[2];
@@ -486,7 +479,6 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int r = quad * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     OutT* const out = reinterpret_cast<OutT*>(p.out);
-    const bool store_thread = (threadIdx.x == kEpiWarp0 * 32);
 
     uint32_t it = 0;
     uint32_t epi_phase = 0;
@@ -500,14 +492,15 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       return __all_sync(0xffffffffu, ok);
     };
 
-    // What the promotion loop needs per tile: where this thread's scales live (32-bit indices, so
-    // that few registers stay live across the loop; addresses are formed at use).
+    // What the promotion loop needs per tile: where this thread's scales of K block 0 live. The loop
+    // only bumps these pointers: a warp that runs a chain of dependent scalar instructions issues one
+    // every 4-6 cycles, so index arithmetic per K block shows up directly in the K-block period.
+    // Rows without a valid token read the scales of row 0 (their results are never stored).
     struct ScaleCtx {
-      int sa_idx;      // scale_a[kb * sa_stride + sa_idx]
-      int sa_stride;
-      int sb_idx0;     // scale_b[sb_idx0 + kb] for column group 0
-      int sb_idx1;     // ... group 1
-      bool row_ok;
+      const float* sa;     // scale_a of this thread's row; K block kb at sa + kb * sa_step
+      const float* sb0;    // scale_b of column group 0; K block kb at sb0 + kb
+      const float* sb1;    // ... group 1
+      long long sa_step;
     };
     // What the store phase needs; recomputed after the loop instead of being kept live through it.
     struct OutCtx {
@@ -530,52 +523,53 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       return true;
     };
     // Fills the scale context of `tile`; false if the tile has nothing to do (MoE block without expert).
-    auto setup_scales = [&](int tile, ScaleCtx& c) -> bool {
-      int m_blk, n_tile;
-      walk.decode(tile, m_blk, n_tile);
+    auto setup_scales = [&](const TilePos& pos, ScaleCtx& c) -> bool {
+      const int m_blk = pos.m_blk, n_tile = pos.n_tile;
+      long long sa_idx, sb_idx0, sb_idx1;
       if constexpr (MODE == kDense) {
         const int row = m_blk * BM + r;
-        c.row_ok = row < p.M;
-        c.sa_idx = c.row_ok ? row : 0;
-        c.sa_stride = p.M;
+        sa_idx = row < p.M ? row : 0;
+        c.sa_step = p.M;
         const int n0 = n_tile * BN;
         const int nblk_max = (p.N + 127) / 128 - 1;
-        c.sb_idx0 = min((n0 + half * CH) / 128, nblk_max) * KB;
-        c.sb_idx1 = min((n0 + BN / 2 + half * CH) / 128, nblk_max) * KB;
+        sb_idx0 = static_cast<long long>(min((n0 + half * CH) / 128, nblk_max)) * KB;
+        sb_idx1 = static_cast<long long>(min((n0 + BN / 2 + half * CH) / 128, nblk_max)) * KB;
       } else {
         const int e = p.expert_ids[m_blk];
         if (e < 0 || e >= p.experts) return false;
         int t, slot;
-        c.row_ok = moe_row(m_blk, t, slot);
+        moe_row(m_blk, t, slot);   // (0, 0) for rows without a valid token
         if (p.a_sorted) {   // scales follow the permuted activations: one per sorted row
-          c.sa_idx = m_blk * p.tile_m + (r < p.tile_m ? r : 0);
-          c.sa_stride = p.a_rows;
+          sa_idx = static_cast<long long>(m_blk) * p.tile_m + (r < p.tile_m ? r : 0);
+          c.sa_step = p.a_rows;
         }
         if constexpr (MODE == kMoe1) {
           if (!p.a_sorted) {
-            c.sa_idx = t;
-            c.sa_stride = p.M;
+            sa_idx = t;
+            c.sa_step = p.M;
           }
-          const int nb_exp = (2 * p.N) / 128;  // scale rows per expert
+          const long long nb_exp = (2 * p.N) / 128;  // scale rows per expert
           const int cg = min(n_tile * (BN / 2) + half * CH, p.N - 1);
-          c.sb_idx0 = (e * nb_exp + cg / 128) * KB;
-          c.sb_idx1 = (e * nb_exp + (p.N + cg) / 128) * KB;
+          sb_idx0 = (e * nb_exp + cg / 128) * KB;
+          sb_idx1 = (e * nb_exp + (p.N + cg) / 128) * KB;
         } else {
           if (!p.a_sorted) {
-            c.sa_idx = t * p.topk + slot;
-            c.sa_stride = p.M * p.topk;
+            sa_idx = static_cast<long long>(t) * p.topk + slot;
+            c.sa_step = static_cast<long long>(p.M) * p.topk;
           }
           const int n0 = n_tile * BN;
-          const int nb_exp = p.N / 128;
-          c.sb_idx0 = (e * nb_exp + min(n0 + half * CH, p.N - 1) / 128) * KB;
-          c.sb_idx1 = (e * nb_exp + min(n0 + BN / 2 + half * CH, p.N - 1) / 128) * KB;
+          const long long nb_exp = p.N / 128;
+          sb_idx0 = (e * nb_exp + min(n0 + half * CH, p.N - 1) / 128) * KB;
+          sb_idx1 = (e * nb_exp + min(n0 + BN / 2 + half * CH, p.N - 1) / 128) * KB;
         }
       }
+      c.sa = p.scale_a + sa_idx;
+      c.sb0 = p.scale_b + sb_idx0;
+      c.sb1 = p.scale_b + sb_idx1;
       return true;
     };
-    auto setup_output = [&](int tile, OutCtx& c) {
-      int m_blk, n_tile;
-      walk.decode(tile, m_blk, n_tile);
+    auto setup_output = [&](const TilePos& pos, OutCtx& c) {
+      const int m_blk = pos.m_blk, n_tile = pos.n_tile;
       c.m_blk = m_blk;
       c.route_w = 1.0f;
       if constexpr (MODE == kDense) {
@@ -603,46 +597,69 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
       }
     };
-    // first tile >= `tile` (stepping by the grid) that has work; walk.total if none
-    auto find_tile = [&](int tile, ScaleCtx& c) -> int {
-      while (tile < walk.total && !setup_scales(tile, c)) tile = walk.next(tile);
-      return tile < walk.total ? tile : walk.total;
+    // first position at or after `pos` (stepping by the grid) that has work
+    auto find_tile = [&](TilePos& pos, ScaleCtx& c) {
+      while (walk.valid(pos) && !setup_scales(pos, c)) walk.advance(pos);
     };
-    auto ld_sa = [&](const ScaleCtx& c, int kb) -> float {
-      return (kb < KB && c.row_ok)
-                 ? __ldg(p.scale_a + static_cast<size_t>(kb) * c.sa_stride + c.sa_idx) : 0.f;
-    };
-    auto ld_sb = [&](int idx, int kb) -> float { return kb < KB ? __ldg(p.scale_b + idx + kb) : 0.f; };
 
     // Scales are prefetched kRing K blocks ahead into a register ring; the ring of the NEXT tile is
     // loaded before the current tile's store phase so that its latency hides behind the stores.
     constexpr int kRing = 2;
     ScaleCtx cur;
     float ring_a[kRing], ring_b0[kRing], ring_b1[kRing];
-    int tile = find_tile(walk.first(), cur);
-    if (tile < walk.total) {
+    TilePos pos = walk.start();
+    find_tile(pos, cur);
+    if (walk.valid(pos)) {
 #pragma unroll
       for (int j = 0; j < kRing; ++j) {
-        ring_a[j] = ld_sa(cur, j);
-        ring_b0[j] = ld_sb(cur.sb_idx0, j);
-        ring_b1[j] = ld_sb(cur.sb_idx1, j);
+        const int kb = j < KB ? j : 0;
+        ring_a[j] = __ldg(cur.sa + kb * cur.sa_step);
+        ring_b0[j] = __ldg(cur.sb0 + kb);
+        ring_b1[j] = __ldg(cur.sb1 + kb);
       }
     }
 
-#ifndef FLYB200_LD_WIDE
-#define FLYB200_LD_WIDE 16
-#endif
-    constexpr int LDW = (CH > 32) ? FLYB200_LD_WIDE : CH;  // columns per tcgen05.ld
+    // Columns per tcgen05.ld. Measured on B200 (MMA issuer + epilogue alone, no loads): 16-, 32- and
+    // 64-column loads give the same K-block period (608-630 cycles against 512 of MMA) -- the TMEM
+    // read path moves one 32-lane column per cycle and sub-partition, 256 cycles per 128 x 256 block,
+    // whatever the instruction width -- so the narrowest pipelined load, which needs the fewest
+    // registers, stays.
+    constexpr int LDW = (CH > 32) ? 16 : CH;
     constexpr int NSUB = CH / LDW;            // loads per column group
     constexpr int NQ = 2 * NSUB;              // loads per K block (two column groups)
+    uint32_t tiles_done = 0;                  // dense: tiles this CTA has staged so far
+    uint32_t dn_i = 0, dn_ph = 0;             // it % kDone and (it / kDone) & 1, kept as counters
 
-    while (tile < walk.total && alive) {
+    while (walk.valid(pos) && alive) {
       // acc[0 .. CH/2) = column group 0, acc[CH/2 .. CH) = column group 1, two columns per float2.
       float2 acc[CH];
 #pragma unroll
       for (int j = 0; j < CH; ++j) acc[j] = make_float2(0.f, 0.f);
+      // addresses of the scales that the next prefetch takes (K block kRing of this tile)
+      const float* pf_a = cur.sa + kRing * cur.sa_step;
+      const float* pf_b0 = cur.sb0 + kRing;
+      const float* pf_b1 = cur.sb1 + kRing;
+      const long long pf_step = cur.sa_step;
 
+      ScaleCtx nxt;
+      float nring_a[kRing], nring_b0[kRing], nring_b1[kRing];
+      TilePos npos = pos;
       for (int kb0 = 0; kb0 < KB && alive; kb0 += kRing) {
+        if (kb0 + kRing >= KB) {
+          // last trip: the next tile's scale context and first scales are fetched now, so that their
+          // latency is over when the store phase ends
+          walk.advance(npos);
+          find_tile(npos, nxt);
+          if (walk.valid(npos)) {
+#pragma unroll
+            for (int j = 0; j < kRing; ++j) {
+              const int kbn = j < KB ? j : 0;
+              nring_a[j] = __ldg(nxt.sa + kbn * nxt.sa_step);
+              nring_b0[j] = __ldg(nxt.sb0 + kbn);
+              nring_b1[j] = __ldg(nxt.sb1 + kbn);
+            }
+          }
+        }
 #pragma unroll
         for (int j = 0; j < kRing; ++j) {
           const int kb = kb0 + j;
@@ -650,97 +667,64 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const int buf = it % kAccBufs;
             const float s0 = ring_a[j] * ring_b0[j];
             const float s1 = ring_a[j] * ring_b1[j];
-            ring_a[j] = ld_sa(cur, kb + kRing);
-            ring_b0[j] = ld_sb(cur.sb_idx0, kb + kRing);
-            ring_b1[j] = ld_sb(cur.sb_idx1, kb + kRing);
+            if (kb + kRing < KB) {
+              ring_a[j] = __ldg(pf_a);
+              ring_b0[j] = __ldg(pf_b0);
+              ring_b1[j] = __ldg(pf_b1);
+            }
+            pf_a += pf_step;
+            ++pf_b0;
+            ++pf_b1;
             const uint32_t t0 = tmem_base + lane_base + buf * BN + half * CH;
-            // Loads of LDW columns are software-pipelined against the FMAs of the previous load (two
-            // register buffers). Measured on B200: wider single-shot loads (32/64 columns per wait)
-            // are slower -- the TMEM read port, not latency, bounds a K block at roughly 350
-            // cycles, and the extra registers spill.
             auto taddr = [&](int q) {  // load q: q < NSUB -> group 0, else group 1
               return t0 + (q >= NSUB ? BN / 2 : 0) + (q % NSUB) * LDW;
             };
-            constexpr int NL = NQ / kHalves;  // loads per wait segment
+            // warp-uniform outcome: the tcgen05.ld below needs the whole warp
+            const bool got = mbar_wait(done_bar(dn_i), dn_ph, abort_flag, p.err, kErrWaitTmemFull);
+            if (!__all_sync(0xffffffffu, got)) {
+              alive = false;
+              break;
+            }
+            tc_fence_after();
+            // Loads of LDW columns are software-pipelined against the FMAs of the previous load (two
+            // register buffers); the buffer goes back to the issuer as soon as the last load landed.
+            uint32_t va[LDW], vb[LDW];
+            tmem_ld<LDW>(taddr(0), va);
+            tmem_wait_dep<LDW>(va);
+            auto release = [&]() {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(tempty_bar(buf));
+            };
 #pragma unroll
-            for (int h = 0; h < kHalves; ++h) {
-              if (!alive) break;
-              // warp-uniform outcome: the tcgen05.ld below needs the whole warp
-              const bool got = mbar_wait((kHalves == 2 && h == 0) ? half_bar(it % kDone) : done_bar(it % kDone),
-                                         (it / kDone) & 1, abort_flag, p.err, kErrWaitTmemFull);
-              if (!__all_sync(0xffffffffu, got)) {
-                alive = false;
-                break;
-              }
-              if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(3, it);
-              tc_fence_after();
-#ifdef FLYB200_DBG_SKIP_PROMOTE
-              if (kb + 1 < KB) {
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                  mbar_arrive(tempty_bar(buf, h));
-                  if (kHalves == 1) mbar_arrive(tempty_bar(buf, 1));
-                }
-                continue;
-              }
-#endif
-              uint32_t va[LDW], vb[LDW];
-              tmem_ld<LDW>(taddr(h * NL), va);
-              tmem_wait_dep<LDW>(va);
-              auto release = [&]() {  // every load of this segment has landed: hand the columns back
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                  mbar_arrive(tempty_bar(buf, h));
-                  if (kHalves == 1) mbar_arrive(tempty_bar(buf, 1));
-                }
-                if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(4, it);
-              };
-              if (NL == 1) release();
+            for (int q = 0; q < NQ; ++q) {
+              uint32_t* cv = (q & 1) ? vb : va;
+              uint32_t* nv = (q & 1) ? va : vb;
+              if (q + 1 < NQ) tmem_ld<LDW>(taddr(q + 1), nv);   // in flight during the FMAs
+              const float s = (q >= NSUB) ? s1 : s0;
+              const float2 s2 = make_float2(s, s);
+              float2* a = acc + (q >= NSUB ? CH / 2 : 0) + (q % NSUB) * (LDW / 2);
 #pragma unroll
-              for (int ql = 0; ql < NL; ++ql) {
-                const int q = h * NL + ql;
-                uint32_t* cv = (ql & 1) ? vb : va;
-                uint32_t* nv = (ql & 1) ? va : vb;
-                if (ql + 1 < NL) tmem_ld<LDW>(taddr(q + 1), nv);   // in flight during the FMAs
-                const float s = (q >= NSUB) ? s1 : s0;
-                const float2 s2 = make_float2(s, s);
-                float2* a = acc + (q >= NSUB ? CH / 2 : 0) + (q % NSUB) * (LDW / 2);
-#pragma unroll
-                for (int c = 0; c < LDW / 2; ++c)
-                  a[c] = __ffma2_rn(make_float2(__uint_as_float(cv[2 * c]),
-                                                __uint_as_float(cv[2 * c + 1])), s2, a[c]);
-                if (ql + 1 < NL) {
-                  tmem_wait_dep<LDW>(nv);
-                  if (ql + 2 == NL) release();
-                }
+              for (int c = 0; c < LDW / 2; ++c)
+                a[c] = __ffma2_rn(make_float2(__uint_as_float(cv[2 * c]),
+                                              __uint_as_float(cv[2 * c + 1])), s2, a[c]);
+              if (q + 1 < NQ) {
+                tmem_wait_dep<LDW>(nv);
+                if (q + 2 == NQ) release();
               }
             }
-            if (alive) {
-              ++it;
+            ++it;
+            if (++dn_i == kDone) {
+              dn_i = 0;
+              dn_ph ^= 1;
             }
           }
         }
       }
       if (!alive) break;
 
-      if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(0, it);
-      // next tile's scale context and first scales: issued now, consumed after the store phase
-      ScaleCtx nxt;
-      float nring_a[kRing], nring_b0[kRing], nring_b1[kRing];
-      const int tile_next = find_tile(walk.next(tile), nxt);
-      if (tile_next < walk.total) {
-#pragma unroll
-        for (int j = 0; j < kRing; ++j) {
-          nring_a[j] = ld_sa(nxt, j);
-          nring_b0[j] = ld_sb(nxt.sb_idx0, j);
-          nring_b1[j] = ld_sb(nxt.sb_idx1, j);
-        }
-      }
-
       OutCtx oc;
-      setup_output(tile, oc);
+      setup_output(pos, oc);
       const bool row_ok = oc.row_ok;
       const int m_blk = oc.m_blk;
       const int n0 = oc.n0, col0 = oc.col0, col1 = oc.col1;
@@ -749,13 +733,18 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const float* accf = reinterpret_cast<const float*>(acc);  // [0,CH) group 0, [CH,2CH) group 1
       // ---- output ----
       if constexpr (C::kStaged) {
-        // (1) the staging tile must be free: previous TMA store has read it / previous tile's
-        //     cooperative row stores are done (every thread passes this barrier after its own)
+        // (1) the staging tile must be free. Dense: the store warp's TMA store of the previous tile
+        //     has read it (cfree; 16 K blocks have passed, so this wait is normally over at once).
+        //     MoE: the previous tile's cooperative row stores are done (every thread passes this
+        //     barrier after its own).
         if constexpr (MODE == kDense) {
-          if (store_thread) bulk_wait_group_read0();
+          if (tiles_done > 0) {
+            const bool ok = mbar_wait(cfree_bar, (tiles_done - 1) & 1, abort_flag, p.err, kErrWaitEpilogue);
+            if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+          }
+        } else {
+          if (!epi_sync()) { alive = false; break; }
         }
-        if (!epi_sync()) { alive = false; break; }
-        if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(5, it);
         // (2) thread r writes its columns of row r into the swizzled staging tile
         auto stage8 = [&](int col, const float* v) {   // col: tile-relative output column, % 8 == 0
           const uint32_t addr = cstage_base + (col >> 6) * kRegionBytes + r * 128 +
@@ -872,25 +861,17 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
           }
         }
-        if (!tile_stored) {
-          if constexpr (MODE != kDense) {
-            if (half == 0) row_off[r] = row_ok ? static_cast<long long>(out_row) : -1LL;
-          } else {
-            fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA store
-          }
-          if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(6, it);
+        if constexpr (MODE == kDense) {
+          // (3) hand the staged tile to the store warp and go on with the next tile
+          fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA store
+          __syncwarp();
+          if (lane == 0) mbar_arrive(cfull_bar);
+          ++tiles_done;
+        } else if (!tile_stored) {
+          if (half == 0) row_off[r] = row_ok ? static_cast<long long>(out_row) : -1LL;
           if (!epi_sync()) { alive = false; break; }
-          if (threadIdx.x == kEpiWarp0 * 32) FLYB200_TRACE(7, it);
           // (3) write the tile out
-          if constexpr (MODE == kDense) {
-            if (store_thread) {
-#pragma unroll
-              for (int reg = 0; reg < C::kRegions; ++reg)
-                if (n0 + reg * 64 < p.N)
-                  tma_store_2d(&tmap_c, cstage_base + reg * kRegionBytes, n0 + reg * 64, m_blk * BM);
-              bulk_commit_group();
-            }
-          } else {
+          {
             constexpr int CPR = C::kOutCols / 8;   // 16-byte chunks per output row
             constexpr int RPI = 32 / CPR;          // rows per warp instruction
             const int rows = min(BM, p.tile_m);
@@ -962,10 +943,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         ring_b0[j] = nring_b0[j];
         ring_b1[j] = nring_b1[j];
       }
-      tile = tile_next;
-    }
-    if constexpr (C::kStaged && MODE == kDense) {
-      if (store_thread) bulk_wait_group0();  // the last tile's TMA store must finish before exit
+      pos = npos;
     }
   }
 
@@ -1037,8 +1015,17 @@ static int launch(const CUtensorMap& tmap_a, const CUtensorMap& tmap_c, const Ge
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
     configured_dev = dev;
   }
-  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(tmap_a, tmap_c, p);
-  FLYB200_CUDA_CHECK(cudaGetLastError());
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  FLYB200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmap_a, tmap_c, p));
   return FLYB200_OK;
 }
 
@@ -1105,12 +1092,6 @@ bool decode_path_pays_off(int M, int N, int K);
 }  // namespace flyb200
 
 using namespace flyb200;
-
-#ifdef FLYB200_DBG_TRACE
-extern "C" int flyb200_debug_read_trace(long long* host, int n) {
-  return cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * n) == cudaSuccess ? 0 : -3;
-}
-#endif
 
 extern "C" int flyb200_blockscale_gemm(void* c, const void* a, const void* b_repacked,
                                        const float* scale_a_t, const float* scale_b, int32_t M,
@@ -1193,12 +1174,6 @@ static int moe_common_checks(const void* out, const void* x, const void* w, cons
   return FLYB200_OK;
 }
 
-// Tiles a CTA takes back to back (TileWalker::group). Measured on the 256-expert layer: taking the
-// adjacent row blocks of an expert on ONE CTA (so the second finds the weight tile in L2) is slower
-// (4.25 ms) than letting neighbouring CTAs fetch the tile at the same time (3.75 ms), so the
-// grouping stays at 1.
-static int moe_tile_group(int, int, int, int) { return 1; }
-
 // cfg.path of the MoE entry points is a bit set: bit 0 = the activation argument is already in
 // routing order ([T*k + E*tile_m - k, K] rows, scales [K/128, same rows]) and is fetched by TMA;
 // bit 1 (stage 1 only) = write the output in routing order too.
@@ -1267,7 +1242,6 @@ static int moe_gemm1_impl(void* out, void* out_q, float* out_scale_t, const void
   p.experts = E; p.doweight = doweight; p.accumulate = 0;
   CUtensorMap tmap{};
   if ((rc = moe_sorted_layout(cfg, T, E, k, tile_m, H, x, &p, &tmap))) return rc;
-  p.group = moe_tile_group(T, k, E, tile_m);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (out_dtype == FLYB200_BF16)
     return launch_bn<kMoe1, __nv_bfloat16>(bn, tmap, tmap, p, grid, st);
@@ -1333,7 +1307,6 @@ extern "C" int flyb200_moe_gemm2(void* out, const void* a2, const void* w_repack
   p.experts = E; p.doweight = doweight; p.accumulate = accumulate ? 1 : 0;
   CUtensorMap tmap{};
   if ((rc = moe_sorted_layout(cfg, T, E, k, tile_m, I, a2, &p, &tmap))) return rc;
-  p.group = moe_tile_group(T, k, E, tile_m);
   if (p.out_sorted)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "stage 2 has no sorted output layout (cfg.path bit 1)");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
