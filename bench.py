@@ -22,8 +22,13 @@ from its own weight shard, no collective (strong scaling). Rank 0 prints ONE JSO
   sweep/moe  extra measurements (dense M-sweep of the three (N,K) pairs; the 256-expert top-8 MoE
              layer) so the whole scope is measured in one run; skipped with --no-extras
 
+  check      outside every timed region the result of the headline GEMM (each rank: its column shard)
+             and a handful of MoE tokens are compared with the CPU oracle on the same seeded inputs;
+             a miss of the parity bar (max|d|/max|ref| <= 1e-2, cosine >= 0.9999) fails the run
+
 ``--impl reference`` times the reference's own path for this workload, which is its torch CPU
-oracle (its kernels are AMD-only), on the host cores.
+oracle (its kernels are AMD-only), on the host cores, on the same seeded operands, for exactly
+``--steps`` timed and ``--warmup`` untimed passes.
 """
 from __future__ import annotations
 
@@ -114,8 +119,38 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------
-# workload construction (synthetic, seeded; values follow the BASELINE distributions)
+# workload construction (synthetic, seeded): A ~ N(0,1) with 1x128 scales, B ~ N(0,0.02) with
+# 128x128 block scales, amax/448 -- the distributions the headline configuration names
 # ------------------------------------------------------------------------------------------------
+MAX_REL, MIN_COS = 1e-2, 0.9999   # parity bar of the in-bench check (same as tests/helpers.py)
+
+
+def workload_config(M, N, K, world):
+    """The keys that identify the workload; printed identically by both arms."""
+    return {"workload": f"dense_fp8_blockscale_M{M}_N{N}_K{K}", "sharding": f"N/{world} columns per GPU",
+            "scales": "1x128 act, 128x128 weight, fp32", "inputs": "seed 0: A~N(0,1), B~N(0,0.02), amax/448 e4m3"}
+
+
+def make_dense_host(M, N, K, seed=0):
+    """The headline operands, generated on the CPU so that the GPU arm and the CPU arm compute on the
+    same bytes: (a_q [M,K] fp8, a_scale [M,K/128], b_q [N,K] fp8, b_scale [N/128,K/128])."""
+    g = torch.Generator().manual_seed(seed)
+    a_q, a_s = quant_1x128_torch(torch.randn(M, K, generator=g))
+    npad = ((N + 127) // 128) * 128
+    b = torch.zeros(npad, K)
+    b[:N] = torch.randn(N, K, generator=g) * 0.02
+    b_q, b_s = block_quant_torch(b)
+    return a_q, a_s.contiguous(), b_q[:N].contiguous(), b_s.contiguous()
+
+
+def parity(out, ref):
+    """(max|out-ref| / max|ref|, cosine) of two tensors, in float64 on the CPU."""
+    o, r = out.detach().double().cpu().flatten(), ref.detach().double().cpu().flatten()
+    denom = r.abs().max().item() or 1.0
+    mr = (o - r).abs().max().item() / denom
+    cs = (o @ r).item() / max(o.norm().item() * r.norm().item(), 1e-300)
+    return mr, cs
+
 def quant_1x128_torch(x):
     """1x128 amax quantisation with torch ops on the GPU (input generation only)."""
     r, c = x.shape
@@ -136,23 +171,17 @@ def block_quant_torch(w):
 
 
 def make_dense_gpu(M, N, K, dev, seed=0, n_lo=0, n_hi=None):
-    """A ~ N(0,1) 1x128-quantised, B ~ N(0,0.02) 128x128-quantised; rows [n_lo, n_hi) of B kept."""
+    """The headline operands on the device; rows [n_lo, n_hi) of B (this rank's column shard) kept.
+    The host copies stay in the dict for the oracle check."""
     from flydsl_b200.utils import shuffle_weight
 
     n_hi = N if n_hi is None else n_hi
-    g = torch.Generator(device=dev).manual_seed(seed)
-    a = torch.randn(M, K, generator=g, device=dev)
-    a_q, a_s = quant_1x128_torch(a)
-    del a
-    npad = ((N + 127) // 128) * 128
-    b = torch.zeros(npad, K, device=dev)
-    b[:N] = torch.randn(N, K, generator=g, device=dev) * 0.02
-    b_q, b_s = block_quant_torch(b)
-    del b
+    a_q, a_s, b_q, b_s = make_dense_host(M, N, K, seed)
     b_q = b_q[n_lo:n_hi].contiguous()
     b_s = b_s[n_lo // 128:(n_hi + 127) // 128].contiguous()
-    return {"a_q": a_q, "a_scale_t": a_s.t().contiguous(), "b_q": b_q, "b_sh": shuffle_weight(b_q),
-            "b_scale": b_s}
+    return {"a_q": a_q.to(dev), "a_scale_t": a_s.t().contiguous().to(dev), "b_q": b_q.to(dev),
+            "b_sh": shuffle_weight(b_q.to(dev)), "b_scale": b_s.to(dev),
+            "host": {"a_q": a_q, "a_scale": a_s, "b_q": b_q, "b_scale": b_s}}
 
 
 def time_steps(fn, steps, warmup, flush):
@@ -231,13 +260,9 @@ def barrier(world):
 
 def cpu_baseline_dense(M, N, K, budget_s=12.0):
     """The CPU oracle on the host cores: full workload, repeated while the budget allows."""
-    from oracle import blockscale_ref as O  # CPU-baseline leg: the one place bench executes oracle/
+    from oracle import blockscale_ref as O  # CPU-baseline leg: bench executes oracle/ here and in the checks
 
-    g = torch.Generator().manual_seed(0)
-    a_q = (torch.randn(M, K, generator=g)).clamp(-3, 3).to(torch.float8_e4m3fn)
-    b_q = (torch.randn(N, K, generator=g)).clamp(-3, 3).to(torch.float8_e4m3fn)
-    a_s = torch.rand(M, K // 128, generator=g)
-    b_s = torch.rand((N + 127) // 128, K // 128, generator=g)
+    a_q, a_s, b_q, b_s = make_dense_host(M, N, K, seed=0)
     O.run_torch_blockscale(a_q[:64], b_q, a_s[:64], b_s)  # warm-up (thread pool, allocator)
     times, t_start = [], time.perf_counter()
     while True:
@@ -253,7 +278,8 @@ def cpu_baseline_dense(M, N, K, budget_s=12.0):
 
 
 def run_reference(args):
-    """The reference's path for this workload on this box = its torch CPU oracle (restated port)."""
+    """The reference's path for this workload on this box = its torch CPU oracle (restated port), on
+    the operands of the GPU arm, for exactly --warmup untimed and --steps timed passes."""
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
@@ -262,33 +288,57 @@ def run_reference(args):
     torch.set_num_threads(os.cpu_count() or 1)
     from oracle import blockscale_ref as O
 
-    g = torch.Generator().manual_seed(0)
-    a_q = torch.randn(M, K, generator=g).clamp(-3, 3).to(torch.float8_e4m3fn)
-    b_q = torch.randn(N, K, generator=g).clamp(-3, 3).to(torch.float8_e4m3fn)
-    a_s = torch.rand(M, K // 128, generator=g)
-    b_s = torch.rand((N + 127) // 128, K // 128, generator=g)
-    for _ in range(min(args.warmup, 2)):
+    a_q, a_s, b_q, b_s = make_dense_host(M, N, K, seed=0)
+    for _ in range(args.warmup):
         O.run_torch_blockscale(a_q, b_q, a_s, b_s)
-    steps = max(1, min(args.steps, 10))
     t0 = time.perf_counter()
-    for _ in range(steps):
+    for _ in range(args.steps):
         O.run_torch_blockscale(a_q, b_q, a_s, b_s)
-    dt = (time.perf_counter() - t0) / steps
+    dt = (time.perf_counter() - t0) / args.steps
     val = 2.0 * M * N * K / dt / 1e12
     cpu = {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-           "sample": f"full {M}x{N}x{K} GEMM incl. dequantisation, {steps} timed runs"}
+           "sample": f"full {M}x{N}x{K} GEMM incl. dequantisation, {args.steps} timed passes"}
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": world,
-        "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32 (dequantised fp8)", "data": "synthetic",
-        "config": {"workload": f"dense_fp8_blockscale_M{M}_N{N}_K{K}", "where": "host cores, torch CPU"},
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (f32 accumulate, bf16 out)",
+        "data": "synthetic", "config": workload_config(M, N, K, world),
+        "where": "host cores, torch CPU (dequantise to f32, F.linear)",
         "cpu_baseline": cpu,
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0}))
 
 
+def dense_check(w, c, world):
+    """Output of the headline GEMM (this rank's column shard, as left by the timed steps) against the
+    oracle on the same operands. Returns {"max_rel", "cosine", "ok"}, worst over the ranks."""
+    from oracle import blockscale_ref as O  # checker only
+
+    h = w["host"]
+    ref = O.run_torch_blockscale(h["a_q"], h["b_q"], h["a_scale"], h["b_scale"], dtype=torch.float32)
+    mr, cs = parity(c, ref)
+    mr = max_over_ranks(mr, world)
+    cs = -max_over_ranks(-cs, world)
+    return {"max_rel": mr, "cosine": cs, "ok": bool(mr <= MAX_REL and cs >= MIN_COS),
+            "against": "CPU oracle, every rank its column shard; worst over ranks"}
+
+
+def profile_traffic(name):
+    """`traffic_bytes_per_launch` recorded in a committed ncu summary under profiles/ (dram bytes read
+    + written by one launch of the kernel), or None. The number is a property of the kernel and the
+    shape, captured once under ncu; it is not measured by this run."""
+    path = os.path.join(ROOT, "profiles", name)
+    try:
+        for line in open(path):
+            if line.strip().startswith("traffic_bytes_per_launch:"):
+                return float(line.split(":", 1)[1].split()[0])
+    except OSError:
+        pass
+    return None
+
+
 def dense_sweep(dev, peaks, quick=False):
-    """BASELINE's dense M-sweep on one GPU: cold-L2 kernel time via a CUDA graph that rotates over
+    """The dense M-sweep (M in {1, 32, 256, 4096, 16384} x three (N, K) pairs) on one GPU: cold-L2 kernel time via a CUDA graph that rotates over
     enough independent weight/activation copies to exceed L2."""
     from flydsl_b200.kernels import compile_blockscale_preshuffle_gemm
     from flydsl_b200.utils import shuffle_weight
@@ -360,9 +410,19 @@ def int4_sweep(dev, peaks, quick=False):
     return rows
 
 
+def gen_expert(e, H, I, dev, seed):
+    """Weights of global expert `e` (N(0,0.02), 128x128 block-quantised), generated on the GPU from a
+    seed derived from the expert id, so that any rank can regenerate any expert: (w1_q [2I,H],
+    w1_scale flat, w2_q [H,I], w2_scale flat)."""
+    g = torch.Generator(device=dev).manual_seed(seed * 1000003 + e + 1)
+    q1, s1 = block_quant_torch(torch.randn(2 * I, H, generator=g, device=dev) * 0.02)
+    q2, s2 = block_quant_torch(torch.randn(H, I, generator=g, device=dev) * 0.02)
+    return q1, s1.reshape(-1), q2, s2.reshape(-1)
+
+
 def make_moe_gpu(T, H, I, E_local, topk, dev, seed, e_lo=0):
-    """Expert weights generated expert by expert on the GPU (N(0,0.02), 128x128 block-quantised,
-    seed derived from the global expert id) and repacked in place into the final buffers."""
+    """Expert weights generated expert by expert on the GPU and repacked in place into the final
+    buffers."""
     from flydsl_b200 import _lib
 
     w1 = torch.empty((E_local, 2 * I, H), dtype=torch.float8_e4m3fn, device=dev)
@@ -371,15 +431,37 @@ def make_moe_gpu(T, H, I, E_local, topk, dev, seed, e_lo=0):
     w2_s = torch.empty((E_local, (H // 128) * (I // 128)), dtype=torch.float32, device=dev)
     lib = _lib.load()
     for e in range(E_local):
-        g = torch.Generator(device=dev).manual_seed(seed * 1000003 + e_lo + e + 1)
-        q, s = block_quant_torch(torch.randn(2 * I, H, generator=g, device=dev) * 0.02)
+        q, s, q2, s2 = gen_expert(e_lo + e, H, I, dev, seed)
         _lib.check(lib.flyb200_repack_weight_fp8(w1[e].data_ptr(), q.data_ptr(), 1, 2 * I, H, _lib.stream_handle(None)))
-        w1_s[e] = s.reshape(-1)
-        q2, s2 = block_quant_torch(torch.randn(H, I, generator=g, device=dev) * 0.02)
+        w1_s[e] = s
         _lib.check(lib.flyb200_repack_weight_fp8(w2[e].data_ptr(), q2.data_ptr(), 1, H, I, _lib.stream_handle(None)))
-        w2_s[e] = s2.reshape(-1)
+        w2_s[e] = s2
         torch.cuda.synchronize()
     return w1, w1_s, w2, w2_s
+
+
+def moe_check(x_q, x_s, ids, tw, out, H, I, topk, dev, seed=0, n_tokens=4):
+    """A few tokens of an MoE result against the CPU oracle (two-stage, fp16 intermediate,
+    re-quantised 1x128), with the weights of the experts those tokens use regenerated from their
+    seeds. x_s is token-major [T, H/128]. Returns {"max_rel", "cosine", "ok", ...}."""
+    from oracle import blockscale_ref as O  # checker only
+
+    T = x_q.shape[0]
+    sel = torch.linspace(0, T - 1, steps=min(n_tokens, T)).long().unique()
+    ids_sel = ids[sel.to(ids.device)].cpu().long()
+    used = torch.unique(ids_sel)
+    remap = {int(e): i for i, e in enumerate(used.tolist())}
+    w1_q, w1_s, w2_q, w2_s = [], [], [], []
+    for e in used.tolist():
+        q1, s1, q2, s2 = gen_expert(int(e), H, I, dev, seed)
+        w1_q.append(q1.cpu()); w1_s.append(s1.cpu()); w2_q.append(q2.cpu()); w2_s.append(s2.cpu())
+    local_ids = torch.tensor([[remap[int(e)] for e in row] for row in ids_sel.tolist()], dtype=torch.int32)
+    ref, _, _, _ = O.torch_moe_two_stage_ref(
+        x_q[sel.to(x_q.device)].cpu(), x_s[sel.to(x_s.device)].cpu(), torch.stack(w1_q), torch.stack(w1_s),
+        torch.stack(w2_q), torch.stack(w2_s), local_ids, tw[sel.to(tw.device)].cpu().float(), I)
+    mr, cs = parity(out[sel.to(out.device)], ref)
+    return {"max_rel": mr, "cosine": cs, "ok": bool(mr <= MAX_REL and cs >= MIN_COS), "tokens": sel.tolist(),
+            "experts_regenerated": int(used.numel()), "against": "CPU oracle (two-stage, fp16 intermediate)"}
 
 
 def moe_layer_bench(rank, world, dev, peaks, quick=False):
@@ -419,6 +501,7 @@ def moe_layer_bench(rank, world, dev, peaks, quick=False):
             e1.synchronize()
             times.append(e0.elapsed_time(e1))
         ms = statistics.median(times)
+        chk = moe_check(x_q, x_s, ids, tw, out, H, I, topk, dev, seed=0, n_tokens=4 if T >= 1024 else 2)
         active = int(torch.unique(ids).numel())
         wbytes = active * 3 * I * H
         abytes = T * H + T * topk * I * (2 + 2 + 1 + 1) + T * topk * H * 2 * 2 + T * H * 2
@@ -428,7 +511,7 @@ def moe_layer_bench(rank, world, dev, peaks, quick=False):
                     "hbm_gbs_on_algorithmic_bytes": round((wbytes + abytes) / (ms * 1e-3) / 1e9, 1),
                     "frac_hbm_peak": round((wbytes + abytes) / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
                     "tflops": round((2.0 * T * topk * 3 * I * H) / (ms * 1e-3) / 1e12, 1),
-                    "launches_per_step": layer_t.launches_per_step,
+                    "launches_per_step": layer_t.launches_per_step, "check": chk,
                     "l2": "weights of the active experts (>= 3 GB) exceed L2"})
     return res
 
@@ -473,6 +556,14 @@ def moe_ep_bench(rank, world, dev, peaks, quick=False):
             e1.synchronize()
             times.append(e0.elapsed_time(e1) / per_batch)
         ms = max_over_ranks(statistics.median(times), world)
+        y = ep.forward(x_q, x_s, ids, tw)
+        torch.cuda.synchronize()
+        # every rank checks tokens of its own against the oracle (experts of other ranks regenerated here)
+        chk = moe_check(x_q, x_s, ids, tw, y, H, I, topk, dev, seed=0, n_tokens=2)
+        chk["max_rel"] = max_over_ranks(chk["max_rel"], world)
+        chk["cosine"] = -max_over_ranks(-chk["cosine"], world)
+        chk["ok"] = bool(chk["max_rel"] <= MAX_REL and chk["cosine"] >= MIN_COS)
+        chk["against"] += "; every rank 2 of its own tokens, worst over ranks"
         ep.trace = True
         ep.forward(x_q, x_s, ids, tw)     # one extra, instrumented step: phase times of rank 0
         ep.trace = False
@@ -482,6 +573,7 @@ def moe_ep_bench(rank, world, dev, peaks, quick=False):
         out.append({"tokens": T, "tokens_per_rank": TL, "experts_per_rank": EL, "ms": round(ms, 4),
                     "tokens_per_s": round(T / (ms * 1e-3), 1), "parallelism": f"ep{world}",
                     "exchange": mode, "phase_ms_rank0": stats.get("phase_ms"), "collective": notes[mode],
+                    "check": chk,
                     "timing": f"3 batches of {per_batch} steps enqueued back to back, median batch / "
                               f"{per_batch}, max over ranks; weights of the local experts exceed L2"})
     return out
@@ -545,6 +637,9 @@ def run_ours(args):
     assert _lib.query_device_error() == 0
     flops = 2.0 * M * N * K
     value = flops / (ms * 1e-3) / 1e12
+
+    # ---- check (outside the timed regions): this rank's column shard against the CPU oracle ----
+    check = dense_check(w, c, world)
 
     # ---- end to end: host buffers in, host buffer out ----
     a_host = w["a_q"].cpu().pin_memory()
@@ -618,11 +713,11 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "fp8_e4m3 (f32 accumulate, bf16 out)", "data": "synthetic",
-        "config": {"workload": f"dense_fp8_blockscale_M{M}_N{N}_K{K}", "sharding": f"N/{world} columns per GPU",
-                   "l2": f"steps rotate over {n_sets} independent operand sets ({n_sets * set_bytes >> 20} MiB > 2 x L2)",
-                   "timing": "W warm-up steps, then K steps enqueued back to back inside one CUDA-event "
-                             "bracket, max over ranks",
-                   "scales": "1x128 act, 128x128 weight, fp32"},
+        "config": workload_config(M, N, K, world),
+        "l2": f"steps rotate over {n_sets} independent operand sets ({n_sets * set_bytes >> 20} MiB > 2 x L2)",
+        "timing": "W warm-up steps, then K steps enqueued back to back inside one CUDA-event bracket, "
+                  "max over ranks",
+        "check": check,
         "isolated_launch": {"ms_per_step": isolated_ms, "value": flops / (isolated_ms * 1e-3) / 1e12,
                             "note": "one launch per event pair, 256 MiB L2 flush between launches "
                                     "(launch latency and pipeline ramp fully exposed)"},
@@ -636,8 +731,9 @@ def run_ours(args):
         "roofline": {"bound": "tensor", "achieved": per_gpu_tflops, "peak": fp8_peak, "unit": "TFLOP/s",
                      "frac": per_gpu_tflops / fp8_peak,
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at N=1,
-                     # from the ncu capture summarised in profiles/bs_gemm_dense_M4096_N7168_K2048.md
-                     "traffic": 31.1e6 if world == 1 else None,
+                     # read from the committed ncu summary (not measured by this run)
+                     "traffic": profile_traffic(f"bs_gemm_dense_M{M}_N{N}_K{K}.md") if world == 1 else None,
+                     "traffic_source": f"profiles/bs_gemm_dense_M{M}_N{N}_K{K}.md" if world == 1 else None,
                      "peak_source": f"2 x bf16_tflops ({peaks['source']}); dense FP8 rate is twice bf16",
                      "frac_of_nominal_4500": per_gpu_tflops / 4500.0},
         "clocks": clk.summary(),
@@ -656,8 +752,11 @@ def run_ours(args):
 
         dist.barrier()
         dist.destroy_process_group()
+    ok = out["check"]["ok"] and all(m.get("check", {}).get("ok", True) for m in (out.get("moe") or []))
     if rank == 0:
         print(json.dumps(out))
+    if not ok:
+        sys.exit("bench: a result missed the parity bar against the oracle (see the check entries)")
 
 
 def run_probe(args):

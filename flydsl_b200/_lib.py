@@ -62,7 +62,7 @@ SIGNATURES = {
                                             c_void_p]),
     "flyb200_ep_plan_pack": (c_int, [c_void_p] * 4 + [c_int32] * 5 + [c_void_p] * 5),
     "flyb200_ep_gather_packed": (c_int, [c_void_p] * 5 + [c_int32] * 4 + [c_void_p]),
-    "flyb200_ep_unpack_meta": (c_int, [c_void_p] + [c_int32] * 5 + [c_void_p] * 4),
+    "flyb200_ep_unpack_meta": (c_int, [c_void_p] + [c_int32] * 6 + [c_void_p] * 4),
     "flyb200_ep_combine": (c_int, [c_void_p] * 4 + [c_int32] * 4 + [c_void_p]),
     "flyb200_ep_buffer_create": (c_int, [c_int64, c_void_p, c_void_p]),
     "flyb200_ep_buffer_open": (c_int, [c_void_p, c_void_p]),

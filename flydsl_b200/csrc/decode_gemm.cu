@@ -12,8 +12,9 @@
 //     deterministic.
 //   * each CTA issues its whole K range of bulk copies at once when it fits the ring (<= 8 stages),
 //     so the HBM queue is full from the first microsecond.
-//   * launched with programmatic stream serialisation: setup (barriers, TMEM) overlaps the tail of
-//     the previous kernel in the stream; griddepcontrol.wait precedes the first global read.
+//   * launched with programmatic stream serialisation: setup (barriers, TMEM) and the first ring fill
+//     of WEIGHT tiles overlap the tail of the previous kernel in the stream; griddepcontrol.wait
+//     precedes every access to activations, scales and the output.
 //
 // Same arithmetic contract as the main kernel (blockscale_gemm.cu): per 128-K block the exact fp8
 // products are summed in fp32 by the tensor core, then acc += partial * (sa[kb,m] * sb[n/128,kb]).
@@ -124,19 +125,32 @@ bs_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecodePa
   cluster_sync_all();
 
   // Everything above touched no global memory: it may overlap the previous kernel of the stream.
+  // The WEIGHT tiles of the first ring fill are requested before the dependency wait as well:
+  // weights are parameters, not results of the kernel that runs just before (a kernel that lets its
+  // dependents start early -- the GEMM and MoE kernels of this library -- never writes weights, and
+  // any other kernel has exited before this one starts), so back-to-back launches stream weights
+  // without a gap. Activations, scales and the output are touched only after the wait.
+  const int first_fill = count < stages ? count : stages;
+  if (warp == 0 && lane == 0) {
+    for (int i = 0; i < first_fill; ++i) {
+      const uint32_t sw = smem_base + i * C::kStageBytes;
+      mbar_arrive_expect_tx(full_bar(i), rows_w * 128 + C::kXTileBytes);
+      bulk_load(sw, p.b + (static_cast<size_t>(kb_begin + i) * p.N + n0) * 128, rows_w * 128, full_bar(i));
+    }
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == 0) {
     if (lane == 0) {
       // ---------------- producer ----------------
-      for (int i = 0; i < count; ++i) {
+      for (int i = 0; i < first_fill; ++i)   // activation tiles of the stages whose weights are on their way
+        tma_load_2d(smem_base + i * C::kStageBytes + kWTileBytes, &tmap_x, (kb_begin + i) * 128, 0, full_bar(i));
+      for (int i = first_fill; i < count; ++i) {
         const int s = i % stages;
-        if (i >= stages) {
-          const uint32_t j = i - stages;
-          if (!mbar_wait(done_bar(j % kDone), (j / kDone) & 1, abort_flag, p.err, kErrWaitSmemEmpty))
-            break;
-        }
+        const uint32_t j = i - stages;
+        if (!mbar_wait(done_bar(j % kDone), (j / kDone) & 1, abort_flag, p.err, kErrWaitSmemEmpty))
+          break;
         const int kb = kb_begin + i;
         const uint32_t sw = smem_base + s * C::kStageBytes;
         mbar_arrive_expect_tx(full_bar(s), rows_w * 128 + C::kXTileBytes);

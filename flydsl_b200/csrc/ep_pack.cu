@@ -102,7 +102,7 @@ ep_gather_packed_kernel(const uint8_t* __restrict__ packed, const int* __restric
 // dense tensors the sorter and the masked reduce take: one launch instead of five framework ops.
 __global__ void __launch_bounds__(256)
 ep_unpack_meta_kernel(const uint8_t* __restrict__ packed, int rows, int H, int k, int row_bytes,
-                      int experts_per_rank, int rank, int* __restrict__ ids_out,
+                      int experts_per_rank, int rank, int local_ids, int* __restrict__ ids_out,
                       float* __restrict__ w_out, uint8_t* __restrict__ valid_out) {
   const int total = rows * k;
   const int meta = H + 4 * (H / 128);
@@ -110,9 +110,12 @@ ep_unpack_meta_kernel(const uint8_t* __restrict__ packed, int rows, int H, int k
     const int r = i / k, j = i - r * k;
     const uint8_t* row = packed + static_cast<size_t>(r) * row_bytes + meta;
     const int id = reinterpret_cast<const int*>(row)[j];
-    ids_out[i] = id;
+    const bool mine = id >= 0 && id / experts_per_rank == rank;
+    // local_ids: ids relative to this rank's first expert, -1 for every foreign or unused route, so
+    // that the routing sort runs over experts_per_rank experts only
+    ids_out[i] = local_ids ? (mine ? id - rank * experts_per_rank : -1) : id;
     w_out[i] = reinterpret_cast<const float*>(row + 4 * k)[j];
-    valid_out[i] = (id >= 0 && id / experts_per_rank == rank) ? 1 : 0;
+    valid_out[i] = mine ? 1 : 0;
   }
 }
 
@@ -171,8 +174,9 @@ extern "C" int flyb200_ep_gather_packed(const void* packed, const int32_t* sorte
 }
 
 extern "C" int flyb200_ep_unpack_meta(const void* packed, int32_t rows, int32_t H, int32_t k,
-                                      int32_t experts_per_rank, int32_t rank, int32_t* ids_out,
-                                      float* weights_out, uint8_t* valid_out, void* stream) {
+                                      int32_t experts_per_rank, int32_t rank, int32_t local_ids,
+                                      int32_t* ids_out, float* weights_out, uint8_t* valid_out,
+                                      void* stream) {
   if (!packed || !ids_out || !weights_out || !valid_out)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_unpack_meta: NULL buffer");
   if (rows < 1 || H < 128 || H % 128 || k < 1 || experts_per_rank < 1 || rank < 0 ||
@@ -183,7 +187,7 @@ extern "C" int flyb200_ep_unpack_meta(const void* packed, int32_t rows, int32_t 
   if (total > 0x7fffffffLL) return set_error(FLYB200_ERR_INVALID_ARGUMENT, "ep_unpack_meta: too many routes");
   const int blocks = static_cast<int>((total + 255) / 256);
   ep_unpack_meta_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint8_t*>(packed), rows, H, k, row_bytes, experts_per_rank, rank, ids_out,
+      static_cast<const uint8_t*>(packed), rows, H, k, row_bytes, experts_per_rank, rank, local_ids, ids_out,
       weights_out, valid_out);
   FLYB200_CUDA_CHECK(cudaGetLastError());
   return FLYB200_OK;

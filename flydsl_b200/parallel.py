@@ -514,7 +514,8 @@ ExpertParallelMoE._forward_peer = _forward_peer
 
 
 class LocalExpertShard:
-    """The experts of one rank on its GPU: routing sort restricted by ``expert_mask``, activations
+    """The experts of one rank on its GPU: routing sort over the local experts (routes renumbered to
+    local ids, foreign ones dropped), activations
     permuted into routing order, the two TMA-fed GEMM stages, and the masked top-k reduce that yields
     one partial row per received token. Rows whose expert ids are all foreign (or -1) give zeros."""
 
@@ -527,14 +528,18 @@ class LocalExpertShard:
             raise ValueError("LocalExpertShard uses the routing-order layout: tile_m must be a multiple of 8")
         self.E, self.k, self.rank, self.world = experts, topk, rank, world
         self.EL = experts // world
+        if self.EL < topk:
+            raise ValueError(f"LocalExpertShard needs experts per rank ({self.EL}) >= topk ({topk}): the routing "
+                             "buffers are sized for the local experts")
         self.w1, self.w2 = w1, w2                       # repacked local experts [EL, 2I, H], [EL, H, I]
         self.w1_scale, self.w2_scale = w1_scale.contiguous().view(-1), w2_scale.contiguous().view(-1)
         self.H, self.I = w1.shape[2], w1.shape[1] // 2
         self.tile_m, self.mid_dtype, self.out_dtype = tile_m, mid_dtype, out_dtype
         names = {torch.float16: "f16", torch.bfloat16: "bf16"}
-        # the stage kernels see the GLOBAL expert count for the length of the routing buffers
-        # (sorted length = R*k + E*tile_m - k) but only local, compacted expert ids occur in them
-        common = dict(model_dim=self.H, inter_dim=self.I, experts=experts, topk=topk, tile_m=tile_m,
+        # routes are renumbered to local expert ids (foreign routes become -1, which the sorter
+        # skips like any id outside [0, E)), so sort, routing buffers and stage kernels are sized for
+        # the EL local experts: sorted length = R*k + EL*tile_m - k
+        common = dict(model_dim=self.H, inter_dim=self.I, experts=self.EL, topk=topk, tile_m=tile_m,
                       tile_n=256, tile_k=128)
         self.gemm1 = compile_moe_blockscale_gemm1(doweight_stage1=False, out_dtype=names[mid_dtype],
                                                   a_sorted=True, out_sorted=True, **common)
@@ -544,15 +549,12 @@ class LocalExpertShard:
                                             use_mask=True)
         self._mid_code = {torch.float16: 1, torch.bfloat16: 0}[mid_dtype]
         self.fused_quant = bool(fused_quant)   # re-quantisation inside the stage-1 epilogue
-        mask = torch.zeros(experts, dtype=torch.int32, device=w1.device)
-        mask[rank * self.EL:(rank + 1) * self.EL] = 1
-        self.expert_mask = mask
         self._buf = {}
 
     def _buffers(self, R, dev):
         b = self._buf.get(R)
         if b is None:
-            L = R * self.k + self.E * self.tile_m - self.k
+            L = R * self.k + self.EL * self.tile_m - self.k
             b = {"L": L,
                  "x_sorted": torch.empty((L, self.H), dtype=torch.float8_e4m3fn, device=dev),
                  "xs_sorted": torch.empty((self.H // 128, L), dtype=torch.float32, device=dev),
@@ -579,7 +581,11 @@ class LocalExpertShard:
             moe_gather_rows(x_q_u8.view(torch.float8_e4m3fn), xs_t, sid, npp, topk=self.k,
                             out=b["x_sorted"], scale_out=b["xs_sorted"])
 
-        return self._run(R, x_q_u8.device, topk_ids, topk_weights, gather, None)
+        lo = self.rank * self.EL
+        local = topk_ids.to(torch.int32) - lo
+        local = torch.where((local >= 0) & (local < self.EL), local, torch.full_like(local, -1))
+        valid = (local >= 0).to(torch.uint8)
+        return self._run(R, x_q_u8.device, local, topk_weights, gather, None, valid)
 
     def forward_packed(self, rows, out=None, reducer=None):
         """Same as calling the shard on ``unpack_rows(rows)``, but the packed rows
@@ -596,7 +602,7 @@ class LocalExpertShard:
         b = self._buffers(R, rows.device)
         ids, w, valid = b["ids"], b["w"], b["valid"]
         _lib.check(_lib.load().flyb200_ep_unpack_meta(
-            rows.data_ptr(), R, H, k, self.EL, self.rank, ids.data_ptr(), w.data_ptr(), valid.data_ptr(),
+            rows.data_ptr(), R, H, k, self.EL, self.rank, 1, ids.data_ptr(), w.data_ptr(), valid.data_ptr(),
             _lib.stream_handle(None)))
 
         def gather(b, sid, npp):
@@ -611,8 +617,9 @@ class LocalExpertShard:
         from .utils import moe_sorting
 
         b = self._buffers(R, dev)
-        sid, sw, seid, npp = moe_sorting(topk_ids, topk_weights, num_experts=self.E,
-                                         block_size=self.tile_m, expert_mask=self.expert_mask)
+        # topk_ids are LOCAL expert ids here (-1 = not this rank's route)
+        sid, sw, seid, npp = moe_sorting(topk_ids, topk_weights, num_experts=self.EL,
+                                         block_size=self.tile_m)
         nblk = seid.numel()
         gather(b, sid, npp)
         if self.fused_quant:
@@ -626,9 +633,9 @@ class LocalExpertShard:
                 self.I, self._mid_code, _lib.stream_handle(None)))
         self.gemm2(b["routes"], b["a2_q"], self.w2, b["a2_s"], self.w2_scale, sid, seid, sw, npp, R,
                    self.H, self.I, nblk, None)
-        # a route counts here iff its expert lives on this rank (-1 marks an unused slot)
+        # a route counts here iff its expert lives on this rank
         if valid is None:
-            valid = (torch.div(topk_ids, self.EL, rounding_mode="floor") == self.rank).to(torch.uint8)
+            valid = (topk_ids >= 0).to(torch.uint8)
         if reducer is not None:            # e.g. PeerExchange.reduce_push: rows leave this GPU
             reducer(b["routes"], valid)
             return None

@@ -218,10 +218,11 @@ int flyb200_ep_gather_packed(const void* packed, const int32_t* sorted_ids,
 /* Expert-parallel receive side: the [rows, k] expert ids and route weights of a packed receive buffer
  * as dense tensors, plus valid[r][j] = 1 iff that expert lives on `rank` (ids / experts_per_rank ==
  * rank; -1 marks an unused slot) -- the sorter's inputs and the valid_mask of flyb200_moe_reduce.
- * No reference counterpart. */
+ * local_ids != 0: ids_out holds ids relative to the rank's first expert and -1 for every route that
+ * is not this rank's, so that the sort runs over experts_per_rank experts. No reference counterpart. */
 int flyb200_ep_unpack_meta(const void* packed, int32_t rows, int32_t H, int32_t k,
-                           int32_t experts_per_rank, int32_t rank, int32_t* ids_out,
-                           float* weights_out, uint8_t* valid_out, void* stream);
+                           int32_t experts_per_rank, int32_t rank, int32_t local_ids,
+                           int32_t* ids_out, float* weights_out, uint8_t* valid_out, void* stream);
 
 /* Expert-parallel final sum: out[t] = sum over ranks r, ascending, of back[r*T + slot[t][r]] where
  * need[t][r] (fp32 accumulate; back/out BF16|F16 [*, H]). No reference counterpart. */

@@ -7,8 +7,9 @@ library. The test drives it through the C ABI twice in a row and compares each r
 regular entry point (caller-provided workspace) on the same inputs; the second call uses a slot mask
 so that rows left in the shared array by the first call must not leak into the result.
 
-This file sorts last on purpose: a run that stops at the first failure has then already executed
-every other test.
+The module name sorts after the other test modules, so in a whole-suite run the shared array is used
+after every other test has gone through the library in the same process -- the order in which
+state left behind by earlier calls would show.
 """
 import ctypes
 
