@@ -44,6 +44,9 @@ SIGNATURES = {
                                         c_int32, c_int32, c_int32, POINTER(GemmCfg), c_void_p]),
     "flyb200_moe_sort": (c_int, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p,
                                  c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "flyb200_moe_sort_permute": (c_int, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p,
+                                         c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_void_p, c_int32, c_void_p]),
     "flyb200_moe_route_topk": (c_int, [c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
     "flyb200_moe_gemm1": (c_int, [c_void_p] * 9 + [c_int32] * 9 + [POINTER(GemmCfg), c_void_p]),
     "flyb200_moe_gemm1_q8": (c_int, [c_void_p] * 10 + [c_int32] * 9 + [POINTER(GemmCfg), c_void_p]),

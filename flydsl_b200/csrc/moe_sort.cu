@@ -12,6 +12,12 @@
 // j = 0..7. Positions follow the global id order (warp, j, lane, element): per-j warp prefix sums
 // (packed four to a register), one block-level prefix over the warps, then each lane writes its
 // matches.
+//
+// Fused permute (flyb200_moe_sort_permute): the CTA that has just placed an expert's routes also
+// copies the activation rows of those routes into routing order -- fp8 rows and their 1x128 scales,
+// the layout the TMA-fed stage kernels read -- so sort and permute are one launch and one pass of
+// latency instead of two. The reference gathers inside its stage kernels
+// (kernels/moe_blockscale_2stage.py:394-439); here the gather happens once for both stages.
 #include "common.cuh"
 
 namespace flyb200 {
@@ -57,6 +63,13 @@ struct SortParams {
   int block_m;
   int max_len;     // T*k + E*block_m - k
   int max_blocks;  // ceil(max_len / block_m)
+  // optional fused permute (x == nullptr: sort only)
+  const uint4* x;       // activations [rows_in, K] fp8, 16-byte chunks
+  const float* xs_t;    // their scales [K/128, rows_in]
+  uint4* x_out;         // [max_len, K]
+  float* xs_out;        // [K/128, max_len]
+  int K;
+  int rows_in;
 };
 
 __global__ void __launch_bounds__(kSortThreads)
@@ -215,6 +228,41 @@ moe_sort_kernel(const SortParams p) {
   }
   for (int b = tid; b < my_padded / p.block_m; b += kSortThreads)
     p.sorted_expert_ids[my_base / p.block_m + b] = cid;
+
+  if (p.x == nullptr) return;
+  // ---- fused permute: rows my_base .. my_base + my_padded of the routing-order buffers ----
+  __syncthreads();   // this CTA's sorted ids are visible to all of its threads
+  const int chunks = p.K / 16;
+  const int nscale = p.K / 128;
+  for (int i = warp; i < my_padded; i += kSortThreads / 32) {
+    const int r = my_base + i;
+    const int t = p.sorted_ids[r] & 0xFFFFFF;
+    const bool ok = i < my_cnt && t < p.rows_in;
+    const uint4* srow = p.x + static_cast<long long>(ok ? t : 0) * chunks;
+    uint4* drow = p.x_out + static_cast<long long>(r) * chunks;
+    for (int c0 = lane; c0 < chunks; c0 += 128) {   // four 16-byte loads per lane in flight
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + 32 * u;
+        v[u] = (ok && c < chunks) ? __ldg(srow + c) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + 32 * u;
+        if (c < chunks) drow[c] = v[u];
+      }
+    }
+  }
+  // scales: sorted position fastest, so that the stores to the transposed output are coalesced
+  for (int j = tid; j < nscale * my_padded; j += kSortThreads) {
+    const int sidx = j / my_padded;
+    const int i = j - sidx * my_padded;
+    const int t = p.sorted_ids[my_base + i] & 0xFFFFFF;
+    const bool ok = i < my_cnt && t < p.rows_in;
+    p.xs_out[static_cast<long long>(sidx) * p.max_len + my_base + i] =
+        ok ? __ldg(p.xs_t + static_cast<long long>(sidx) * p.rows_in + t) : 0.f;
+  }
 }
 
 // Router: top-k of a token's expert scores in descending order (= slot order) and a softmax over the
@@ -290,11 +338,11 @@ extern "C" int flyb200_moe_route_topk(const float* logits, int32_t T, int32_t E,
   return FLYB200_OK;
 }
 
-extern "C" int flyb200_moe_sort(const int32_t* topk_ids, const float* topk_weights, int32_t T,
-                                int32_t k, int32_t E, int32_t block_m, const int32_t* expert_mask,
-                                int32_t num_local_tokens, int32_t* sorted_ids,
-                                float* sorted_weights, int32_t* sorted_expert_ids,
-                                int32_t* num_valid_ids, void* stream) {
+static int moe_sort_impl(const int32_t* topk_ids, const float* topk_weights, int32_t T, int32_t k, int32_t E,
+                         int32_t block_m, const int32_t* expert_mask, int32_t num_local_tokens,
+                         int32_t* sorted_ids, float* sorted_weights, int32_t* sorted_expert_ids,
+                         int32_t* num_valid_ids, const void* x, const float* xs_t, void* x_out,
+                         float* xs_out, int32_t K, void* stream) {
   if (!topk_ids || !topk_weights || !sorted_ids || !sorted_weights || !sorted_expert_ids ||
       !num_valid_ids)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "moe_sort: NULL buffer");
@@ -316,8 +364,38 @@ extern "C" int flyb200_moe_sort(const int32_t* topk_ids, const float* topk_weigh
   p.k = k; p.E = E; p.block_m = block_m;
   p.max_len = static_cast<int>(max_len);
   p.max_blocks = static_cast<int>((max_len + block_m - 1) / block_m);
+  p.x = static_cast<const uint4*>(x); p.xs_t = xs_t;
+  p.x_out = static_cast<uint4*>(x_out); p.xs_out = xs_out;
+  p.K = K; p.rows_in = T;
   moe_sort_kernel<<<E, kSortThreads, 2 * E * sizeof(int),
                     reinterpret_cast<cudaStream_t>(stream)>>>(p);
   FLYB200_CUDA_CHECK(cudaGetLastError());
   return FLYB200_OK;
+}
+
+extern "C" int flyb200_moe_sort(const int32_t* topk_ids, const float* topk_weights, int32_t T,
+                                int32_t k, int32_t E, int32_t block_m, const int32_t* expert_mask,
+                                int32_t num_local_tokens, int32_t* sorted_ids,
+                                float* sorted_weights, int32_t* sorted_expert_ids,
+                                int32_t* num_valid_ids, void* stream) {
+  return moe_sort_impl(topk_ids, topk_weights, T, k, E, block_m, expert_mask, num_local_tokens, sorted_ids,
+                       sorted_weights, sorted_expert_ids, num_valid_ids, nullptr, nullptr, nullptr, nullptr, 0,
+                       stream);
+}
+
+extern "C" int flyb200_moe_sort_permute(const int32_t* topk_ids, const float* topk_weights, int32_t T,
+                                        int32_t k, int32_t E, int32_t block_m, const int32_t* expert_mask,
+                                        int32_t num_local_tokens, int32_t* sorted_ids,
+                                        float* sorted_weights, int32_t* sorted_expert_ids,
+                                        int32_t* num_valid_ids, const void* x, const float* x_scale_t,
+                                        void* x_sorted, float* x_scale_sorted_t, int32_t K, void* stream) {
+  if (!x || !x_scale_t || !x_sorted || !x_scale_sorted_t)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "moe_sort_permute: NULL buffer");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(x_sorted)) % 16)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "moe_sort_permute: x and x_sorted must be 16-byte aligned");
+  if (K < 128 || K % 128)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "moe_sort_permute: K (%d) must be a multiple of 128", K);
+  return moe_sort_impl(topk_ids, topk_weights, T, k, E, block_m, expert_mask, num_local_tokens, sorted_ids,
+                       sorted_weights, sorted_expert_ids, num_valid_ids, x, x_scale_t, x_sorted,
+                       x_scale_sorted_t, K, stream);
 }

@@ -233,48 +233,43 @@ class MoeGemm2Mode:
 
 
 class _MoeGemm2ReduceWrapper:
-    """Stage 2 without atomics followed by the top-k reduce; allocates the ``[tokens*topk,
-    model_dim]`` intermediate per call, like the reference wrapper (:2709-2715)."""
+    """Stage 2 in reduce mode: per-route rows into a scratch tensor, then the fixed-order sum over
+    the top-k slots -- one C-ABI call. Call signature of the reference's wrapper (:2642-2737):
+    ``fn(out, x, w, scale_x, scale_w, sorted_token_ids, expert_ids, sorted_weights, num_valid_ids,
+    tokens, n, k, size_expert_ids, valid_mask=None, stream=None)``. The ``[tokens*topk, model_dim]``
+    scratch is allocated per call, as the reference does (:2709-2715)."""
 
-    def __init__(self, gemm2_exe, reduce_exe, topk, model_dim, out_dtype_str="f16", use_mask=False):
-        self._gemm2_exe, self._reduce_exe = gemm2_exe, reduce_exe
-        self._topk, self._model_dim = int(topk), int(model_dim)
-        self._out_dtype_str, self._use_mask = out_dtype_str, bool(use_mask)
+    _TORCH_DTYPES = {_lib.F16: "float16", _lib.BF16: "bfloat16", _lib.F32: "float32"}
 
-    def _get_torch_dtype(self):
+    def __init__(self, stage2: MoeGemm2Launcher, masked: bool):
+        self._stage2 = stage2
+        self._masked = bool(masked)
+
+    def __call__(self, out, x, w, scale_x, scale_w, sorted_token_ids, expert_ids, sorted_weights,
+                 num_valid_ids, tokens, n, k, size_expert_ids, valid_mask=None, stream=None):
         import torch
 
-        return {"f16": torch.float16, "fp16": torch.float16, "bf16": torch.bfloat16,
-                "f32": torch.float32}.get(self._out_dtype_str, torch.float16)
-
-    def __call__(self, arg_out, arg_x, arg_w, arg_scale_x, arg_scale_w, arg_sorted_token_ids,
-                 arg_expert_ids, arg_sorted_weights, arg_num_valid_ids, tokens_in, n_in, k_in,
-                 size_expert_ids_in, valid_mask=None, stream=None):
-        import torch
-
-        if stream is None:
-            stream = torch.cuda.current_stream()
-        inter = torch.empty(tokens_in * self._topk, self._model_dim, device=arg_out.device,
-                            dtype=self._get_torch_dtype())
-        if not self._use_mask and valid_mask is not None:
-            logging.warning("valid_mask provided but use_mask=False; ignoring valid_mask")
-        g = self._gemm2_exe
-        if int(n_in) != g.model_dim or int(k_in) != g.inter_dim:
-            raise ValueError(f"launcher was built for model_dim={g.model_dim}, inter_dim={g.inter_dim}; "
-                             f"got n={n_in}, k={k_in}")
+        g = self._stage2
+        if (int(n), int(k)) != (g.model_dim, g.inter_dim):
+            raise ValueError(f"built for model_dim={g.model_dim}, inter_dim={g.inter_dim}; called with n={n}, k={k}")
+        tokens = int(tokens)
         mask_ptr = None
-        if self._use_mask:
-            if valid_mask is None or valid_mask.numel() != int(tokens_in) * self._topk or valid_mask.element_size() != 1:
-                raise ValueError("use_mask=True needs a 1-byte valid_mask [tokens, topk]")
+        if self._masked:
+            if valid_mask is None or valid_mask.numel() != tokens * g.topk or valid_mask.element_size() != 1:
+                raise ValueError("this launcher was built with a valid_mask: pass a 1-byte mask [tokens, topk]")
             mask_ptr = valid_mask.data_ptr()
-        # one C-ABI call: zero-fill (no mask) -> stage 2 per-route rows -> top-k reduce
+        elif valid_mask is not None:
+            logging.getLogger(__name__).warning(
+                "a valid_mask was passed to a reduce-mode launcher built without one; it is not applied")
+        scratch = torch.empty((tokens * g.topk, g.model_dim), device=out.device,
+                              dtype=getattr(torch, self._TORCH_DTYPES[g.out_code]))
+        # zero-fill (when there is no mask) -> stage 2 per-route rows -> top-k reduce
         _lib.check(_lib.load().flyb200_moe_gemm2_reduce(
-            arg_out.data_ptr(), arg_x.data_ptr(), arg_w.data_ptr(), arg_scale_x.data_ptr(),
-            arg_scale_w.data_ptr(), arg_sorted_token_ids.data_ptr(), arg_expert_ids.data_ptr(),
-            arg_sorted_weights.data_ptr(), arg_num_valid_ids.data_ptr(), mask_ptr, int(tokens_in),
-            g.model_dim, g.inter_dim, int(size_expert_ids_in), g.experts, g.topk, g.tile_m, g.doweight,
-            g.out_code, g._cfg_ref, inter.data_ptr(), inter.numel() * inter.element_size(),
-            _lib.stream_handle(stream)))
+            out.data_ptr(), x.data_ptr(), w.data_ptr(), scale_x.data_ptr(), scale_w.data_ptr(),
+            sorted_token_ids.data_ptr(), expert_ids.data_ptr(), sorted_weights.data_ptr(),
+            num_valid_ids.data_ptr(), mask_ptr, tokens, g.model_dim, g.inter_dim, int(size_expert_ids),
+            g.experts, g.topk, g.tile_m, g.doweight, g.out_code, g._cfg_ref, scratch.data_ptr(),
+            scratch.numel() * scratch.element_size(), _lib.stream_handle(stream)))
 
     @property
     def mode(self) -> str:
@@ -306,14 +301,8 @@ def compile_moe_blockscale_gemm2_ex(
                   tile_m=tile_m, tile_n=tile_n, tile_k=tile_k, doweight_stage2=doweight_stage2,
                   out_dtype=out_dtype, use_cshuffle_epilog=use_cshuffle_epilog)
     if mode == MoeGemm2Mode.REDUCE:
-        use_mask = valid_mask is not None
-        gemm2_exe = compile_moe_blockscale_gemm2(accumulate=False, **common)
-        out_s = str(out_dtype).strip().lower()
-        dtype_str = "f16" if out_s in ("f16", "fp16", "half") else (
-            "bf16" if out_s in ("bf16", "bfloat16") else "f32")
-        reduce_exe = compile_moe_reduction(topk=topk, model_dim=model_dim, dtype_str=dtype_str,
-                                           use_mask=use_mask)
-        return _MoeGemm2ReduceWrapper(gemm2_exe, reduce_exe, topk, model_dim, dtype_str, use_mask)
+        stage2 = compile_moe_blockscale_gemm2(accumulate=False, **common)   # validates out_dtype too
+        return _MoeGemm2ReduceWrapper(stage2, masked=valid_mask is not None)
     if mode != MoeGemm2Mode.ATOMIC:
         raise ValueError(f"mode must be 'atomic' or 'reduce', got {mode!r}")
     return compile_moe_blockscale_gemm2(accumulate=True, **common)

@@ -120,9 +120,14 @@ class BlockscaleMoE:
         T = x_q.shape[0]
         dev = x_q.device
         b = self._buffers(T, dev)
+        permuted = False
         if routing is None:
-            sid, sw, seid, npp = moe_sorting(topk_ids, topk_weights, num_experts=self.E,
-                                             block_size=self.tile_m)
+            # routing-order layouts: the sort kernel also permutes the activations (one launch)
+            fuse = self.sorted_layout and x_q.is_contiguous() and x_scale_t.is_contiguous()
+            sid, sw, seid, npp = moe_sorting(
+                topk_ids, topk_weights, num_experts=self.E, block_size=self.tile_m,
+                permute=(x_q, x_scale_t, b["x_sorted"], b["xs_sorted"]) if fuse else None)
+            permuted = fuse
         else:
             sid, sw, seid, npp = routing
         nblk = seid.numel()
@@ -130,8 +135,9 @@ class BlockscaleMoE:
         if self.sorted_layout:
             if sid.numel() != b["rows"]:
                 raise ValueError("routing buffers do not match this layer's experts/tile_m/topk")
-            moe_gather_rows(x_q, x_scale_t, sid, npp, topk=self.topk, out=b["x_sorted"],
-                            scale_out=b["xs_sorted"])
+            if not permuted:
+                moe_gather_rows(x_q, x_scale_t, sid, npp, topk=self.topk, out=b["x_sorted"],
+                                scale_out=b["xs_sorted"])
             if self.fused_quant:
                 self.gemm1.quantized(b["a2_q"], b["a2_s"], b["x_sorted"], self.w1, b["xs_sorted"],
                                      self.w1_scale, sid, seid, sw, npp, T, nblk, None)
@@ -164,8 +170,8 @@ class BlockscaleMoE:
             self.reduce(b["routes"], out, None, T, None)
         return out
 
-    #: kernels one forward() launches (sort, [gather], gemm1, quant, gemm2, reduce | memset+gemm2)
+    #: kernels one forward() launches (sort[+permute], gemm1, quant, gemm2, reduce | memset+gemm2)
     @property
     def launches_per_step(self) -> int:
-        return (5 if self.fused_quant else 6) if self.sorted_layout else 5
+        return 4 if (self.sorted_layout and self.fused_quant) else 5
 

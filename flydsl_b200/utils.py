@@ -110,11 +110,15 @@ def quant_1x128(x: torch.Tensor, stream=None) -> Tuple[torch.Tensor, torch.Tenso
 
 def moe_sorting(topk_ids: torch.Tensor, topk_weights: torch.Tensor, *, num_experts: int,
                 block_size: int, expert_mask: Optional[torch.Tensor] = None,
-                num_local_tokens=None, stream=None
+                num_local_tokens=None, stream=None, permute=None
                 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """CUDA routing sort with the outputs of moe_sorting_torch_native
     (tests/kernels/test_moe_gemm.py:97-161): (sorted_ids i32, sorted_weights f32,
-    sorted_expert_ids i32, num_tokens_post_pad i32[2])."""
+    sorted_expert_ids i32, num_tokens_post_pad i32[2]).
+
+    ``permute=(x, x_scale_t, x_sorted, x_scale_sorted_t)`` fuses the permute of the activations into
+    routing order into the same launch (what ``moe_gather_rows`` does separately): x fp8 ``[T, K]``,
+    x_scale_t f32 ``[K/128, T]``, outputs ``[len(sorted_ids), K]`` and ``[K/128, len(sorted_ids)]``."""
     _require_cuda(topk_ids, "topk_ids")
     _require_cuda(topk_weights, "topk_weights")
     if topk_ids.dtype != torch.int32:
@@ -140,10 +144,21 @@ def moe_sorting(topk_ids: torch.Tensor, topk_weights: torch.Tensor, *, num_exper
     else:
         nlt = int(num_local_tokens)
     with torch.cuda.device(dev):
-        _lib.check(_lib.load().flyb200_moe_sort(
-            topk_ids.data_ptr(), topk_weights.data_ptr(), tokens, topk, int(num_experts),
-            int(block_size), mask_ptr, nlt, sorted_ids.data_ptr(), sorted_weights.data_ptr(),
-            sorted_expert_ids.data_ptr(), num_post_pad.data_ptr(), _lib.stream_handle(stream)))
+        if permute is None:
+            _lib.check(_lib.load().flyb200_moe_sort(
+                topk_ids.data_ptr(), topk_weights.data_ptr(), tokens, topk, int(num_experts),
+                int(block_size), mask_ptr, nlt, sorted_ids.data_ptr(), sorted_weights.data_ptr(),
+                sorted_expert_ids.data_ptr(), num_post_pad.data_ptr(), _lib.stream_handle(stream)))
+        else:
+            x, xs_t, x_sorted, xs_sorted = permute
+            if x.shape[0] != tokens or tuple(x_sorted.shape) != (max_len, x.shape[1]) or \
+                    tuple(xs_sorted.shape) != (x.shape[1] // 128, max_len):
+                raise ValueError("permute buffers do not match [T, K] -> [T*k + E*block - k, K]")
+            _lib.check(_lib.load().flyb200_moe_sort_permute(
+                topk_ids.data_ptr(), topk_weights.data_ptr(), tokens, topk, int(num_experts),
+                int(block_size), mask_ptr, nlt, sorted_ids.data_ptr(), sorted_weights.data_ptr(),
+                sorted_expert_ids.data_ptr(), num_post_pad.data_ptr(), x.data_ptr(), xs_t.data_ptr(),
+                x_sorted.data_ptr(), xs_sorted.data_ptr(), int(x.shape[1]), _lib.stream_handle(stream)))
     return sorted_ids, sorted_weights, sorted_expert_ids, num_post_pad
 
 

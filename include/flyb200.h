@@ -83,6 +83,19 @@ int flyb200_moe_sort(const int32_t* topk_ids, const float* topk_weights, int32_t
                      int32_t num_local_tokens, int32_t* sorted_ids, float* sorted_weights,
                      int32_t* sorted_expert_ids, int32_t* num_valid_ids, void* stream);
 
+/* flyb200_moe_sort fused with the permute of the activations into routing order (what
+ * flyb200_moe_gather_rows does in a second launch): x fp8 [T, K] and x_scale_t f32 [K/128, T] are
+ * copied to x_sorted [T*k + E*block_m - k, K] and x_scale_sorted_t [K/128, same rows], row i = the
+ * token of sorted position i, zeros on padding rows (rows at or beyond num_valid_ids[0] are left
+ * untouched). The reference gathers inside its stage kernels
+ * (kernels/moe_blockscale_2stage.py:394-439). K % 128 == 0. */
+int flyb200_moe_sort_permute(const int32_t* topk_ids, const float* topk_weights, int32_t T, int32_t k,
+                             int32_t E, int32_t block_m, const int32_t* expert_mask,
+                             int32_t num_local_tokens, int32_t* sorted_ids, float* sorted_weights,
+                             int32_t* sorted_expert_ids, int32_t* num_valid_ids, const void* x,
+                             const float* x_scale_t, void* x_sorted, float* x_scale_sorted_t, int32_t K,
+                             void* stream);
+
 /* Router: topk_ids[t] = the k experts with the largest logits[t] in descending order (slot order),
  * topk_weights[t] = softmax over those k values. Replaces the reference test's
  * torch.topk + torch.softmax (tests/kernels/test_moe_blockscale.py:228-230). logits f32 [T, E],

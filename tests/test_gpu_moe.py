@@ -54,6 +54,36 @@ def test_sort_vs_oracle_full_size(T, k, E, bs, hot):
     assert n_valid % bs == 0 and (got[2][: n_valid // bs] >= 0).all()
 
 
+@pytest.mark.parametrize("T,k,E,bs,K,masked", [(300, 4, 16, 32, 512, False), (4096, 8, 256, 128, 1024, False),
+                                                 (77, 6, 40, 16, 256, True), (1, 2, 8, 128, 128, False)])
+def test_sort_with_fused_permute_matches_sort_then_gather(T, k, E, bs, K, masked):
+    """flyb200_moe_sort_permute = the sorter's buffers bit for bit, plus the routing-order activations
+    and scales that moe_gather_rows produces from them (rows below num_valid; padding rows zero)."""
+    from flydsl_b200.utils import moe_gather_rows, moe_sorting
+
+    g = torch.Generator().manual_seed(T + E)
+    ids, w = O.route_topk(torch.randn(T, E, generator=g), k)
+    x = torch.randint(0, 255, (T, K), generator=g, dtype=torch.uint8).view(torch.float8_e4m3fn).to(DEV)
+    xs_t = torch.rand(K // 128, T, generator=g).to(DEV)
+    mask = None
+    if masked:
+        mask = (torch.rand(E, generator=g) > 0.4).to(torch.int32).to(DEV)
+    L = T * k + E * bs - k
+    xo = torch.full((L, K), 0x55, dtype=torch.uint8, device=DEV).view(torch.float8_e4m3fn)
+    so = torch.full((K // 128, L), -1.0, device=DEV)
+    fused = moe_sorting(ids.to(DEV), w.to(DEV), num_experts=E, block_size=bs, expert_mask=mask,
+                        permute=(x, xs_t, xo, so))
+    plain = moe_sorting(ids.to(DEV), w.to(DEV), num_experts=E, block_size=bs, expert_mask=mask)
+    torch.cuda.synchronize()
+    for a, b in zip(fused, plain):
+        assert torch.equal(a, b)
+    n = int(plain[3][0])
+    xg, sg = moe_gather_rows(x, xs_t, plain[0], plain[3], topk=k)
+    assert torch.equal(xo[:n].view(torch.uint8), xg[:n].view(torch.uint8))
+    assert torch.equal(so[:, :n], sg[:, :n])
+    assert (xo[n:].view(torch.uint8) == 0x55).all() and (so[:, n:] == -1.0).all()   # beyond the used rows: untouched
+
+
 def test_quant_1x128_bit_exact():
     from flydsl_b200.utils import quant_1x128
 
