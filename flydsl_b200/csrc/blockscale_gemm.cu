@@ -255,13 +255,17 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   // arrivals per stage: the producer's expect_tx (+ the two gather warps when rows are gathered)
   const bool gather_a = (MODE != kDense) && !p.a_sorted;
+  // MoE tiles that leave through the staging tile are written out by warps 2-3 while the epilogue
+  // warps go on with the next tile -- when those warps are not gathering rows and the epilogue does
+  // not re-quantise (that path stores its fp8 rows itself).
+  const bool moe_async_store = (MODE != kDense) && C::kStaged && !gather_a && p.out_q == nullptr;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) mbar_init(full_bar(s), gather_a ? 3 : 1);
     for (int i = 0; i < kDone; ++i) mbar_init(done_bar(i), 1);
     for (int b = 0; b < kAccBufs; ++b) mbar_init(tempty_bar(b), kEpiWarps);  // one arrival per warp
     mbar_init(epi_bar, kEpiWarps);
     mbar_init(cfull_bar, kEpiWarps);
-    mbar_init(cfree_bar, 1);
+    mbar_init(cfree_bar, MODE == kDense ? 1 : 2);
     *abort_flag = 0;
     fence_proxy_async_smem();
     fence_barrier_init();
@@ -403,6 +407,53 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         mbar_arrive(cfree_bar);
       }
       bulk_wait_group0();  // every store has been written before the CTA exits
+    } else if (MODE != kDense && C::kStaged && warp >= 2 && moe_async_store) {
+      // ---------------- MoE: output store (routing-order activations) ----------------
+      // Warps 2-3 copy every staged tile to its output rows (row_off: element offset of each row,
+      // -1 for rows without a token) while the epilogue warps run the next tile's K loop: cfull
+      // says the tile and its row offsets are staged, cfree gives both back.
+      if constexpr (C::kStaged) {
+        OutT* const out = reinterpret_cast<OutT*>(p.out);
+        constexpr int CPR = C::kOutCols / 8;   // 16-byte chunks per output row
+        constexpr int RPI = 32 / CPR;          // rows per warp instruction
+        const int sw = warp - 2;
+        const int rows = min(BM, p.tile_m);
+        const int ch = lane % CPR;
+        const int col = ch * 8;
+        uint32_t n = 0;
+        for (TilePos pos = walk.start(); walk.valid(pos); walk.advance(pos)) {
+          const int e = p.expert_ids[pos.m_blk];
+          if (e < 0 || e >= p.experts) continue;
+          const bool ok = mbar_wait(cfull_bar, n & 1, abort_flag, p.err, kErrWaitEpilogue);
+          if (!__all_sync(0xffffffffu, ok)) break;
+          ++n;
+          const int n0 = pos.n_tile * C::kOutCols;
+          if (n0 + col + 8 <= p.N) {
+            for (int r0 = sw * RPI; r0 < rows; r0 += 2 * RPI) {
+              const int rr = r0 + lane / CPR;
+              if (rr < rows) {
+                const long long off = row_off[rr];
+                if (off >= 0) {
+                  const uint32_t addr = cstage_base + (col >> 6) * kRegionBytes + rr * 128 +
+                                        ((((col & 63) >> 3) ^ (rr & 7)) << 4);
+                  uint4 q;
+                  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                               : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                               : "r"(addr)
+                               : "memory");
+                  OutT* dst = out + off + n0 + col;
+                  if (MODE == kMoe2 && p.accumulate)
+                    red8_packed(dst, q);
+                  else
+                    *reinterpret_cast<uint4*>(dst) = q;
+                }
+              }
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(cfree_bar);
+        }
+      }
     } else if (MODE != kDense && warp >= 2 && gather_a) {
       // ---------------- MoE: gather activation rows with cp.async ----------------
       // Thread g owns rows g and g+64 of the tile; row r, 16-byte chunk c lands at
@@ -742,6 +793,11 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const bool ok = mbar_wait(cfree_bar, (tiles_done - 1) & 1, abort_flag, p.err, kErrWaitEpilogue);
             if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
           }
+        } else if (moe_async_store) {
+          if (tiles_done > 0) {
+            const bool ok = mbar_wait(cfree_bar, (tiles_done - 1) & 1, abort_flag, p.err, kErrWaitEpilogue);
+            if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+          }
         } else {
           if (!epi_sync()) { alive = false; break; }
         }
@@ -864,6 +920,12 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if constexpr (MODE == kDense) {
           // (3) hand the staged tile to the store warp and go on with the next tile
           fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA store
+          __syncwarp();
+          if (lane == 0) mbar_arrive(cfull_bar);
+          ++tiles_done;
+        } else if (moe_async_store) {
+          // (3) hand the staged tile and its row offsets to the store warps
+          if (half == 0) row_off[r] = row_ok ? static_cast<long long>(out_row) : -1LL;
           __syncwarp();
           if (lane == 0) mbar_arrive(cfull_bar);
           ++tiles_done;
