@@ -299,12 +299,18 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // ---------------- producer: weights (and dense A) via TMA ----------------
       uint32_t it = 0;
       bool alive = true;
+      const uint64_t pol_evict_first = l2_policy_evict_first();
+      auto load_w = [&](uint32_t dst, const uint8_t* src, uint32_t bytes, uint32_t bar, bool last_use) {
+        if (last_use) bulk_load_hint(dst, src, bytes, bar, pol_evict_first);
+        else bulk_load(dst, src, bytes, bar);
+      };
       for (TilePos pos = walk.start(); walk.valid(pos) && alive; walk.advance(pos)) {
         const int m_blk = pos.m_blk, n_tile = pos.n_tile;
         const uint8_t* wbase = p.b;
         int rows_b;  // weight rows this tile brings per column group
         size_t row_stride_kb;  // bytes between consecutive K blocks of the repacked weight
         int n0;
+        bool w_last_use = false;
         if constexpr (MODE == kDense) {
           n0 = n_tile * BN;
           rows_b = min(BN, p.N - n0);
@@ -312,6 +318,10 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         } else {
           const int e = p.expert_ids[m_blk];
           if (e < 0 || e >= p.experts) continue;
+          // An expert's weights are read by its row blocks only: the last of them marks the lines
+          // "evict first", which keeps L2 for the activations and for weights that a following row
+          // block still needs.
+          w_last_use = (m_blk + 1 >= walk.num_m) || (p.expert_ids[m_blk + 1] != e);
           if constexpr (MODE == kMoe1) {
             n0 = n_tile * (BN / 2);
             rows_b = min(BN / 2, p.N - n0);
@@ -340,13 +350,13 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           } else if constexpr (MODE == kMoe1) {
             mbar_arrive_expect_tx(full_bar(s), 2 * rows_b * BK + (p.a_sorted ? p.a_box_rows * BK : 0));
             if (p.a_sorted) tma_load_2d(sa, &tmap_a, kb * BK, m_blk * p.tile_m, full_bar(s));
-            bulk_load(sb, src, rows_b * BK, full_bar(s));
-            bulk_load(sb + (BN / 2) * BK, src + static_cast<size_t>(p.N) * BK, rows_b * BK,
-                      full_bar(s));
+            load_w(sb, src, rows_b * BK, full_bar(s), w_last_use);
+            load_w(sb + (BN / 2) * BK, src + static_cast<size_t>(p.N) * BK, rows_b * BK, full_bar(s),
+                   w_last_use);
           } else {
             mbar_arrive_expect_tx(full_bar(s), rows_b * BK + (p.a_sorted ? p.a_box_rows * BK : 0));
             if (p.a_sorted) tma_load_2d(sa, &tmap_a, kb * BK, m_blk * p.tile_m, full_bar(s));
-            bulk_load(sb, src, rows_b * BK, full_bar(s));
+            load_w(sb, src, rows_b * BK, full_bar(s), w_last_use);
           }
         }
       }
