@@ -257,8 +257,8 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const bool gather_a = (MODE != kDense) && !p.a_sorted;
   // MoE tiles that leave through the staging tile are written out by warps 2-3 while the epilogue
   // warps go on with the next tile -- when those warps are not gathering rows and the epilogue does
-  // not re-quantise (that path stores its fp8 rows itself).
-  const bool moe_async_store = (MODE != kDense) && C::kStaged && !gather_a && p.out_q == nullptr;
+  // stays with the arithmetic.
+  const bool moe_async_store = (MODE != kDense) && C::kStaged && !gather_a;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) mbar_init(full_bar(s), gather_a ? 3 : 1);
     for (int i = 0; i < kDone; ++i) mbar_init(done_bar(i), 1);
@@ -438,7 +438,31 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (!__all_sync(0xffffffffu, ok)) break;
           ++n;
           const int n0 = pos.n_tile * C::kOutCols;
-          if (n0 + col + 8 <= p.N) {
+          if (MODE == kMoe1 && BN == 256 && p.out_q) {
+            // re-quantised tile: 128 rows x 128 fp8 bytes in region 0, the rows' scales in region 1
+            const float* scale_s = reinterpret_cast<const float*>(smem_al + kStages * C::kStageBytes +
+                                                                  kRegionBytes) + 2 * BM;
+            const int c8 = lane & 7;   // 8 chunks of 16 bytes per row
+            if (n0 + 128 <= p.N) {
+              for (int r0 = sw * 4; r0 < rows; r0 += 8) {
+                const int rr = r0 + (lane >> 3);
+                if (rr < rows) {
+                  const long long srow = row_off[rr];
+                  if (srow >= 0) {
+                    const uint32_t addr = cstage_base + rr * 128 + ((c8 ^ (rr & 7)) << 4);
+                    uint4 q;
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                                 : "r"(addr)
+                                 : "memory");
+                    *reinterpret_cast<uint4*>(p.out_q + srow * p.N + n0 + c8 * 16) = q;
+                    if (c8 == 0)
+                      p.out_scale_t[static_cast<long long>(n0 / 128) * p.a_rows + srow] = scale_s[rr];
+                  }
+                }
+              }
+            }
+          } else if (n0 + col + 8 <= p.N) {
             for (int r0 = sw * RPI; r0 < rows; r0 += 2 * RPI) {
               const int rr = r0 + lane / CPR;
               if (rr < rows) {
@@ -880,6 +904,11 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               row_off[r] = row_ok ? static_cast<long long>(m_blk * p.tile_m + r) : -1LL;  // sorted row
               scale_s[r] = scale;
             }
+            if (moe_async_store) {   // the store warps write the rows and scales out
+              __syncwarp();
+              if (lane == 0) mbar_arrive(cfull_bar);
+              ++tiles_done;
+            } else {
             if (!epi_sync()) { alive = false; break; }
             const int rows = min(BM, p.tile_m);
             const int ch = lane & 7;                       // 8 chunks of 16 bytes per row
@@ -901,6 +930,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                   }
                 }
               }
+            }
             }
             tile_stored = true;
           }
@@ -933,6 +963,8 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           __syncwarp();
           if (lane == 0) mbar_arrive(cfull_bar);
           ++tiles_done;
+        } else if (moe_async_store && tile_stored) {
+          // the re-quantised tile has been handed over above
         } else if (moe_async_store) {
           // (3) hand the staged tile and its row offsets to the store warps
           if (half == 0) row_off[r] = row_ok ? static_cast<long long>(out_row) : -1LL;
