@@ -25,10 +25,12 @@
 // kernels/moe_gemm_2stage.py:607-630 and the int4 unpack of kernels/mfma_preshuffle_pipeline.py:
 // 202-222); the contract is "dequantise, then matmul".
 //
-// Packed layout (flyb200_int4_repack): wq [K/128][N][64 bytes]; the 8 nibbles of each 32-bit word
-// hold 8 consecutive K elements in the order e0 e2 e4 e6 e1 e3 e5 e7 (low nibble first), so that
-// (word >> 4q) & 0x000F000F yields the pair (e_2q, e_2q+1) in the two 16-bit halves. Scales
-// [K/128][N] bf16.
+// Packed layout (flyb200_int4_repack): wq [K/128][N/8][4][8][16 bytes] -- per 128-K group and block
+// of 8 rows, four 16-byte chunks (32 K elements each), each chunk holding its 8 rows back to back,
+// so that a warp reading one chunk of 8 consecutive rows touches 128 contiguous bytes. The 8 nibbles
+// of each 32-bit word hold 8 consecutive K elements in the order e0 e2 e4 e6 e1 e3 e5 e7 (low nibble
+// first), so that (word >> 4q) & 0x000F000F yields the pair (e_2q, e_2q+1) in the two 16-bit
+// halves. Scales [K/128][N] bf16.
 #include "common.cuh"
 #include "cluster.cuh"
 
@@ -43,7 +45,7 @@ constexpr int kI4MaxStages = 6;
 constexpr int kI4WBytes = 2 * 128 * 128;   // two 64-K bf16 sub-tiles of 128 rows
 
 struct Int4Params {
-  const uint8_t* wq;               // [K/128][N][64]
+  const uint8_t* wq;               // [K/128][N/8][4][8][16]
   const __nv_bfloat16* scales_t;   // [K/128][N]
   void* out;                       // [M, N] bf16
   int* err;
@@ -251,8 +253,8 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const Int4Params p)
       const uint32_t sw = smem_base + s * C::kStageBytes;
 #pragma unroll
       for (int j = 0; j < kVecs; ++j) {
-        const int vec = j * kDqThreads + dt;
-        const int r = vec >> 2, part = vec & 3;
+        const int vec = j * kDqThreads + dt;        // position in the packed tile: [row / 8][part][row % 8]
+        const int r = ((vec >> 5) << 3) | (vec & 7), part = (vec >> 3) & 3;
         const uint32_t row_base = sw + (part >> 1) * (128 * 128) + r * 128;
         const uint32_t w[4] = {cur[j].x, cur[j].y, cur[j].z, cur[j].w};
 #pragma unroll
@@ -396,7 +398,9 @@ int4_repack_kernel(const int8_t* __restrict__ q, const __nv_bfloat16* __restrict
       const int pos = (e & 1) ? 4 + (e >> 1) : (e >> 1);   // e0 e2 e4 e6 e1 e3 e5 e7
       w |= nib << (4 * pos);
     }
-    wq[i] = w;
+    // [kb][n / 8][chunk = wi / 4][row = n % 8][word = wi % 4]: a warp reading one chunk of eight
+    // consecutive rows touches 128 contiguous bytes of the shared-memory copy (no bank conflicts)
+    wq[(((static_cast<long long>(kb) * (N / 8) + n / 8) * 4 + (wi >> 2)) * 8 + (n & 7)) * 4 + (wi & 3)] = w;
     if (wi == 0) scales_t[static_cast<size_t>(kb) * N + n] = scales[static_cast<size_t>(n) * KB + kb];
   }
 }
@@ -469,14 +473,20 @@ static int launch_int4(const CUtensorMap& tmap, const Int4Params& p, cudaStream_
 
 }  // namespace flyb200
 
+namespace flyb200 {
+int launch_int4_stream(void* c, const void* a, const void* wq, const void* scales_t, int M, int N, int K,
+                       int force_splits, cudaStream_t stream);  // int4_stream.cu
+}
+
 using namespace flyb200;
 
 extern "C" int flyb200_int4_repack(const int8_t* q, const void* scales, int32_t N, int32_t K, void* wq_out,
                                    void* scales_t_out, void* stream) {
   if (!q || !scales || !wq_out || !scales_t_out)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "int4_repack: NULL buffer");
-  if (N < 1 || K < 128 || K % 128 || reinterpret_cast<uintptr_t>(wq_out) % 16)
-    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "int4_repack: K %% 128 == 0 and a 16-byte aligned output");
+  if (N < 8 || N % 8 || K < 128 || K % 128 || reinterpret_cast<uintptr_t>(wq_out) % 16)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT,
+                     "int4_repack: K %% 128 == 0, N %% 8 == 0 and a 16-byte aligned output");
   const int sms = sm_count();
   if (sms <= 0) return FLYB200_ERR_CUDA;
   int4_repack_kernel<<<sms * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
@@ -494,6 +504,13 @@ extern "C" int flyb200_int4_gemm(void* c, const void* a, const void* wq, const v
   if (M < 1 || M > 64) return set_error(FLYB200_ERR_UNSUPPORTED, "int4_gemm: 1 <= M <= 64 (got %d)", M);
   if (N < 128 || N % 128 || K < 128 || K % 128)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "int4_gemm: N and K must be multiples of 128 (N=%d K=%d)", N, K);
+  // cfg.path: 1 = the register-dequantising mma.sync kernel (int4_stream.cu), 2 = the tcgen05 kernel
+  // of this file, 0 = whichever was measured faster: up to 32 tokens the former (21.5 / 26.9 us
+  // against 32.3 / 33.5 us at N = K = 8192), above that the latter (35.6 against 38.4 us at 64)
+  const int path = (cfg && cfg->path) ? cfg->path : (M <= 32 ? 1 : 2);
+  if (path != 2)
+    return launch_int4_stream(c, a, wq, scales_t, M, N, K, cfg ? cfg->split_k : 0,
+                              reinterpret_cast<cudaStream_t>(stream));
   const int sms = sm_count();
   if (sms <= 0) return FLYB200_ERR_CUDA;
   const I4Plan plan = plan_int4(M, N, K, sms, cfg ? cfg->split_k : 0);

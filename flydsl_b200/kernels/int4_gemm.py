@@ -34,15 +34,16 @@ def quantize_int4_groupwise(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor
 
 def pack_int4_weight(q: torch.Tensor, scales: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """int8 values ``[N, K]`` in [-8, 7] + bf16 scales ``[N, K/128]`` -> the kernel's layout:
-    packed uint8 ``[K/128, N, 64]`` and scales bf16 ``[K/128, N]`` (CUDA)."""
+    packed uint8 ``[K/128, N/8, 4, 8, 16]`` (per group and block of 8 rows: four 16-byte chunks, each
+    holding its 8 rows back to back) and scales bf16 ``[K/128, N]`` (CUDA). ``N % 8 == 0``."""
     if not q.is_cuda:
         raise ValueError("pack_int4_weight needs CUDA tensors (this library has no CPU path)")
     N, K = q.shape
-    if q.dtype != torch.int8 or K % GROUP or tuple(scales.shape) != (N, K // GROUP):
-        raise ValueError("expected int8 [N, K] with K % 128 == 0 and scales [N, K/128]")
+    if q.dtype != torch.int8 or K % GROUP or N % 8 or tuple(scales.shape) != (N, K // GROUP):
+        raise ValueError("expected int8 [N, K] with K % 128 == 0, N % 8 == 0 and scales [N, K/128]")
     q = q.contiguous()
     scales = scales.to(torch.bfloat16).contiguous()
-    wq = torch.empty((K // GROUP, N, 64), dtype=torch.uint8, device=q.device)
+    wq = torch.empty((K // GROUP, N // 8, 4, 8, 16), dtype=torch.uint8, device=q.device)
     st = torch.empty((K // GROUP, N), dtype=torch.bfloat16, device=q.device)
     with torch.cuda.device(q.device):
         _lib.check(_lib.load().flyb200_int4_repack(q.data_ptr(), scales.data_ptr(), N, K, wq.data_ptr(),
@@ -54,9 +55,12 @@ class Int4GemmLauncher:
     """``fn(c, a, wq, scales_t, m, stream)``: c bf16 ``[m, N]``; a bf16 ``[m, K]``; ``wq`` / ``scales_t``
     from :func:`pack_int4_weight`."""
 
-    def __init__(self, N: int, K: int, split_k: Optional[int]):
+    def __init__(self, N: int, K: int, split_k: Optional[int], path: str = "auto"):
+        if path not in ("auto", "stream", "tensor"):
+            raise ValueError("path must be 'auto', 'stream' (mma.sync, weights unpacked in registers) or "
+                             "'tensor' (tcgen05, weights unpacked through shared memory)")
         self.N, self.K = int(N), int(K)
-        self._cfg = _lib.GemmCfg(0, 0, 0, int(split_k or 0))
+        self._cfg = _lib.GemmCfg(0, 0, {"auto": 0, "stream": 1, "tensor": 2}[path], int(split_k or 0))
         self._fn = _lib.load().flyb200_int4_gemm
 
     def __call__(self, c, a, wq, scales_t, m, stream=None):
@@ -73,10 +77,13 @@ class Int4GemmLauncher:
 
 
 @functools.lru_cache(maxsize=256)
-def compile_int4_weight_only_gemm(*, N: int, K: int, group_size: int = GROUP, split_k: Optional[int] = None):
-    """Launcher for ``C[m, N] = A[m, K] @ dequant(W)^T``, ``m <= 64`` chosen per call."""
+def compile_int4_weight_only_gemm(*, N: int, K: int, group_size: int = GROUP, split_k: Optional[int] = None,
+                                  path: str = "auto"):
+    """Launcher for ``C[m, N] = A[m, K] @ dequant(W)^T``, ``m <= 64`` chosen per call. ``path`` picks
+    the kernel: ``"stream"`` (csrc/int4_stream.cu), ``"tensor"`` (csrc/int4_gemm.cu) or ``"auto"``
+    (the default: the former up to 32 tokens, the latter above)."""
     if group_size != GROUP:
         raise ValueError(f"group_size must be {GROUP}")
     if N % 128 or K % 128:
         raise ValueError(f"N and K must be multiples of 128 (N={N}, K={K})")
-    return Int4GemmLauncher(N, K, split_k)
+    return Int4GemmLauncher(N, K, split_k, path)

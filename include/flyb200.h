@@ -52,6 +52,7 @@ typedef struct flyb200_gemm_cfg {
   int32_t block_n;  /* MMA N / CTA tile width: 32, 64, 128 or 256; 0 = auto */
   int32_t max_ctas; /* cap on the persistent grid; 0 = one CTA per SM       */
   int32_t path;     /* dense GEMM: 0 = auto, 1 = tiled kernel, 2 = decode kernel (M <= 64).
+                     * int4 GEMM: see flyb200_int4_gemm.
                      * MoE stages: bit 0 = activations already in routing order (TMA-fed),
                      *             bit 1 = stage-1 output in routing order                   */
   int32_t split_k;  /* decode kernel: K splits per weight tile (cluster size, 1..8); 0 = auto    */
@@ -276,15 +277,19 @@ int flyb200_ep_pull_combine(const void* const* peers, int64_t part_off, const ui
  * reference has no kernel of this exact format -- nearest: the W4A16 path of
  * kernels/moe_gemm_2stage.py:607-630 and the int4 unpack of kernels/mfma_preshuffle_pipeline.py:202-222). ---- */
 
-/* q int8 [N, K] with values in [-8, 7] and scales bf16 [N, K/128] -> wq_out uint8 [K/128][N][64]
- * (nibble = q + 8; the eight nibbles of a 32-bit word hold K elements e0 e2 e4 e6 e1 e3 e5 e7) and
- * scales_t_out bf16 [K/128][N]. K % 128 == 0. */
+/* q int8 [N, K] with values in [-8, 7] and scales bf16 [N, K/128] -> wq_out uint8
+ * [K/128][N/8][4][8][16]: per 128-K group and block of 8 rows, four 16-byte chunks (32 K elements
+ * each), each chunk holding its 8 rows back to back (nibble = q + 8; the eight nibbles of a 32-bit
+ * word hold K elements e0 e2 e4 e6 e1 e3 e5 e7), and scales_t_out bf16 [K/128][N].
+ * K % 128 == 0, N % 8 == 0. */
 int flyb200_int4_repack(const int8_t* q, const void* scales, int32_t N, int32_t K, void* wq_out,
                         void* scales_t_out, void* stream);
 
 /* c bf16 [M, N] = a bf16 [M, K] * dequant(W)^T, W as produced by flyb200_int4_repack; fp32
  * accumulation, the group scale applied per 128-K group in fp32. 1 <= M <= 64; N, K % 128 == 0.
- * cfg (optional): split_k forces the split-K factor (cluster size, 1..8). */
+ * cfg (optional): split_k forces the split-K factor (cluster size, 1..8); path picks the kernel:
+ * 1 = weights unpacked in registers and fed to mma.sync (faster up to 32 tokens), 2 = weights
+ * unpacked through shared memory for tcgen05.mma, 0 = by token count. Same arithmetic either way. */
 int flyb200_int4_gemm(void* c, const void* a, const void* wq, const void* scales_t, int32_t M, int32_t N,
                       int32_t K, const flyb200_gemm_cfg* cfg, void* stream);
 

@@ -36,16 +36,18 @@ def int4_gemm_ref(a: torch.Tensor, q: torch.Tensor, scales: torch.Tensor) -> tor
 
 
 def pack_int4_ref(q: np.ndarray) -> np.ndarray:
-    """The kernel's packed layout in numpy: q int8 [N, K] -> uint8 [K/128, N, 64]. Nibble = q + 8; the
-    eight nibbles of a 32-bit little-endian word hold K elements e0 e2 e4 e6 e1 e3 e5 e7."""
+    """The kernel's packed layout in numpy: q int8 [N, K] -> uint8 [K/128, N/8, 4, 8, 16]: per group of
+    128 K elements and block of 8 rows, four 16-byte chunks (32 K elements each), each chunk holding
+    its 8 rows back to back. Nibble = q + 8; the eight nibbles of a 32-bit little-endian word hold K
+    elements e0 e2 e4 e6 e1 e3 e5 e7. N % 8 == 0."""
     N, K = q.shape
     nib = (q.astype(np.int32) + 8).astype(np.uint32).reshape(N, K // GROUP, 16, 8)
     order = [0, 2, 4, 6, 1, 3, 5, 7]
     word = np.zeros((N, K // GROUP, 16), dtype=np.uint32)
     for pos, e in enumerate(order):
         word |= nib[..., e] << np.uint32(4 * pos)
-    out = word.transpose(1, 0, 2).copy()                       # [K/128, N, 16] words
-    return out.view(np.uint8).reshape(K // GROUP, N, 64)
+    out = word.reshape(N // 8, 8, K // GROUP, 4, 4).transpose(2, 0, 3, 1, 4).copy()   # [g, n/8, chunk, row, word]
+    return out.view(np.uint8).reshape(K // GROUP, N // 8, 4, 8, 16)
 
 
 def make_int4_case(M: int, N: int, K: int, seed: int = 0, w_std: float = 0.02):

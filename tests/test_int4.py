@@ -17,8 +17,8 @@ def test_oracle_quantiser_and_pack_layout():
     assert (err <= 0.5 * s.float() * 1.01 + 1e-8).all()
     # packed layout: unpack by the documented rule and compare
     packed = R.pack_int4_ref(q.numpy())
-    assert packed.shape == (4, 256, 64)
-    words = packed.reshape(4, 256, 16, 4).view(np.uint32)[..., 0]
+    assert packed.shape == (4, 32, 4, 8, 16)          # [group, row / 8, chunk, row % 8, 16 bytes]
+    words = packed.view(np.uint32).reshape(4, 32, 4, 8, 4).transpose(0, 1, 3, 2, 4).reshape(4, 256, 16)
     order = [0, 2, 4, 6, 1, 3, 5, 7]
     back = np.zeros((4, 256, 16, 8), dtype=np.int32)
     for pos, e in enumerate(order):
@@ -44,22 +44,24 @@ def test_gpu_pack_matches_oracle_layout():
 @pytest.mark.gpu
 @pytest.mark.parametrize("M,N,K,split_k", [(1, 256, 512, None), (7, 384, 1024, 1), (16, 1024, 2048, 2),
                                            (33, 512, 1024, 4), (64, 1024, 1024, None), (16, 8192, 8192, None),
-                                           (64, 8192, 8192, None), (1, 8192, 8192, None)])
-def test_gpu_int4_gemm_vs_oracle(M, N, K, split_k):
+                                           (64, 8192, 8192, None), (1, 8192, 8192, None),
+                                           (17, 128, 128, None), (32, 640, 3072, 8), (48, 256, 8192, 3)])
+@pytest.mark.parametrize("path", ["stream", "tensor"])
+def test_gpu_int4_gemm_vs_oracle(M, N, K, split_k, path):
     from flydsl_b200 import _lib
     from flydsl_b200.kernels import compile_int4_weight_only_gemm, pack_int4_weight
 
     c = R.make_int4_case(M, N, K, seed=M + N)
     ref = R.int4_gemm_ref(c["a"], c["q"], c["scales"])
     wq, st = pack_int4_weight(c["q"].cuda(), c["scales"].cuda())
-    fn = compile_int4_weight_only_gemm(N=N, K=K, split_k=split_k)
+    fn = compile_int4_weight_only_gemm(N=N, K=K, split_k=split_k, path=path)
     out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
     fn(out, c["a"].cuda(), wq, st, M, None)
     out2 = torch.empty_like(out)
     fn(out2, c["a"].cuda(), wq, st, M, torch.cuda.current_stream())
     torch.cuda.synchronize()
     assert _lib.query_device_error() == 0
-    assert_close_to_oracle(out, ref, f"int4 M={M} N={N} K={K} split_k={split_k}")
+    assert_close_to_oracle(out, ref, f"int4 {path} M={M} N={N} K={K} split_k={split_k}")
     assert torch.equal(out, out2)                       # fixed summation order
 
 
