@@ -83,6 +83,10 @@ moe_sort_kernel(const SortParams p) {
   __shared__ int my_compact_id;
 
   const int e = blockIdx.x;
+  // Fused permute with few experts: gridDim.y CTAs per expert. Each repeats the (cheap, L2-fed)
+  // placement of the expert's routes -- all of them write the same sorted ids -- and copies every
+  // gridDim.y-th row, so that the copy is spread over the whole GPU instead of E SMs.
+  const int part = blockIdx.y, parts = gridDim.y;
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
@@ -90,7 +94,7 @@ moe_sort_kernel(const SortParams p) {
   const int sentinel = (p.k << 24) | p.T;
 
   // A masked expert owns no rows and nobody depends on its CTA (CTA 0 also writes the buffer tails).
-  if (e != 0 && p.expert_mask && p.expert_mask[e] == 0) return;
+  if ((e != 0 || part != 0) && p.expert_mask && p.expert_mask[e] == 0) return;
   for (int i = tid; i < p.E; i += kSortThreads) hist[i] = 0;
   __syncthreads();
   const bool vec_ok = (reinterpret_cast<uintptr_t>(p.topk_ids) & 15) == 0;
@@ -140,7 +144,7 @@ moe_sort_kernel(const SortParams p) {
   const int total = total_rows;
 
   // Tail of the buffers beyond the used rows/blocks, and the counters: CTA 0.
-  if (e == 0) {
+  if (e == 0 && part == 0) {
     for (int i = total + tid; i < p.max_len; i += kSortThreads) {
       p.sorted_ids[i] = sentinel;
       p.sorted_weights[i] = 0.f;
@@ -234,7 +238,7 @@ moe_sort_kernel(const SortParams p) {
   __syncthreads();   // this CTA's sorted ids are visible to all of its threads
   const int chunks = p.K / 16;
   const int nscale = p.K / 128;
-  for (int i = warp; i < my_padded; i += kSortThreads / 32) {
+  for (int i = warp + part * (kSortThreads / 32); i < my_padded; i += parts * (kSortThreads / 32)) {
     const int r = my_base + i;
     const int t = p.sorted_ids[r] & 0xFFFFFF;
     const bool ok = i < my_cnt && t < p.rows_in;
@@ -255,7 +259,7 @@ moe_sort_kernel(const SortParams p) {
     }
   }
   // scales: sorted position fastest, so that the stores to the transposed output are coalesced
-  for (int j = tid; j < nscale * my_padded; j += kSortThreads) {
+  for (int j = tid + part * kSortThreads; j < nscale * my_padded; j += parts * kSortThreads) {
     const int sidx = j / my_padded;
     const int i = j - sidx * my_padded;
     const int t = p.sorted_ids[my_base + i] & 0xFFFFFF;
@@ -367,7 +371,14 @@ static int moe_sort_impl(const int32_t* topk_ids, const float* topk_weights, int
   p.x = static_cast<const uint4*>(x); p.xs_t = xs_t;
   p.x_out = static_cast<uint4*>(x_out); p.xs_out = xs_out;
   p.K = K; p.rows_in = T;
-  moe_sort_kernel<<<E, kSortThreads, 2 * E * sizeof(int),
+  int parts = 1;
+  if (x) {
+    const int sms = sm_count();
+    if (sms <= 0) return FLYB200_ERR_CUDA;
+    parts = (2 * sms) / E;
+    parts = parts < 1 ? 1 : (parts > 8 ? 8 : parts);
+  }
+  moe_sort_kernel<<<dim3(E, parts), kSortThreads, 2 * E * sizeof(int),
                     reinterpret_cast<cudaStream_t>(stream)>>>(p);
   FLYB200_CUDA_CHECK(cudaGetLastError());
   return FLYB200_OK;
