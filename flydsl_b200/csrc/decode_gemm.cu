@@ -44,15 +44,25 @@ template <int NT>
 struct DecCfg {
   static constexpr int kXTileBytes = NT * 128;
   static constexpr int kStageBytes = kWTileBytes + kXTileBytes;
-  static constexpr int kAccBufs = (256 / NT) > 8 ? 8 : (256 / NT);   // <= 256 TMEM columns per CTA
+  // Four accumulator buffers (64-256 TMEM columns): with the small shared-memory footprint below,
+  // three or four CTAs fit an SM, so the CTAs of the NEXT launch (programmatic dependent launch) are
+  // resident and streaming their weights while this launch exchanges, reduces and stores.
+  static constexpr int kAccBufs = (256 / NT) > 4 ? 4 : (256 / NT);
   static constexpr int kTmemCols = NT * kAccBufs < 32 ? 32 : NT * kAccBufs;
   // fp32 partial sums received from the cluster: [sender][local column][128]; sender count x
   // columns per owner can exceed NT by up to splits-1 because of rounding
   static constexpr int kPartialBytes = (NT + 8) * 128 * 4;
+  // The pipeline ring doubles as send buffer ([0, NT) token rows) and receive area (behind it) of
+  // the split-K exchange: every MMA of the whole cluster has completed before the first copy.
+  static constexpr int kExchangeBytes = NT * 512 + kPartialBytes;
+  __host__ __device__ static int ring_bytes(int stages) {
+    const int r = stages * kStageBytes;
+    return r > kExchangeBytes ? r : kExchangeBytes;
+  }
   static constexpr int kScaleBytes = kDecMaxStages * 2 * (NT + 1) * 4 + 64;  // generous
   static constexpr int kMiscBytes = 1024;
   static int smem_bytes(int stages, int kbps) {
-    return stages * kStageBytes + kPartialBytes + (kbps * (NT + 1) * 4 + 64) + kMiscBytes + 1024;
+    return ring_bytes(stages) + (kbps * (NT + 1) * 4 + 64) + kMiscBytes + 1024;
   }
 };
 
@@ -69,12 +79,12 @@ bs_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecodePa
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t recv_base = smem_base + stages * C::kStageBytes;   // fp32 [sender][column][128]
-  float* recv = reinterpret_cast<float*>(smem_al + stages * C::kStageBytes);
-  float* sa_s = recv + (NT + 8) * 128;                              // [kbps][NT]
+  const int ring_bytes = C::ring_bytes(stages);
+  const uint32_t recv_base = smem_base + NT * 512;                  // fp32 [sender][column][128], in the ring
+  float* recv = reinterpret_cast<float*>(smem_al + NT * 512);
+  float* sa_s = reinterpret_cast<float*>(smem_al + ring_bytes);     // [kbps][NT]
   float* sb_s = sa_s + p.kbps * NT;                                            // [kbps]
-  const uint32_t misc_off = stages * C::kStageBytes + C::kPartialBytes +
-                            ((p.kbps * (NT + 1) * 4 + 63) & ~63);
+  const uint32_t misc_off = static_cast<uint32_t>(ring_bytes) + ((p.kbps * (NT + 1) * 4 + 63) & ~63);
   const uint32_t bar_base = smem_base + misc_off;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto done_bar = [&](uint32_t i) { return bar_base + 8u * (kDecMaxStages + i); };
@@ -137,6 +147,11 @@ bs_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecodePa
       mbar_arrive_expect_tx(full_bar(i), rows_w * 128 + C::kXTileBytes);
       bulk_load(sw, p.b + (static_cast<size_t>(kb_begin + i) * p.N + n0) * 128, rows_w * 128, full_bar(i));
     }
+    // the weight tiles beyond the ring go to L2 now, so that their loads (issued when a stage frees
+    // up, after the wait) do not pay an HBM latency each: 2.3 -> 0.9 us for the fourth K block of a
+    // three-stage ring in a trace of back-to-back launches
+    for (int i = first_fill; i < count; ++i)
+      l2_prefetch(p.b + (static_cast<size_t>(kb_begin + i) * p.N + n0) * 128, rows_w * 128);
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -158,6 +173,8 @@ bs_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecodePa
         tma_load_2d(sw + kWTileBytes, &tmap_x, kb * 128, 0, full_bar(s));
       }
     }
+    __syncwarp();
+    cluster_sync_all();   // (exchange barrier, see the epilogue)
   } else if (warp == 1) {
     if (lane == 0) {
       // ---------------- MMA issuer ----------------
@@ -180,6 +197,8 @@ bs_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecodePa
         tc_commit(done_bar(i % kDone));
       }
     }
+    __syncwarp();
+    cluster_sync_all();   // (exchange barrier, see the epilogue)
   } else {
     // ---------------- epilogue: 128 threads, thread = output column n (accumulator lane) ----------
     const int et = threadIdx.x - 64;            // 0..127
@@ -237,10 +256,18 @@ bs_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecodePa
     // column j = j / cpc). Partials go to this CTA's own shared memory as [j][n] (the pipeline
     // stages are free by now: every MMA of this CTA has completed), then one bulk copy per owner
     // moves that owner's column slice into its receive area, slot [sender][local column][n].
+    // Exchange barrier: the send and receive areas live in the pipeline ring, so no copy may start
+    // before every CTA of the cluster has consumed its last stage (the epilogue has seen the commit
+    // of its last K block by now; the other warps arrive as soon as they have issued their work).
+    // The send area is this CTA's own (only its finished MMAs read it), so it is written between
+    // the arrival and the wait.
+    __syncwarp();
+    cluster_arrive();
     float* send = reinterpret_cast<float*>(smem_al);
 #pragma unroll
     for (int j = 0; j < NT; ++j)
       if (j < p.M) send[j * 128 + n_loc] = acc[j];
+    cluster_wait();
     fence_proxy_async_smem();
     asm volatile("bar.sync 1, 128;" ::: "memory");
     const int cpc = (p.M + p.splits - 1) / p.splits;
@@ -330,15 +357,24 @@ static DecodePlan plan_decode(int M, int N, int K, int sms, int force_splits) {
     if (s_eff != s && force_splits <= 0) continue;  // same plan as a smaller s
     int stages = kbps < kDecMaxStages ? kbps : kDecMaxStages;
     if (stages < 2) stages = 2;  // the stage area doubles as the send buffer of the exchange
-    const int fixed = (nt + 8) * 512 + kbps * (nt + 1) * 4 + 64 + 2048;
+    const int fixed = kbps * (nt + 1) * 4 + 64 + 2048;
+    const int exchange = (2 * nt + 8) * 512;   // send + receive areas, inside the ring
+    // Three stages: with more, the CTAs of a deep-K plan (seven K blocks each at K = 7168) no longer
+    // fit three to an SM and the launch needs a second wave (13.5 -> 11.1 us at M=32, N=4096).
+    if (stages > 3) stages = 3;
     while (stages > 2 && stages * stage_bytes + fixed > 232448) --stages;
-    const int smem = stages * stage_bytes + fixed;
+    const int ring = stages * stage_bytes > exchange ? stages * stage_bytes : exchange;
+    const int smem = ring + fixed;
     if (smem > 232448) continue;
     int cps = 232448 / (smem + 1024);
-    if (cps > 2) cps = 2;  // TMEM: 256 columns per CTA
+    const int tmem_cols = nt * 4 < 32 ? 32 : nt * 4;
+    if (cps > 512 / tmem_cols) cps = 512 / tmem_cols;
+    if (cps > 4) cps = 4;
     if (cps < 1) continue;
     const long ctas = static_cast<long>(n_tiles) * s_eff;
-    const long slots = static_cast<long>(sms) * cps;
+    // the K split is chosen as if two CTAs shared an SM (more splits only lengthen the exchange);
+    // the rest of the SM is left to the next launch
+    const long slots = static_cast<long>(sms) * (cps > 2 ? 2 : cps);
     const long rounds = (ctas + slots - 1) / slots;
     // a round costs the MMA-issue time of its K blocks (~0.2 us each; two co-resident CTAs share
     // the SM) plus a fixed ~1 us (fill latency, reduction, store)

@@ -150,17 +150,36 @@ int4_stream_kernel(const __grid_constant__ CUtensorMap tmap_x, const Int4StreamP
   __syncthreads();
   cluster_sync_all();   // the receive barriers of the whole cluster exist before anybody signals them
 
+  // Programmatic dependent launch: the packed weights and group scales of the first ring fill are
+  // requested BEFORE the dependency wait -- they are parameters, never the result of the kernel that
+  // runs just before (a kernel of this library that lets its dependents start early writes no
+  // weights; any other kernel has exited before this one starts) -- so that back-to-back launches
+  // stream weights while the previous one still reduces and stores. The tokens are read after it.
+  const int first_fill = count < slots ? count : slots;
+  if (warp == kConsumers && lane == 0 && count > 0) {
+    mbar_arrive_expect_tx(scale_bar, static_cast<uint32_t>(count) * 256u);
+    for (int i = 0; i < count; ++i)
+      bulk_load(smem_base + scale_off + i * 256, p.scales_t + static_cast<size_t>(kb_begin + i) * p.N + n0,
+                256, scale_bar);
+    for (int i = 0; i < first_fill; ++i) {
+      mbar_arrive_expect_tx(full_bar(i), C::kSlotBytes);
+      bulk_load(smem_base + i * C::kSlotBytes, p.wq + (static_cast<size_t>(kb_begin + i) * p.N + n0) * 64,
+                kS4PackedBytes, full_bar(i));
+    }
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == kConsumers) {
     if (lane == 0 && count > 0) {
       // ---------------- producer ----------------
-      mbar_arrive_expect_tx(scale_bar, static_cast<uint32_t>(count) * 256u);
-      for (int i = 0; i < count; ++i)
-        bulk_load(smem_base + scale_off + i * 256, p.scales_t + static_cast<size_t>(kb_begin + i) * p.N + n0,
-                  256, scale_bar);
-      for (int i = 0; i < count; ++i) {
+      for (int i = 0; i < first_fill; ++i) {   // tokens of the slots whose weights are on their way
+        const uint32_t base = smem_base + i * C::kSlotBytes;
+        const int k0 = (kb_begin + i) * 128;
+        tma_load_2d(base + kS4PackedBytes, &tmap_x, k0, 0, full_bar(i));
+        tma_load_2d(base + kS4PackedBytes + C::kXSub, &tmap_x, k0 + 64, 0, full_bar(i));
+      }
+      for (int i = first_fill; i < count; ++i) {
         const int s = i % slots;
         if (i >= slots &&
             !mbar_wait(empty_bar(s), ((i / slots) & 1) ^ 1, abort_flag, p.err, kErrWaitSmemEmpty))
@@ -349,7 +368,6 @@ static S4Plan plan_int4_stream(int M, int N, int K, int sms, int force_splits) {
   const int n_tiles = N / 128;
   const int KBt = K / 128;
   const int slot = kS4PackedBytes + 2 * 16 * mb * 128;
-  const int cps_max = 1;
   double best_cost = 1e30;
   for (int s = 1; s <= 8; ++s) {
     if (force_splits > 0 && s != force_splits) continue;
@@ -358,14 +376,16 @@ static S4Plan plan_int4_stream(int M, int N, int K, int sms, int force_splits) {
     if (s_eff != s && force_splits <= 0) continue;
     const long ctas = static_cast<long>(n_tiles) * s_eff;
     const long per_sm = (ctas + sms - 1) / sms;
-    const int cps = per_sm >= 2 ? cps_max : 1;
+    // up to 32 tokens a CTA takes at most half of an SM's shared memory, so that the CTAs of the
+    // next launch are resident (and prefetching) while this one computes
+    const int cps = mb <= 2 ? 2 : 1;
     const int fixed = (16 * mb + 8) * 512 + kbps * 256 + 2048;
     int slots = (232448 / cps - 1024 - fixed) / slot;
     if (slots > kS4MaxSlots) slots = kS4MaxSlots;
     if (slots > kbps) slots = kbps;
     if (slots < 2) slots = 2;   // the ring doubles as the send buffer of the exchange
     if (slots * slot + fixed > 232448) continue;
-    const long waves = (ctas + static_cast<long>(sms) * cps - 1) / (static_cast<long>(sms) * cps);
+    const long waves = (ctas + sms - 1) / sms;
     const double cost = static_cast<double>(per_sm) * kbps + 6.0 * waves + 0.5 * s_eff;
     if (cost < best_cost - 1e-9) {
       best_cost = cost;
