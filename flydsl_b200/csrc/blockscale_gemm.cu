@@ -586,6 +586,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const float* sb0;    // scale_b of column group 0; K block kb at sb0 + kb
       const float* sb1;    // ... group 1
       long long sa_step;
+      bool active;         // MoE: some row of this warp's 32 holds a token (warp-uniform)
     };
     // What the store phase needs; recomputed after the loop instead of being kept live through it.
     struct OutCtx {
@@ -623,7 +624,10 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int e = p.expert_ids[m_blk];
         if (e < 0 || e >= p.experts) return false;
         int t, slot;
-        moe_row(m_blk, t, slot);   // (0, 0) for rows without a valid token
+        // (0, 0) for rows without a valid token. A warp whose 32 rows are all padding (most of an
+        // expert's second row block) skips the TMEM reads and the promotion of the whole tile: its
+        // results are never stored, and the kernel runs against the power cap.
+        c.active = __any_sync(0xffffffffu, moe_row(m_blk, t, slot));
         if (p.a_sorted) {   // scales follow the permuted activations: one per sorted row
           sa_idx = static_cast<long long>(m_blk) * p.tile_m + (r < p.tile_m ? r : 0);
           c.sa_step = p.a_rows;
@@ -771,16 +775,19 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               break;
             }
             tc_fence_after();
-            // Loads of LDW columns are software-pipelined against the FMAs of the previous load (two
-            // register buffers); the buffer goes back to the issuer as soon as the last load landed.
-            uint32_t va[LDW], vb[LDW];
-            tmem_ld<LDW>(taddr(0), va);
-            tmem_wait_dep<LDW>(va);
             auto release = [&]() {
               tc_fence_before();
               __syncwarp();
               if (lane == 0) mbar_arrive(tempty_bar(buf));
             };
+            // Loads of LDW columns are software-pipelined against the FMAs of the previous load (two
+            // register buffers); the buffer goes back to the issuer as soon as the last load landed.
+            uint32_t va[LDW], vb[LDW];
+            if (MODE != kDense && !cur.active) {
+              release();
+            } else {
+            tmem_ld<LDW>(taddr(0), va);
+            tmem_wait_dep<LDW>(va);
 #pragma unroll
             for (int q = 0; q < NQ; ++q) {
               uint32_t* cv = (q & 1) ? vb : va;
@@ -797,6 +804,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 tmem_wait_dep<LDW>(nv);
                 if (q + 2 == NQ) release();
               }
+            }
             }
             ++it;
             if (++dn_i == kDone) {
