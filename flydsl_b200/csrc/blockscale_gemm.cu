@@ -888,7 +888,9 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             auto quot = [&](float y) -> float {
               if (exact_div) return __fdiv_rn(y, scale);
               const float q0 = y * rc;
-              return __fmaf_rn(__fmaf_rn(-scale, q0, y), rc, q0);
+              const float qc = __fmaf_rn(__fmaf_rn(-scale, q0, y), rc, q0);
+              // the sign of y, for the one case the correction step loses it: -0 / scale = -0
+              return __uint_as_float(__float_as_uint(qc) | (__float_as_uint(y) & 0x80000000u));
             };
 #pragma unroll
             for (int j = 0; j < CH; j += 16) {

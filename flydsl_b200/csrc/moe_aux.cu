@@ -5,6 +5,8 @@
 //     stages, tests/kernels/test_moe_blockscale.py:346-361 + pertoken_quant tests/utils.py:29-73)
 #include <cuda_fp8.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace flyb200 {
@@ -57,93 +59,112 @@ moe_reduce_kernel(const T* __restrict__ x, T* __restrict__ y, const uint8_t* __r
 }
 
 // 16-bit inputs: half a warp per 128-wide group (16 lanes x 16 bytes), so a warp moves 512 bytes per
-// load instruction; the amax reduction stays inside the half-warp. `raw` holds the lane's 8 values.
+// load instruction; the amax reduction stays inside the half-warp. `raw` holds the lane's 8 values
+// (zeros for a lane without work). The kernel is bound by its instruction count, so the group's amax
+// is taken on the packed 16-bit patterns: |v| as unsigned 16-bit integers order like the values, and
+// anything at or above the pattern of +Inf is an Inf/NaN, so one and + one packed max per PAIR of
+// elements finds both the amax and whether the rare clean-up path (NaN -> 0, +-Inf -> +-448, as
+// pertoken_quant's nan_to_num does) is needed at all.
 template <typename T>
-__device__ __forceinline__ void quant_group16(const uint4& raw, uint8_t* __restrict__ q,
-                                              float* __restrict__ scale_t, int64_t row, int g,
-                                              int cols, int64_t scale_stride, bool active, int sub) {
+__device__ __forceinline__ void quant_group16(const uint4& raw, uint8_t* __restrict__ q_dst,
+                                              float* __restrict__ scale_dst, bool active, int sub) {
+  constexpr uint32_t kInfBits = (sizeof(T) == 2 && std::is_same<T, __half>::value) ? 0x7c00u : 0x7f80u;
+  const uint32_t m2 = __vmaxu2(__vmaxu2(raw.x & 0x7fff7fffu, raw.y & 0x7fff7fffu),
+                               __vmaxu2(raw.z & 0x7fff7fffu, raw.w & 0x7fff7fffu));
+  uint32_t amax_bits = max(m2 & 0xffffu, m2 >> 16);
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1)  // xor distances < 16 stay inside the half-warp
+    amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, o));
   float v[8];
   const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) v[j] = active ? to_f32<T>(e[j]) : 0.f;
-  float vmax = -3.4e38f, vmin = 3.4e38f;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    if (v[j] != v[j]) v[j] = 0.f;
-    else if (isinf(v[j])) v[j] = v[j] > 0 ? 448.f : -448.f;
-    vmax = fmaxf(vmax, v[j]);
-    vmin = fminf(vmin, v[j]);
-  }
-#pragma unroll
-  for (int o = 8; o > 0; o >>= 1) {  // xor distances < 16 stay inside the half-warp
-    vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
-    vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, o));
-  }
-  float scale = __fdiv_rn(fmaxf(vmax, -vmin), 448.f);
-  if (scale == 0.f) scale = 1.f;
-  if (active) {
-    // v / scale, correctly rounded, from one reciprocal: q0 = v*rc, q = fma(fma(-scale, q0, v), rc, q0)
-    // is the IEEE quotient when rc is the correctly rounded reciprocal and the mantissa of scale is
-    // not all ones (Markstein); that rare scale takes the true division. Eight IEEE divisions per
-    // lane made this kernel compute-bound at a quarter of the copy bandwidth.
-    const float rc = __frcp_rn(scale);
-    const bool exact_div = (__float_as_uint(scale) & 0x7fffffu) == 0x7fffffu;
-    float qv[8];
+  for (int j = 0; j < 8; ++j) v[j] = to_f32<T>(e[j]);
+  float amax;
+  if (__any_sync(0xffffffffu, amax_bits >= kInfBits)) {
+    float vmax = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float q0 = v[j] * rc;
-      qv[j] = exact_div ? __fdiv_rn(v[j], scale) : __fmaf_rn(__fmaf_rn(-scale, q0, v[j]), rc, q0);
+      if (v[j] != v[j]) v[j] = 0.f;
+      else if (isinf(v[j])) v[j] = v[j] > 0 ? 448.f : -448.f;
+      vmax = fmaxf(vmax, fabsf(v[j]));
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+    amax = vmax;
+  } else if constexpr (std::is_same<T, __half>::value) {
+    amax = __half2float(__ushort_as_half(static_cast<unsigned short>(amax_bits)));
+  } else {
+    amax = __uint_as_float(amax_bits << 16);
+  }
+  // Quotients from one reciprocal: q0 = y*rc, q = fma(fma(-d, q0, y), rc, q0) is the IEEE quotient
+  // y/d when rc is the correctly rounded reciprocal of d, the mantissa of d is not all ones and
+  // nothing is subnormal (Markstein); the rare other cases take the true division.
+  float scale;
+  {
+    constexpr float kRc448 = 1.0f / 448.0f;   // correctly rounded by the compiler
+    const float q0 = amax * kRc448;
+    scale = __fmaf_rn(__fmaf_rn(-448.f, q0, amax), kRc448, q0);
+  }
+  const bool tiny = amax < 1e-30f;            // quotient or residual may be subnormal
+  if (__any_sync(0xffffffffu, tiny)) scale = __fdiv_rn(amax, 448.f);
+  if (scale == 0.f) scale = 1.f;
+  if (active) {
+    float qv[8];
+    if (((__float_as_uint(scale) & 0x7fffffu) == 0x7fffffu) || tiny) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) qv[j] = __fdiv_rn(v[j], scale);
+    } else {
+      const float rc = __frcp_rn(scale);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float q0 = v[j] * rc;
+        const float qc = __fmaf_rn(__fmaf_rn(-scale, q0, v[j]), rc, q0);
+        // the sign of the input, for the one case the correction step loses it: -0 / scale = -0
+        qv[j] = __uint_as_float(__float_as_uint(qc) | (__float_as_uint(v[j]) & 0x80000000u));
+      }
     }
     const uint32_t lo = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qv[0], qv[1]), __NV_SATFINITE, __NV_E4M3)) |
                         (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qv[2], qv[3]), __NV_SATFINITE, __NV_E4M3)) << 16);
     const uint32_t hi = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qv[4], qv[5]), __NV_SATFINITE, __NV_E4M3)) |
                         (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qv[6], qv[7]), __NV_SATFINITE, __NV_E4M3)) << 16);
-    *reinterpret_cast<uint2*>(q + row * cols + g * 128 + sub * 8) = make_uint2(lo, hi);
-    if (sub == 0) scale_t[static_cast<int64_t>(g) * scale_stride + row] = scale;
+    *reinterpret_cast<uint2*>(q_dst) = make_uint2(lo, hi);
+    if (sub == 0) *scale_dst = scale;
   }
 }
 
-// rows x (cols/128) groups, two groups per warp per step (one per half-warp), four steps' loads in
-// flight at once: the kernel is a dependent load -> reduce -> divide -> store chain per group and was
-// latency-bound at a quarter of the copy bandwidth with one group per thread in flight.
+// A warp takes whole rows (the input streams sequentially, no index arithmetic beyond additions),
+// two groups per step (one per half-warp), four steps' loads in flight at once: a dependent load ->
+// reduce -> divide -> store chain per group is latency-bound with one.
 template <typename T>
 __device__ __forceinline__ void quant_rows16(const T* __restrict__ x, uint8_t* __restrict__ q,
                                              float* __restrict__ scale_t, int64_t rows,
                                              int64_t scale_stride, int cols) {
   constexpr int kInFlight = 4;
   const int groups = cols / 128;
-  const int64_t total = rows * groups;
   const int lane = threadIdx.x & 31;
   const int sub = lane & 15;
-  const int64_t hw0 = ((blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5) * 2 + (lane >> 4);
-  const int64_t nhw = ((static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5) * 2;
-  for (int64_t w = hw0 - (lane >> 4); w < total; w += nhw * kInFlight) {  // warp-uniform trip count
-    uint4 raw[kInFlight];
-    int64_t row[kInFlight];
-    int g[kInFlight];
-    bool active[kInFlight];
+  const int hw = lane >> 4;
+  const int64_t warp0 = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t row = warp0; row < rows; row += nwarps) {
+    const T* xrow = x + row * cols + sub * 8;
+    uint8_t* qrow = q + row * cols + sub * 8;
+    float* srow = scale_t + row;
+    for (int g0 = 0; g0 < groups; g0 += 2 * kInFlight) {
+      uint4 raw[kInFlight];
 #pragma unroll
-    for (int u = 0; u < kInFlight; ++u) {
-      const int64_t idx = w + u * nhw + (lane >> 4);
-      active[u] = idx < total;
-      // rows fastest: neighbouring half-warps write neighbouring entries of the transposed scales.
-      // 32-bit division when the group count allows it (a 64-bit one costs more than the rest of
-      // the group's arithmetic).
-      if (total <= 0x7fffffffLL) {
-        const unsigned gi = active[u] ? static_cast<unsigned>(idx) / static_cast<unsigned>(rows) : 0u;
-        g[u] = static_cast<int>(gi);
-        row[u] = active[u] ? static_cast<int64_t>(static_cast<unsigned>(idx) - gi * static_cast<unsigned>(rows)) : 0;
-      } else {
-        g[u] = active[u] ? static_cast<int>(idx / rows) : 0;
-        row[u] = active[u] ? idx - static_cast<int64_t>(g[u]) * rows : 0;
+      for (int u = 0; u < kInFlight; ++u) {
+        const int g = g0 + 2 * u + hw;
+        raw[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (g < groups) raw[u] = *reinterpret_cast<const uint4*>(xrow + g * 128);
       }
-      raw[u] = make_uint4(0u, 0u, 0u, 0u);
-      if (active[u]) raw[u] = *reinterpret_cast<const uint4*>(x + row[u] * cols + g[u] * 128 + sub * 8);
-    }
 #pragma unroll
-    for (int u = 0; u < kInFlight; ++u)
-      if (w + u * nhw < total)   // warp-uniform: the shuffles inside need the whole warp
-        quant_group16<T>(raw[u], q, scale_t, row[u], g[u], cols, scale_stride, active[u], sub);
+      for (int u = 0; u < kInFlight; ++u) {
+        const int g = g0 + 2 * u + hw;
+        if (g0 + 2 * u < groups)   // warp-uniform: the shuffles inside need the whole warp
+          quant_group16<T>(raw[u], qrow + g * 128, srow + static_cast<int64_t>(g) * scale_stride, g < groups, sub);
+      }
+    }
   }
 }
 

@@ -95,6 +95,7 @@ def test_quant_1x128_bit_exact():
     for dt in (torch.float16, torch.bfloat16, torch.float32):
         x = (torch.randn(77, 384, generator=gen) * 5).to(dt)
         x[3, :128] = 0
+        x[5, 10], x[6, 200], x[7, 300], x[8, 5], x[8, 6] = float("inf"), float("nan"), float("-inf"), 1e-38, -3e-39
         q, st = quant_1x128(x.to(DEV))
         wq, ws = O.quant_1x128(x.float())
         assert torch.equal(q.cpu().view(torch.uint8), wq.view(torch.uint8)), dt
