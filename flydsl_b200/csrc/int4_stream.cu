@@ -214,6 +214,12 @@ int4_stream_kernel(const __grid_constant__ CUtensorMap tmap_x, const Int4StreamP
     // rows 8 (mi & 1) .. +7 and the 16-byte K chunk (mi >> 1) of the K step
     const int lm_row = (lane & 7) + 8 * ((lane >> 3) & 1);
     const int lm_chunk = lane >> 4;
+    // byte offset of that row's chunk for K step a of a 64-K sub-tile (128-byte swizzle: chunk ^ row % 8;
+    // the m-block and sub-tile offsets are multiples of 1024 and do not change row % 8)
+    uint32_t lm_off[4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+      lm_off[a] = static_cast<uint32_t>(lm_row * 128 + (((2 * a + lm_chunk) ^ (lane & 7)) << 4));
     for (int i = 0; i < count && alive; ++i) {
       const int s = i % slots;
       const bool got = mbar_wait(full_bar(s), (i / slots) & 1, abort_flag, p.err, kErrWaitSmemFull);
@@ -249,9 +255,7 @@ int4_stream_kernel(const __grid_constant__ CUtensorMap tmap_x, const Int4StreamP
         uint32_t a[MB][4];
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb) {
-          const int row = mb * 16 + lm_row;
-          const int chunk = 2 * (ks & 3) + lm_chunk;
-          ldmatrix_x4(xs + (ks >> 2) * C::kXSub + row * 128 + ((chunk ^ (row & 7)) << 4), a[mb]);
+          ldmatrix_x4(xs + (ks >> 2) * C::kXSub + mb * 2048 + lm_off[ks & 3], a[mb]);
         }
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
