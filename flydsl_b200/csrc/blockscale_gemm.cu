@@ -8,13 +8,15 @@
 //               pre-swizzled weight tile into a multistage shared-memory ring
 //   warp 1      MMA issuer: tcgen05.mma kind::f8f6f4, 128 x BN x 32, four per 128-wide K block,
 //               each K block into a fresh TMEM accumulator buffer (512/BN buffers in rotation)
-//   warps 2-3   MoE only: gather activation rows by sorted id with cp.async into the same swizzled
-//               image TMA would have produced
+//   warps 2-3   one of: (dense) lane 0 of warp 2 turns every staged tile into TMA stores;
+//               (MoE, activations in routing order) both warps copy every staged tile to its output
+//               rows -- coalesced row stores or vector reductions to the scattered (token, slot) rows;
+//               (MoE, reference-shaped inputs) gather activation rows by sorted id with cp.async
+//               into the same swizzled image TMA would have produced
 //   warps 4-11  epilogue: tcgen05.ld the K-block partial (loads pipelined against the FMAs),
 //               acc = fma(partial, sa*sb, acc) in fp32 registers (the per-128-K scale promotion),
 //               release the TMEM buffer; after the last K block convert, stage the tile in shared
-//               memory and write it with TMA (dense) or with coalesced row stores / vector
-//               reductions to the scattered (token, slot) rows (MoE)
+//               memory and hand it to warps 2-3 (in the gather mode they store it themselves)
 //
 // The computation follows kernel_gemm / compute_tile_blockscale of the reference
 // (kernels/blockscale_preshuffle_gemm.py:161-839, :509-587) and the stage kernels of

@@ -25,14 +25,14 @@
 //     q*a summed in fp32 before scaling. (The template also builds with four n-blocks per warp and
 //     with the K steps of a group dealt out to two or four warps; neither was faster.)
 //
-// Where the time goes (ncu, M=16, N=K=8192): the schedulers issue on 51 % of the cycles, the integer
-// ALU pipe is the busiest at 43 %, the legacy tensor pipe 19 %, DRAM 20 %: the unpack instructions
+// Where the time goes (ncu, M=16, N=K=8192): the schedulers issue on 43 % of the cycles, the integer
+// ALU pipe is the busiest at 41 %, the legacy tensor pipe 22 %, DRAM 17 %: the unpack instructions
 // (three per two weights) bound the kernel at ~960 cycles per 8 KB group against ~330 for the SM's
 // share of HBM bandwidth.
 //
 // Packed layout (flyb200_int4_repack): wq [K/128][N/8][4][8][16 bytes] (see int4_gemm.cu); word j of
-// a row holds K elements
-// 8j..8j+7 as nibbles q+8 in the order e0 e2 e4 e6 e1 e3 e5 e7, so (word >> 4t) & 0x000F000F is the
+// a row holds K elements 8j..8j+7 as nibbles q+8 in the order e0 e2 e4 e6 e1 e3 e5 e7, so
+// (word >> 4t) & 0x000F000F is the
 // pair (e_2t, e_2t+1) in the two 16-bit halves: exactly the (k, k+1) pair that thread t of a quad
 // holds in the B fragment (words 2s and 2s+1 give the fragment's two registers for K step s).
 // (n | 0x4300) is the bf16 value 128 + n; minus 136 gives q exactly.
