@@ -42,6 +42,8 @@ SIGNATURES = {
     "flyb200_repack_weight_fp8": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "flyb200_blockscale_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
                                         c_int32, c_int32, c_int32, POINTER(GemmCfg), c_void_p]),
+    "flyb200_pertoken_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
+                                      c_int32, c_int32, c_int32, POINTER(GemmCfg), c_void_p]),
     "flyb200_moe_sort": (c_int, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p,
                                  c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "flyb200_moe_sort_permute": (c_int, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p,

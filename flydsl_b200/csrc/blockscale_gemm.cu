@@ -35,7 +35,12 @@ constexpr int kEpiWarps = 8;
 constexpr int kATileBytes = BM * BK;
 constexpr int kRegionBytes = BM * 128;  // one 64-column (16-bit) slab of the staged output tile
 
-enum Mode : int { kDense = 0, kMoe1 = 1, kMoe2 = 2 };
+// kDensePT: dense GEMM with one scale per token (row) and one per output channel (column) instead
+// of block scales: C[m,n] = (sum_k A[m,k] B[n,k]) * sa[m] * sb[n]. The whole K range accumulates in
+// one TMEM buffer (no per-128-K promotion), so the epilogue touches a tile once and the tensor pipe
+// runs from one tile into the next. Reference: kernels/preshuffle_gemm.py:206-1266 (in_dtype fp8).
+enum Mode : int { kDense = 0, kMoe1 = 1, kMoe2 = 2, kDensePT = 3 };
+__host__ __device__ constexpr bool is_dense(int mode) { return mode == kDense || mode == kDensePT; }
 
 struct GemmParams {
   const uint8_t* a;        // MoE: activation rows to gather from (dense uses the tensor map)
@@ -165,9 +170,9 @@ struct TileWalker {
   // x top-8, more than L2); instead consecutive CTAs take the column tiles of ONE row block (minor =
   // n): its activation tile is fetched once and shared through L2, and the second row block of an
   // expert follows its first closely enough to find the expert's weights (29 MB) still in L2.
-  static constexpr bool kRowBlockMajor = (MODE != kDense);
+  static constexpr bool kRowBlockMajor = (!is_dense(MODE));
   __device__ __forceinline__ TileWalker(const GemmParams& p) {
-    if constexpr (MODE == kDense) {
+    if constexpr (is_dense(MODE)) {
       num_m = (p.M + BM - 1) / BM;
       num_n = (p.N + BN - 1) / BN;
     } else {
@@ -241,7 +246,8 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto done_bar = [&](uint32_t i) { return bar_base + 8u * (kStages + i); };
   auto tempty_bar = [&](int b) { return bar_base + 8u * (kStages + kDone + b); };
-  constexpr int kNumBars = kStages + kDone + kAccBufs + 3;
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (kStages + kDone + kAccBufs + b); };   // kDensePT
+  constexpr int kNumBars = kStages + kDone + 2 * kAccBufs + 3;
   static_assert(8 * kNumBars + 8 <= 1024, "barrier area overflows the misc block");
   const uint32_t epi_bar = bar_base + 8u * (kNumBars - 3);
   const uint32_t cfull_bar = bar_base + 8u * (kNumBars - 2);
@@ -256,23 +262,24 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   };
 
   // arrivals per stage: the producer's expect_tx (+ the two gather warps when rows are gathered)
-  const bool gather_a = (MODE != kDense) && !p.a_sorted;
+  const bool gather_a = (!is_dense(MODE)) && !p.a_sorted;
   // MoE tiles that leave through the staging tile are written out by warps 2-3 while the epilogue
   // warps go on with the next tile -- when those warps are not gathering rows and the epilogue does
   // stays with the arithmetic.
-  const bool moe_async_store = (MODE != kDense) && C::kStaged && !gather_a;
+  const bool moe_async_store = (!is_dense(MODE)) && C::kStaged && !gather_a;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) mbar_init(full_bar(s), gather_a ? 3 : 1);
     for (int i = 0; i < kDone; ++i) mbar_init(done_bar(i), 1);
     for (int b = 0; b < kAccBufs; ++b) mbar_init(tempty_bar(b), kEpiWarps);  // one arrival per warp
+    for (int b = 0; b < kAccBufs; ++b) mbar_init(tfull_bar(b), 1);
     mbar_init(epi_bar, kEpiWarps);
     mbar_init(cfull_bar, kEpiWarps);
-    mbar_init(cfree_bar, MODE == kDense ? 1 : 2);
+    mbar_init(cfree_bar, is_dense(MODE) ? 1 : 2);
     *abort_flag = 0;
     fence_proxy_async_smem();
     fence_barrier_init();
-    if (MODE == kDense || p.a_sorted) prefetch_tensormap(&tmap_a);
-    if constexpr (MODE == kDense && C::kStaged) prefetch_tensormap(&tmap_c);
+    if (is_dense(MODE) || p.a_sorted) prefetch_tensormap(&tmap_a);
+    if constexpr (is_dense(MODE) && C::kStaged) prefetch_tensormap(&tmap_c);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
@@ -313,7 +320,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         size_t row_stride_kb;  // bytes between consecutive K blocks of the repacked weight
         int n0;
         bool w_last_use = false;
-        if constexpr (MODE == kDense) {
+        if constexpr (is_dense(MODE)) {
           n0 = n_tile * BN;
           rows_b = min(BN, p.N - n0);
           row_stride_kb = static_cast<size_t>(p.N) * BK;
@@ -345,7 +352,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint32_t sa = smem_base + s * C::kStageBytes;
           const uint32_t sb = sa + kATileBytes;
           const uint8_t* src = wbase + kb * row_stride_kb + static_cast<size_t>(n0) * BK;
-          if constexpr (MODE == kDense) {
+          if constexpr (is_dense(MODE)) {
             mbar_arrive_expect_tx(full_bar(s), p.a_box_rows * BK + rows_b * BK);
             tma_load_2d(sa, &tmap_a, kb * BK, m_blk * BM, full_bar(s));
             bulk_load(sb, src, rows_b * BK, full_bar(s));
@@ -370,11 +377,42 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // the epilogue being the slower side.)
       constexpr uint32_t idesc = umma_idesc_e4m3_f32(BM, BN);
       uint32_t it = 0;
+      uint32_t tiles_issued = 0;   // kDensePT
       bool alive = true;
       for (TilePos pos = walk.start(); walk.valid(pos) && alive; walk.advance(pos)) {
-        if constexpr (MODE != kDense) {
+        if constexpr (!is_dense(MODE)) {
           const int e = p.expert_ids[pos.m_blk];
           if (e < 0 || e >= p.experts) continue;
+        }
+        if constexpr (MODE == kDensePT) {
+          // one accumulator buffer per TILE: wait for it once, accumulate every K block into it,
+          // then tell the epilogue; the per-K-block commits only hand the stages back
+          const int buf = static_cast<int>(tiles_issued % kAccBufs);
+          if (!mbar_wait(tempty_bar(buf), ((tiles_issued / kAccBufs) & 1) ^ 1, abort_flag, p.err,
+                         kErrWaitTmemEmpty)) {
+            alive = false;
+            break;
+          }
+          const uint32_t d = tmem_base + buf * BN;
+          for (int kb = 0; kb < KB; ++kb, ++it) {
+            const int s = it % kStages;
+            const uint32_t sa = smem_base + s * C::kStageBytes;
+            const uint64_t adesc = umma_desc_sw128(sa);
+            const uint64_t bdesc = umma_desc_sw128(sa + kATileBytes);
+            if (!mbar_wait(full_bar(s), (it / kStages) & 1, abort_flag, p.err, kErrWaitSmemFull)) {
+              alive = false;
+              break;
+            }
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < BK / 32; ++k)
+              tc_mma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+            tc_commit(done_bar(it % kDone));
+          }
+          if (!alive) break;
+          tc_commit(tfull_bar(buf));
+          ++tiles_issued;
+          continue;
         }
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % kStages;
@@ -400,7 +438,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           tc_commit(done_bar(it % kDone));
         }
       }
-    } else if (MODE == kDense && C::kStaged && warp == 2 && lane == 0) {
+    } else if (is_dense(MODE) && C::kStaged && warp == 2 && lane == 0) {
       // ---------------- dense: output store ----------------
       // One thread turns every staged tile into TMA stores, so the epilogue warps neither wait for
       // one another nor for the store engine at a tile boundary: they signal cfull and go on to the
@@ -419,7 +457,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         mbar_arrive(cfree_bar);
       }
       bulk_wait_group0();  // every store has been written before the CTA exits
-    } else if (MODE != kDense && C::kStaged && warp >= 2 && moe_async_store) {
+    } else if (!is_dense(MODE) && C::kStaged && warp >= 2 && moe_async_store) {
       // ---------------- MoE: output store (routing-order activations) ----------------
       // Warps 2-3 copy every staged tile to its output rows (row_off: element offset of each row,
       // -1 for rows without a token) while the epilogue warps run the next tile's K loop: cfull
@@ -490,7 +528,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (lane == 0) mbar_arrive(cfree_bar);
         }
       }
-    } else if (MODE != kDense && warp >= 2 && gather_a) {
+    } else if (!is_dense(MODE) && warp >= 2 && gather_a) {
       // ---------------- MoE: gather activation rows with cp.async ----------------
       // Thread g owns rows g and g+64 of the tile; row r, 16-byte chunk c lands at
       // r*128 + ((c ^ (r & 7)) << 4): the 128-byte-swizzled K-major image.
@@ -614,7 +652,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     auto setup_scales = [&](const TilePos& pos, ScaleCtx& c) -> bool {
       const int m_blk = pos.m_blk, n_tile = pos.n_tile;
       long long sa_idx, sb_idx0, sb_idx1;
-      if constexpr (MODE == kDense) {
+      if constexpr (is_dense(MODE)) {
         const int row = m_blk * BM + r;
         sa_idx = row < p.M ? row : 0;
         c.sa_step = p.M;
@@ -663,7 +701,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int m_blk = pos.m_blk, n_tile = pos.n_tile;
       c.m_blk = m_blk;
       c.route_w = 1.0f;
-      if constexpr (MODE == kDense) {
+      if constexpr (is_dense(MODE)) {
         const int row = m_blk * BM + r;
         c.row_ok = row < p.M;
         c.n0 = n_tile * BN;
@@ -700,7 +738,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     float ring_a[kRing], ring_b0[kRing], ring_b1[kRing];
     TilePos pos = walk.start();
     find_tile(pos, cur);
-    if (walk.valid(pos)) {
+    if (MODE != kDensePT && walk.valid(pos)) {
 #pragma unroll
       for (int j = 0; j < kRing; ++j) {
         const int kb = j < KB ? j : 0;
@@ -735,7 +773,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       ScaleCtx nxt;
       float nring_a[kRing], nring_b0[kRing], nring_b1[kRing];
       TilePos npos = pos;
-      for (int kb0 = 0; kb0 < KB && alive; kb0 += kRing) {
+      for (int kb0 = 0; MODE != kDensePT && kb0 < KB && alive; kb0 += kRing) {
         if (kb0 + kRing >= KB) {
           // last trip: the next tile's scale context and first scales are fetched now, so that their
           // latency is over when the store phase ends
@@ -785,7 +823,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // Loads of LDW columns are software-pipelined against the FMAs of the previous load (two
             // register buffers); the buffer goes back to the issuer as soon as the last load landed.
             uint32_t va[LDW], vb[LDW];
-            if (MODE != kDense && !cur.active) {
+            if (!is_dense(MODE) && !cur.active) {
               release();
             } else {
             tmem_ld<LDW>(taddr(0), va);
@@ -816,6 +854,50 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
         }
       }
+      if constexpr (MODE == kDensePT) {
+        // Per-token / per-channel scales: the tile's whole K range has been accumulated in TMEM
+        // buffer tiles_done % kAccBufs; read it once, scale by sa[row] * sb[column], hand it back.
+        walk.advance(npos);
+        const int buf = static_cast<int>(tiles_done % kAccBufs);
+        const bool got = mbar_wait(tfull_bar(buf), (tiles_done / kAccBufs) & 1, abort_flag, p.err,
+                                   kErrWaitTmemFull);
+        if (!__all_sync(0xffffffffu, got)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after();
+        const int row = pos.m_blk * BM + r;
+        const float sa = row < p.M ? __ldg(p.scale_a + row) : 0.f;
+        const int n0t = pos.n_tile * BN;
+        const uint32_t t0 = tmem_base + lane_base + buf * BN + half * CH;
+        auto taddr = [&](int q) { return t0 + (q >= NSUB ? BN / 2 : 0) + (q % NSUB) * LDW; };
+        uint32_t va[LDW], vb[LDW];
+        tmem_ld<LDW>(taddr(0), va);
+        tmem_wait_dep<LDW>(va);
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) {
+          uint32_t* cv = (q & 1) ? vb : va;
+          uint32_t* nv = (q & 1) ? va : vb;
+          if (q + 1 < NQ) tmem_ld<LDW>(taddr(q + 1), nv);
+          const int col = (q >= NSUB ? BN / 2 : 0) + half * CH + (q % NSUB) * LDW;  // tile-relative
+          float2* a = acc + (q >= NSUB ? CH / 2 : 0) + (q % NSUB) * (LDW / 2);
+          const bool in_n = n0t + col < p.N;   // N % 16 == 0: a load's columns are all in or all out
+#pragma unroll
+          for (int c = 0; c < LDW / 2; ++c) {
+            const float s0 = in_n ? sa * __ldg(p.scale_b + n0t + col + 2 * c) : 0.f;
+            const float s1 = in_n ? sa * __ldg(p.scale_b + n0t + col + 2 * c + 1) : 0.f;
+            a[c] = make_float2(__uint_as_float(cv[2 * c]) * s0, __uint_as_float(cv[2 * c + 1]) * s1);
+          }
+          if (q + 1 < NQ) {
+            tmem_wait_dep<LDW>(nv);
+            if (q + 2 == NQ) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(tempty_bar(buf));
+            }
+          }
+        }
+      }
       if (!alive) break;
 
       OutCtx oc;
@@ -832,7 +914,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         //     has read it (cfree; 16 K blocks have passed, so this wait is normally over at once).
         //     MoE: the previous tile's cooperative row stores are done (every thread passes this
         //     barrier after its own).
-        if constexpr (MODE == kDense) {
+        if constexpr (is_dense(MODE)) {
           if (tiles_done > 0) {
             const bool ok = mbar_wait(cfree_bar, (tiles_done - 1) & 1, abort_flag, p.err, kErrWaitEpilogue);
             if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
@@ -969,7 +1051,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
           }
         }
-        if constexpr (MODE == kDense) {
+        if constexpr (is_dense(MODE)) {
           // (3) hand the staged tile to the store warp and go on with the next tile
           fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA store
           __syncwarp();
@@ -1052,12 +1134,14 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
 
       // rotate to the prefetched tile
-      cur = nxt;
+      if constexpr (MODE != kDensePT) {
+        cur = nxt;
 #pragma unroll
-      for (int j = 0; j < kRing; ++j) {
-        ring_a[j] = nring_a[j];
-        ring_b0[j] = nring_b0[j];
-        ring_b1[j] = nring_b1[j];
+        for (int j = 0; j < kRing; ++j) {
+          ring_a[j] = nring_a[j];
+          ring_b0[j] = nring_b0[j];
+          ring_b1[j] = nring_b1[j];
+        }
       }
       pos = npos;
     }
@@ -1264,6 +1348,48 @@ extern "C" int flyb200_blockscale_gemm(void* c, const void* a, const void* b_rep
   if (out_dtype == FLYB200_BF16)
     return launch_bn<kDense, __nv_bfloat16>(bn, tmap_a, tmap_c, p, grid, st);
   return launch_bn<kDense, __half>(bn, tmap_a, tmap_c, p, grid, st);
+}
+
+extern "C" int flyb200_pertoken_gemm(void* c, const void* a, const void* b_repacked, const float* scale_a,
+                                     const float* scale_b, int32_t M, int32_t N, int32_t K,
+                                     int32_t out_dtype, const flyb200_gemm_cfg* cfg, void* stream) {
+  int rc;
+  if ((rc = check_ptr(c, 16, "c")) || (rc = check_ptr(a, 16, "a")) ||
+      (rc = check_ptr(b_repacked, 16, "b_repacked")) || (rc = check_ptr(scale_a, 4, "scale_a")) ||
+      (rc = check_ptr(scale_b, 4, "scale_b")))
+    return rc;
+  if (M < 1 || N < 16 || K < 128)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "bad shape M=%d N=%d K=%d", M, N, K);
+  if (N % 16) return set_error(FLYB200_ERR_INVALID_ARGUMENT, "N (%d) must be a multiple of 16", N);
+  if (K % 128) return set_error(FLYB200_ERR_INVALID_ARGUMENT, "K (%d) must be a multiple of 128", K);
+  if (out_dtype != FLYB200_BF16 && out_dtype != FLYB200_F16)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "out_dtype must be BF16 or F16");
+  if (cfg && cfg->block_n && cfg->block_n != 256)
+    return set_error(FLYB200_ERR_UNSUPPORTED, "the per-token-scale GEMM is built with 256-wide tiles only");
+  const int sms = sm_count();
+  if (sms <= 0) return FLYB200_ERR_CUDA;
+  const int m_blocks = cdiv(M, BM);
+  int grid = sms;
+  if (cfg && cfg->max_ctas > 0 && cfg->max_ctas < grid) grid = cfg->max_ctas;
+  const long tiles = static_cast<long>(m_blocks) * cdiv(N, 256);
+  if (tiles < grid) grid = static_cast<int>(tiles);
+
+  GemmParams p{};
+  p.a = reinterpret_cast<const uint8_t*>(a);
+  p.b = reinterpret_cast<const uint8_t*>(b_repacked);
+  p.scale_a = scale_a;   // [M]
+  p.scale_b = scale_b;   // [N]
+  p.out = c;
+  p.err = device_error_word();
+  if (!p.err) return FLYB200_ERR_CUDA;
+  p.M = M; p.N = N; p.K = K;
+  p.a_box_rows = M >= BM ? BM : ((M + 7) / 8) * 8;
+  CUtensorMap tmap_a, tmap_c;
+  if ((rc = make_tensor_map_2d(&tmap_a, a, M, K, 1, p.a_box_rows))) return rc;
+  if ((rc = make_tensor_map_2d(&tmap_c, c, M, N, 2, p.a_box_rows))) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (out_dtype == FLYB200_BF16) return launch<256, kDensePT, __nv_bfloat16>(tmap_a, tmap_c, p, grid, st);
+  return launch<256, kDensePT, __half>(tmap_a, tmap_c, p, grid, st);
 }
 
 static int moe_common_checks(const void* out, const void* x, const void* w, const float* scale_x,

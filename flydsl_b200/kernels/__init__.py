@@ -1,5 +1,6 @@
 """Factory functions with the reference's names (FlyDSL ``kernels/`` directory)."""
 from .blockscale_preshuffle_gemm import compile_blockscale_preshuffle_gemm  # noqa: F401
+from .preshuffle_gemm import compile_preshuffle_gemm_a8  # noqa: F401
 from .moe_blockscale_2stage import (  # noqa: F401
     MoeGemm2Mode,
     compile_moe_blockscale_gemm1,

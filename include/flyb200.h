@@ -73,6 +73,17 @@ int flyb200_blockscale_gemm(void* c, const void* a, const void* b_repacked, cons
                             const float* scale_b, int32_t M, int32_t N, int32_t K,
                             int32_t out_dtype, const flyb200_gemm_cfg* cfg, void* stream);
 
+/* Dense FP8 GEMM with one scale per token and one per output channel:
+ * c[m,n] = (sum_k a[m,k] * b[n,k]) * scale_a[m] * scale_b[n], the whole K range accumulated in fp32
+ * before scaling. Replaces the launcher returned by compile_preshuffle_gemm_a8 with in_dtype "fp8"
+ * (kernels/preshuffle_gemm.py:39-52, launch_gemm :1269-1303, kernel_gemm :206-1266); the contract is
+ * run_torch of tests/kernels/test_preshuffle_gemm.py:55-66. c [M,N] out_dtype (BF16|F16); a [M,K];
+ * b_repacked [N,K] from flyb200_repack_weight_fp8; scale_a [M]; scale_b [N]. Any M >= 1;
+ * N % 16 == 0; K % 128 == 0. cfg: max_ctas only. */
+int flyb200_pertoken_gemm(void* c, const void* a, const void* b_repacked, const float* scale_a,
+                          const float* scale_b, int32_t M, int32_t N, int32_t K, int32_t out_dtype,
+                          const flyb200_gemm_cfg* cfg, void* stream);
+
 /* MoE routing sort. Bit-exact stand-in for moe_sorting_torch_native
  * (tests/kernels/test_moe_gemm.py:97-161) and the sorter half of build_routing_buffers (:223-295).
  * topk_ids i32 [T,k]; topk_weights f32 [T,k]; expert_mask i32 [E] or NULL; num_local_tokens: < 0

@@ -25,6 +25,7 @@ _WANTED = {
     "tests/kernels/test_moe_blockscale.py": ["_expand_blockscale", "torch_stage1_blockscale_ref",
                                              "torch_stage2_blockscale_ref", "torch_moe_blockscale_ref"],
     "tests/kernels/test_moe_gemm.py": ["moe_sorting_torch_native"],
+    "tests/kernels/test_preshuffle_gemm.py": ["run_torch"],
     "tests/utils.py": ["get_dtype_max", "pertoken_quant", "shuffle_weight"],
 }
 

@@ -64,6 +64,22 @@ def dense_cases(ref):
     return out
 
 
+def pertoken_cases(ref):
+    """Per-token / per-channel scaled GEMM: the reference test's recipe (rand operands quantised by
+    pertoken_quant, tests/kernels/test_preshuffle_gemm.py:141-180) and its run_torch."""
+    out = {}
+    for tag, (M, N, K) in {"a": (33, 320, 256), "b": (5, 128, 384)}.items():
+        g = torch.Generator().manual_seed(200 + len(out))
+        a = torch.rand(M, K, generator=g)
+        b = torch.rand(N, K, generator=g)
+        aq, sa = ref["pertoken_quant"](a, quant_dtype=FP8)
+        bq, sb = ref["pertoken_quant"](b, quant_dtype=FP8)
+        c32 = ref["run_torch"](aq, bq, sa, sb, bias=None, dtype=torch.float32)
+        out.update({f"{tag}_a": u8(aq), f"{tag}_b": u8(bq), f"{tag}_sa": sa.reshape(-1).numpy(),
+                    f"{tag}_sb": sb.reshape(-1).numpy(), f"{tag}_c_f32": c32.numpy()})
+    return out
+
+
 def sort_cases(ref):
     out = {}
     cases = {
@@ -151,7 +167,8 @@ def main():
     np.savez_compressed(os.path.join(HERE, "sort.npz"), **sort_cases(ref))
     np.savez_compressed(os.path.join(HERE, "moe.npz"), **moe_case(ref))
     np.savez_compressed(os.path.join(HERE, "quant.npz"), **quant_case(ref))
-    for f in ("dense.npz", "sort.npz", "moe.npz", "quant.npz"):
+    np.savez_compressed(os.path.join(HERE, "pertoken.npz"), **pertoken_cases(ref))
+    for f in ("dense.npz", "sort.npz", "moe.npz", "quant.npz", "pertoken.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
 
 

@@ -23,6 +23,14 @@ def test_dense_oracle_matches_golden(tag):
         assert torch.equal(out32, torch.from_numpy(g[f"{tag}_c_f32"]))
 
 
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_pertoken_oracle_matches_golden(tag):
+    g = load_golden("pertoken.npz")
+    a, b = fp8_from_u8(g[f"{tag}_a"]), fp8_from_u8(g[f"{tag}_b"])
+    c = O.run_torch_pertoken(a, b, torch.from_numpy(g[f"{tag}_sa"]), torch.from_numpy(g[f"{tag}_sb"]))
+    assert torch.equal(c, torch.from_numpy(g[f"{tag}_c_f32"]))
+
+
 def test_quantisers_match_golden():
     g = load_golden("quant.npz")
     q, s = O.pertoken_quant(torch.from_numpy(g["x"]))
