@@ -410,6 +410,55 @@ def int4_sweep(dev, peaks, quick=False):
     return rows
 
 
+def pertoken_sweep(dev, peaks, quick=False):
+    """Per-token / per-channel scaled FP8 GEMM (the reference's kernels/preshuffle_gemm.py, fp8): the
+    headline shape and the reference test's large shapes; steps back to back over operand sets larger
+    than twice the L2; TFLOP/s against twice the measured bf16 rate. A few entries of every result are
+    compared with the fp32 product of the dequantised operands."""
+    from flydsl_b200.kernels import compile_preshuffle_gemm_a8
+    from flydsl_b200.utils import shuffle_weight
+
+    rows = []
+    shapes = [(4096, 7168, 2048)] if quick else [(4096, 7168, 2048), (5120, 5120, 8320), (9728, 8192, 8320)]
+    g = torch.Generator(device=dev).manual_seed(6)
+    for (M, N, K) in shapes:
+        per_set = M * K + N * K + 2 * M * N
+        nset = max(2, int(2.2 * 126e6 / per_set) + 1)
+        sets = []
+        for _ in range(nset):
+            a = torch.randn(M, K, generator=g, device=dev).to(torch.float8_e4m3fn)
+            b = (torch.randn(N, K, generator=g, device=dev) * 0.5).to(torch.float8_e4m3fn)
+            sets.append((a, shuffle_weight(b), torch.rand(M, generator=g, device=dev) + 0.5,
+                         torch.rand(N, generator=g, device=dev) + 0.5,
+                         torch.empty(M, N, dtype=torch.bfloat16, device=dev), b))
+        fn = compile_preshuffle_gemm_a8(M=M, N=N, K=K, tile_m=64, tile_n=256, tile_k=128, out_dtype="bf16")
+        for a, b, sa, sb, c, _ in sets:
+            fn(c, a, b, sa, sb, M, N, None)
+        torch.cuda.synchronize()
+        # check: 64 rows x 64 columns of the first set against fp32 torch on the GPU
+        a, _, sa, sb, c, b_raw = sets[0]
+        ri = torch.linspace(0, M - 1, 64, device=dev).long()
+        ci = torch.linspace(0, N - 1, 64, device=dev).long()
+        want = (a[ri].float() * sa[ri, None]) @ (b_raw[ci].float() * sb[ci, None]).t()
+        got = c[ri][:, ci].float()
+        rel = ((got - want).abs().max() / want.abs().max()).item()
+        reps = 30
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            a, b, sa, sb, c, _ = sets[i % nset]
+            fn(c, a, b, sa, sb, M, N, None)
+        e1.record()
+        e1.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        tf = 2.0 * M * N * K / us / 1e6
+        rows.append({"M": M, "N": N, "K": K, "us": round(us, 2), "tflops": round(tf, 1),
+                     "frac_fp8_peak": round(tf / (2 * peaks["bf16_tflops"]), 4), "copies": nset,
+                     "check": {"max_rel": rel, "ok": bool(rel <= MAX_REL), "against": "fp32 torch on the GPU, 64 x 64 samples"}})
+        del sets
+    return rows
+
+
 def gen_expert(e, H, I, dev, seed):
     """Weights of global expert `e` (N(0,0.02), 128x128 block-quantised), generated on the GPU from a
     seed derived from the expert id, so that any rank can regenerate any expert: (w1_q [2I,H],
@@ -746,13 +795,15 @@ def run_ours(args):
         if world == 1:
             out["sweep"] = dense_sweep(dev, peaks, quick=args.quick)
             out["int4"] = int4_sweep(dev, peaks, quick=args.quick)
+            out["pertoken"] = pertoken_sweep(dev, peaks, quick=args.quick)
         out["moe"] = moe_layer_bench(rank, world, dev, peaks, quick=args.quick)
     if world > 1:
         import torch.distributed as dist
 
         dist.barrier()
         dist.destroy_process_group()
-    ok = out["check"]["ok"] and all(m.get("check", {}).get("ok", True) for m in (out.get("moe") or []))
+    ok = out["check"]["ok"] and all(m.get("check", {}).get("ok", True)
+                                    for m in (out.get("moe") or []) + (out.get("pertoken") or []))
     if rank == 0:
         print(json.dumps(out))
     if not ok:
@@ -815,6 +866,23 @@ def run_probe(args):
             if i >= args.warmup:
                 times.append(e0.elapsed_time(e1))
         print(json.dumps({"probe": "int4", "M": M, "N": N, "K": K, "us": statistics.median(times) * 1e3}))
+    elif args.probe == "pertoken":
+        from flydsl_b200.kernels import compile_preshuffle_gemm_a8
+
+        M, N, K = 4096, 7168, 2048
+        g = torch.Generator(device=dev).manual_seed(0)
+        sets = []
+        for _ in range(4):
+            a = torch.randn(M, K, generator=g, device=dev).to(torch.float8_e4m3fn)
+            b = shuffle_weight((torch.randn(N, K, generator=g, device=dev) * 0.5).to(torch.float8_e4m3fn))
+            sets.append((a, b, torch.rand(M, device=dev), torch.rand(N, device=dev),
+                         torch.empty(M, N, dtype=torch.bfloat16, device=dev)))
+        fn = compile_preshuffle_gemm_a8(M=M, N=N, K=K, tile_m=64, tile_n=256, tile_k=128, out_dtype="bf16")
+        for i in range(args.warmup + args.steps):
+            a, b, sa, sb, c = sets[i % 4]
+            fn(c, a, b, sa, sb, M, N, None)
+        torch.cuda.synchronize()
+        print(json.dumps({"probe": "pertoken", "M": M, "N": N, "K": K, "launches": args.warmup + args.steps}))
     else:
         M, N, K = 32, 7168, 2048
         copies = 18
@@ -835,7 +903,7 @@ def run_probe(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--probe", default=None, choices=["moe", "decode", "int4"], help="small profiling run (see run_probe)")
+    ap.add_argument("--probe", default=None, choices=["moe", "decode", "int4", "pertoken"], help="small profiling run (see run_probe)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
