@@ -19,8 +19,9 @@ from its own weight shard, no collective (strong scaling). Rank 0 prints ONE JSO
              2 x the measured cuBLAS bf16 rate in MEASURED_PEAKS.json
   cpu_baseline  the CPU oracle (torch dequantise-then-matmul, oracle/blockscale_ref.py) timed on the
              host cores on the same workload
-  sweep/moe  extra measurements (dense M-sweep of the three (N,K) pairs; the 256-expert top-8 MoE
-             layer) so the whole scope is measured in one run; skipped with --no-extras
+  sweep/moe/int4/pertoken  extra measurements (dense M-sweep of the three (N,K) pairs; the
+             256-expert top-8 MoE layer; the int4 weight-only decode GEMM; the per-token-scale
+             FP8 GEMM) so the whole scope is measured in one run; skipped with --no-extras
 
   check      outside every timed region the result of the headline GEMM (each rank: its column shard)
              and a handful of MoE tokens are compared with the CPU oracle on the same seeded inputs;
