@@ -82,7 +82,12 @@ struct Cfg {
   // 16-bit outputs of tiles at least 64 wide go through a shared-memory staging tile.
   static constexpr bool kStaged = (sizeof(OutT) == 2) && (kOutCols >= 32) && (BN >= 64);
   static constexpr int kRegions = (kOutCols + 63) / 64;
-  static constexpr int kCBytes = kStaged ? kRegions * kRegionBytes : 0;
+  // The per-token mode is bound by its operand feed, and its epilogue has a whole tile's K loop to
+  // get the previous tile out: it stages and stores a tile in two halves of 128 columns, which leaves
+  // shared memory for a fourth pipeline stage.
+  static constexpr bool kHalfStaging = (MODE == kDensePT) && (BN == 256);
+  static constexpr int kStageRegions = kHalfStaging ? kRegions / 2 : kRegions;
+  static constexpr int kCBytes = kStaged ? kStageRegions * kRegionBytes : 0;
   static constexpr int kBTileBytes = BN * BK;
   static constexpr int kStageBytes = kATileBytes + kBTileBytes;
   static constexpr int kMiscBytes = 2048;  // row offsets (1 KB) + barriers + flags
@@ -444,17 +449,25 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // one another nor for the store engine at a tile boundary: they signal cfull and go on to the
       // next tile's first K block; cfree tells them when the staging tile may be overwritten.
       uint32_t n = 0;
-      for (TilePos pos = walk.start(); walk.valid(pos); walk.advance(pos), ++n) {
+      bool ok = true;
+      for (TilePos pos = walk.start(); walk.valid(pos) && ok; walk.advance(pos)) {
         const int m_blk = pos.m_blk;
-        if (!mbar_wait(cfull_bar, n & 1, abort_flag, p.err, kErrWaitEpilogue)) break;
-        const int n0 = pos.n_tile * BN;
+        constexpr int kPasses = C::kRegions / C::kStageRegions;   // 2 with half-tile staging
 #pragma unroll
-        for (int reg = 0; reg < C::kRegions; ++reg)
-          if (n0 + reg * 64 < p.N)
-            tma_store_2d(&tmap_c, cstage_base + reg * kRegionBytes, n0 + reg * 64, m_blk * BM);
-        bulk_commit_group();
-        bulk_wait_group_read0();
-        mbar_arrive(cfree_bar);
+        for (int h = 0; h < kPasses; ++h, ++n) {
+          if (!mbar_wait(cfull_bar, n & 1, abort_flag, p.err, kErrWaitEpilogue)) {
+            ok = false;
+            break;
+          }
+          const int n0 = pos.n_tile * BN + h * C::kStageRegions * 64;
+#pragma unroll
+          for (int reg = 0; reg < C::kStageRegions; ++reg)
+            if (n0 + reg * 64 < p.N)
+              tma_store_2d(&tmap_c, cstage_base + reg * kRegionBytes, n0 + reg * 64, m_blk * BM);
+          bulk_commit_group();
+          bulk_wait_group_read0();
+          mbar_arrive(cfree_bar);
+        }
       }
       bulk_wait_group0();  // every store has been written before the CTA exits
     } else if (!is_dense(MODE) && C::kStaged && warp >= 2 && moe_async_store) {
@@ -756,7 +769,8 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     constexpr int LDW = (CH > 32) ? 16 : CH;
     constexpr int NSUB = CH / LDW;            // loads per column group
     constexpr int NQ = 2 * NSUB;              // loads per K block (two column groups)
-    uint32_t tiles_done = 0;                  // dense: tiles this CTA has staged so far
+    uint32_t tiles_done = 0;                  // dense: tiles (per-token mode: half tiles) staged so far
+    uint32_t pt_tiles = 0;                    // per-token mode: tiles drained so far
     uint32_t dn_i = 0, dn_ph = 0;             // it % kDone and (it / kDone) & 1, kept as counters
 
     while (walk.valid(pos) && alive) {
@@ -856,11 +870,12 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       if constexpr (MODE == kDensePT) {
         // Per-token / per-channel scales: the tile's whole K range has been accumulated in TMEM
-        // buffer tiles_done % kAccBufs; read it once, scale by sa[row] * sb[column], hand it back.
+        // buffer pt_tiles % kAccBufs; read it once, scale by sa[row] * sb[column], hand it back.
         walk.advance(npos);
-        const int buf = static_cast<int>(tiles_done % kAccBufs);
-        const bool got = mbar_wait(tfull_bar(buf), (tiles_done / kAccBufs) & 1, abort_flag, p.err,
+        const int buf = static_cast<int>(pt_tiles % kAccBufs);
+        const bool got = mbar_wait(tfull_bar(buf), (pt_tiles / kAccBufs) & 1, abort_flag, p.err,
                                    kErrWaitTmemFull);
+        ++pt_tiles;
         if (!__all_sync(0xffffffffu, got)) {
           alive = false;
           break;
@@ -1039,6 +1054,28 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             for (int q = 0; q < 8; ++q) y[q] = silu_mul(accf[j + q], accf[CH + j + q]) * route_w;
             stage8(col0 + j, y);
           }
+        } else if constexpr (C::kHalfStaging) {
+          // column group 0 (tile columns [0, 128)) and group 1 ([128, 256)) go through the same two
+          // staging regions one after the other; each is handed to the store thread on its own
+#pragma unroll
+          for (int grp = 0; grp < 2; ++grp) {
+            if (grp == 1) {
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(cfull_bar);
+              ++tiles_done;
+              const bool ok = mbar_wait(cfree_bar, (tiles_done - 1) & 1, abort_flag, p.err, kErrWaitEpilogue);
+              if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+            }
+#pragma unroll
+            for (int j = 0; j < CH; j += 8) {
+              float y[8];
+#pragma unroll
+              for (int q = 0; q < 8; ++q) y[q] = accf[grp * CH + j + q];
+              stage8(col0 + j, y);   // col0 = this thread's columns inside a 128-column half
+            }
+          }
+          if (!alive) break;
         } else {
 #pragma unroll
           for (int grp = 0; grp < 2; ++grp) {
