@@ -514,6 +514,105 @@ def moe_check(x_q, x_s, ids, tw, out, H, I, topk, dev, seed=0, n_tokens=4):
             "experts_regenerated": int(used.numel()), "against": "CPU oracle (two-stage, fp16 intermediate)"}
 
 
+def moe_pertoken_stages(w1, w2, H, I, E, topk, dev, peaks, T=4096, tile_m=128):
+    """The two stages of the per-token-scale MoE sibling (compile_moe_gemm1 / compile_moe_gemm2_ex in
+    reduce mode) on the block-scale layer's fp8 expert weights with seeded per-channel scales; the
+    per-route re-quantisation between the stages is the reference test's host-side pertoken_quant
+    and stays outside the timed regions. A few tokens are checked against the CPU oracle."""
+    from flydsl_b200.kernels import MoeGemm2Mode, compile_moe_gemm1, compile_moe_gemm2_ex
+    from flydsl_b200.utils import moe_sorting, pertoken_quant
+
+    g = torch.Generator(device=dev).manual_seed(T + 7)
+    x_q, x_s = pertoken_quant(torch.randn(T, H, generator=g, device=dev))
+    w1_cs = (0.5 + torch.rand(E * 2 * I, generator=g, device=dev)) * 1e-3
+    w2_cs = (0.5 + torch.rand(E * H, generator=g, device=dev)) * 1e-3
+    vals, ids = torch.topk(torch.softmax(torch.randn(T, E, generator=g, device=dev), dim=1), k=topk, dim=1)
+    tw = (vals / vals.sum(dim=1, keepdim=True)).float()
+    ids = ids.to(torch.int32)
+    sid, sw, seid, npp = moe_sorting(ids, tw, num_experts=E, block_size=tile_m)
+    blocks = seid.numel()
+    # routing-order copies of the activations (one row per sorted position), made once outside the
+    # timed regions: the stage kernels then fetch their rows by TMA and write in the same order
+    rows = T * topk + E * tile_m - topk
+    pos_tok = (sid[:rows] & 0xFFFFFF).long()
+    pos_slot = (sid[:rows] >> 24).long()
+    valid = pos_tok < T
+    x_sorted = torch.zeros(rows, H, dtype=torch.uint8, device=dev)
+    x_sorted[valid] = x_q.view(torch.uint8)[pos_tok[valid]]
+    x_sorted = x_sorted.view(torch.float8_e4m3fn)
+    xs_sorted = torch.ones(rows, dtype=torch.float32, device=dev)
+    xs_sorted[valid] = x_s.reshape(-1)[pos_tok[valid]]
+    common = dict(model_dim=H, inter_dim=I, experts=E, topk=topk, tile_m=tile_m, tile_n=256, tile_k=128)
+    g1 = compile_moe_gemm1(doweight_stage1=False, in_dtype="fp8", out_dtype="f16", a_sorted=True, out_sorted=True,
+                           **common)
+    g2 = compile_moe_gemm2_ex(doweight_stage2=True, in_dtype="fp8", out_dtype="bf16", mode=MoeGemm2Mode.REDUCE,
+                              a_sorted=True, **common)
+    out1_sorted = torch.zeros(rows, I, dtype=torch.float16, device=dev)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+
+    def stage1():
+        g1(out1_sorted, x_sorted, w1, xs_sorted, w1_cs, sid, seid, sw, npp, T, I, H, blocks)
+
+    stage1()
+    a2_sorted, a2s_sorted = pertoken_quant(out1_sorted.float())
+
+    def stage2():
+        g2(out, a2_sorted, w2, a2s_sorted, w2_cs, sid, seid, sw, npp, T, H, I, blocks)
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        ts = []
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+    ms1, ms2 = timed(stage1), timed(stage2)
+    # back to [T, topk, ...] for the checker
+    out1 = torch.zeros(T, topk, I, dtype=torch.float16, device=dev)
+    out1[pos_tok[valid], pos_slot[valid]] = out1_sorted[valid]
+    a2_q = torch.zeros(T, topk, I, dtype=torch.uint8, device=dev)
+    a2_q[pos_tok[valid], pos_slot[valid]] = a2_sorted.view(torch.uint8)[valid]
+    a2_q = a2_q.view(torch.float8_e4m3fn)
+    a2_s = torch.ones(T, topk, 1, dtype=torch.float32, device=dev)
+    a2_s[pos_tok[valid], pos_slot[valid]] = a2s_sorted.reshape(rows, 1)[valid]
+
+    from oracle import blockscale_ref as O  # checker only
+    sel = torch.linspace(0, T - 1, steps=3).long()
+    ids_sel = ids[sel.to(dev)].cpu().long()
+    used = torch.unique(ids_sel)
+    remap = {int(e): i for i, e in enumerate(used.tolist())}
+    local = torch.tensor([[remap[int(e)] for e in row] for row in ids_sel.tolist()], dtype=torch.int64)
+    q1s, q2s = [], []
+    for e in used.tolist():
+        q1, _, q2, _ = gen_expert(int(e), H, I, dev, 0)
+        q1s.append(q1.cpu()); q2s.append(q2.cpu())
+    s1 = torch.stack([w1_cs.view(E, 2 * I)[int(e)].cpu() for e in used.tolist()])
+    s2 = torch.stack([w2_cs.view(E, H)[int(e)].cpu() for e in used.tolist()])
+    tw_sel = tw[sel.to(dev)].cpu()
+    ref1 = O.torch_moe_gemm1_pertoken_ref(x_q[sel.to(dev)].cpu(), torch.stack(q1s), x_s[sel.to(dev)].cpu(), s1, local,
+                                          tw_sel, I)
+    mr1, cs1 = parity(out1[sel.to(dev)], ref1)
+    ref2 = O.torch_moe_gemm2_pertoken_ref(a2_q[sel.to(dev)].cpu(), torch.stack(q2s), a2_s[sel.to(dev)].cpu(), s2,
+                                          local, tw_sel, H)
+    mr2, cs2 = parity(out[sel.to(dev)], ref2)
+    ok = bool(max(mr1, mr2) <= MAX_REL and min(cs1, cs2) >= MIN_COS)
+    fl1, fl2 = 2.0 * T * topk * 2 * I * H, 2.0 * T * topk * I * H
+    return {"tokens": T, "tile_m": tile_m, "scales": "per token / per output channel",
+            "layout": "routing-order activations (a_sorted / out_sorted extensions)",
+            "stage1_ms": round(ms1, 4), "stage2_reduce_ms": round(ms2, 4),
+            "stage1_tflops": round(fl1 / (ms1 * 1e-3) / 1e12, 1), "stage2_tflops": round(fl2 / (ms2 * 1e-3) / 1e12, 1),
+            "stage1_weight_gbs": round(E * 2 * I * H / (ms1 * 1e-3) / 1e9, 1),
+            "stage2_weight_gbs": round(E * I * H / (ms2 * 1e-3) / 1e9, 1),
+            "check": {"max_rel": max(mr1, mr2), "cosine": min(cs1, cs2), "ok": ok, "tokens": sel.tolist(),
+                      "against": "CPU oracle, both stages on the tensors the GPU chain produced"}}
+
+
 def moe_layer_bench(rank, world, dev, peaks, quick=False):
     """The 256-expert top-8 two-stage MoE layer (H=7168, I=2048). One GPU holds all experts; with
     several GPUs see flydsl_b200.parallel (expert-parallel) -- measured there when available."""
@@ -563,6 +662,9 @@ def moe_layer_bench(rank, world, dev, peaks, quick=False):
                     "tflops": round((2.0 * T * topk * 3 * I * H) / (ms * 1e-3) / 1e12, 1),
                     "launches_per_step": layer_t.launches_per_step, "check": chk,
                     "l2": "weights of the active experts (>= 3 GB) exceed L2"})
+    if not quick:
+        res.append({"kind": "per-token-scale sibling, stages timed separately",
+                    **moe_pertoken_stages(w1, w2, H, I, E, topk, dev, peaks)})
     return res
 
 

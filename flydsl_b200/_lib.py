@@ -53,6 +53,10 @@ SIGNATURES = {
     "flyb200_moe_gemm1": (c_int, [c_void_p] * 9 + [c_int32] * 9 + [POINTER(GemmCfg), c_void_p]),
     "flyb200_moe_gemm1_q8": (c_int, [c_void_p] * 10 + [c_int32] * 9 + [POINTER(GemmCfg), c_void_p]),
     "flyb200_moe_gemm2": (c_int, [c_void_p] * 9 + [c_int32] * 10 + [POINTER(GemmCfg), c_void_p]),
+    "flyb200_moe_gemm1_pertoken": (c_int, [c_void_p] * 9 + [c_int32] * 9 + [POINTER(GemmCfg), c_void_p]),
+    "flyb200_moe_gemm2_pertoken": (c_int, [c_void_p] * 9 + [c_int32] * 10 + [POINTER(GemmCfg), c_void_p]),
+    "flyb200_moe_gemm2_reduce_pertoken": (c_int, [c_void_p] * 10 + [c_int32] * 9 + [POINTER(GemmCfg), c_void_p,
+                                                  c_size_t, c_int32, c_void_p]),
     "flyb200_moe_gemm2_reduce": (c_int, [c_void_p] * 10 + [c_int32] * 9 + [POINTER(GemmCfg), c_void_p, c_size_t,
                                          c_void_p]),
     "flyb200_moe_gemm2_reduce_noalloc": (c_int, [c_void_p] * 10 + [c_int32] * 9 + [POINTER(GemmCfg), c_void_p]),

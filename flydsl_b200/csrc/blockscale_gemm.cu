@@ -39,8 +39,15 @@ constexpr int kRegionBytes = BM * 128;  // one 64-column (16-bit) slab of the st
 // of block scales: C[m,n] = (sum_k A[m,k] B[n,k]) * sa[m] * sb[n]. The whole K range accumulates in
 // one TMEM buffer (no per-128-K promotion), so the epilogue touches a tile once and the tensor pipe
 // runs from one tile into the next. Reference: kernels/preshuffle_gemm.py:206-1266 (in_dtype fp8).
-enum Mode : int { kDense = 0, kMoe1 = 1, kMoe2 = 2, kDensePT = 3 };
+// kMoe1PT / kMoe2PT: the two MoE stages with per-token activation scales ([rows]) and per-channel
+// weight scales ([experts * output channels]) -- the routing, gather and output code of kMoe1 / kMoe2
+// with the whole-K accumulation of kDensePT. Reference: kernels/moe_gemm_2stage.py:93-1264 (stage 1)
+// and :1267-2481 (stage 2), in_dtype fp8.
+enum Mode : int { kDense = 0, kMoe1 = 1, kMoe2 = 2, kDensePT = 3, kMoe1PT = 4, kMoe2PT = 5 };
 __host__ __device__ constexpr bool is_dense(int mode) { return mode == kDense || mode == kDensePT; }
+__host__ __device__ constexpr bool is_moe1(int mode) { return mode == kMoe1 || mode == kMoe1PT; }
+__host__ __device__ constexpr bool is_moe2(int mode) { return mode == kMoe2 || mode == kMoe2PT; }
+__host__ __device__ constexpr bool is_pt(int mode) { return mode >= kDensePT; }
 
 struct GemmParams {
   const uint8_t* a;        // MoE: activation rows to gather from (dense uses the tensor map)
@@ -78,7 +85,7 @@ struct GemmParams {
 
 template <int BN, int MODE, typename OutT>
 struct Cfg {
-  static constexpr int kOutCols = (MODE == kMoe1) ? BN / 2 : BN;   // output columns per tile
+  static constexpr int kOutCols = (is_moe1(MODE)) ? BN / 2 : BN;   // output columns per tile
   // 16-bit outputs of tiles at least 64 wide go through a shared-memory staging tile.
   static constexpr bool kStaged = (sizeof(OutT) == 2) && (kOutCols >= 32) && (BN >= 64);
   static constexpr int kRegions = (kOutCols + 63) / 64;
@@ -185,7 +192,7 @@ struct TileWalker {
       int nb = (valid_rows + p.tile_m - 1) / p.tile_m;
       num_m = nb < p.num_blocks ? nb : p.num_blocks;
       if (num_m < 0) num_m = 0;
-      constexpr int kColsPerTile = (MODE == kMoe1) ? BN / 2 : BN;
+      constexpr int kColsPerTile = (is_moe1(MODE)) ? BN / 2 : BN;
       num_n = (p.N + kColsPerTile - 1) / kColsPerTile;
     }
     total = num_m * num_n;
@@ -336,7 +343,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           // "evict first", which keeps L2 for the activations and for weights that a following row
           // block still needs.
           w_last_use = (m_blk + 1 >= walk.num_m) || (p.expert_ids[m_blk + 1] != e);
-          if constexpr (MODE == kMoe1) {
+          if constexpr (is_moe1(MODE)) {
             n0 = n_tile * (BN / 2);
             rows_b = min(BN / 2, p.N - n0);
             wbase += static_cast<size_t>(e) * 2 * p.N * p.K;
@@ -361,7 +368,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             mbar_arrive_expect_tx(full_bar(s), p.a_box_rows * BK + rows_b * BK);
             tma_load_2d(sa, &tmap_a, kb * BK, m_blk * BM, full_bar(s));
             bulk_load(sb, src, rows_b * BK, full_bar(s));
-          } else if constexpr (MODE == kMoe1) {
+          } else if constexpr (is_moe1(MODE)) {
             mbar_arrive_expect_tx(full_bar(s), 2 * rows_b * BK + (p.a_sorted ? p.a_box_rows * BK : 0));
             if (p.a_sorted) tma_load_2d(sa, &tmap_a, kb * BK, m_blk * p.tile_m, full_bar(s));
             load_w(sb, src, rows_b * BK, full_bar(s), w_last_use);
@@ -389,7 +396,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const int e = p.expert_ids[pos.m_blk];
           if (e < 0 || e >= p.experts) continue;
         }
-        if constexpr (MODE == kDensePT) {
+        if constexpr (is_pt(MODE)) {
           // one accumulator buffer per TILE: wait for it once, accumulate every K block into it,
           // then tell the epilogue; the per-K-block commits only hand the stages back
           const int buf = static_cast<int>(tiles_issued % kAccBufs);
@@ -529,7 +536,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                : "r"(addr)
                                : "memory");
                   OutT* dst = out + off + n0 + col;
-                  if (MODE == kMoe2 && p.accumulate)
+                  if (is_moe2(MODE) && p.accumulate)
                     red8_packed(dst, q);
                   else
                     *reinterpret_cast<uint4*>(dst) = q;
@@ -567,7 +574,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const int t = id & 0xFFFFFF;
             const int slot = static_cast<unsigned>(id) >> 24;
             if (t < p.M && slot < p.topk) {
-              const size_t row = (MODE == kMoe1) ? static_cast<size_t>(t)
+              const size_t row = (is_moe1(MODE)) ? static_cast<size_t>(t)
                                                  : static_cast<size_t>(t) * p.topk + slot;
               src_row[h] = p.a + row * row_bytes;
               src_ok[h] = 16;
@@ -639,6 +646,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const float* sb0;    // scale_b of column group 0; K block kb at sb0 + kb
       const float* sb1;    // ... group 1
       long long sa_step;
+      int c0, c1;          // per-token MoE modes: first output channel of group 0 / 1 (range check)
       bool active;         // MoE: some row of this warp's 32 holds a token (warp-uniform)
     };
     // What the store phase needs; recomputed after the loop instead of being kept live through it.
@@ -685,24 +693,38 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           sa_idx = static_cast<long long>(m_blk) * p.tile_m + (r < p.tile_m ? r : 0);
           c.sa_step = p.a_rows;
         }
-        if constexpr (MODE == kMoe1) {
+        if constexpr (is_moe1(MODE)) {
           if (!p.a_sorted) {
             sa_idx = t;
             c.sa_step = p.M;
           }
-          const long long nb_exp = (2 * p.N) / 128;  // scale rows per expert
-          const int cg = min(n_tile * (BN / 2) + half * CH, p.N - 1);
-          sb_idx0 = (e * nb_exp + cg / 128) * KB;
-          sb_idx1 = (e * nb_exp + (p.N + cg) / 128) * KB;
+          if constexpr (is_pt(MODE)) {
+            // one weight scale per output channel: gate channel c of expert e at e*2N + c, up at +N
+            c.c0 = c.c1 = n_tile * (BN / 2) + half * CH;
+            sb_idx0 = static_cast<long long>(e) * 2 * p.N + c.c0;
+            sb_idx1 = sb_idx0 + p.N;
+          } else {
+            const long long nb_exp = (2 * p.N) / 128;  // scale rows per expert
+            const int cg = min(n_tile * (BN / 2) + half * CH, p.N - 1);
+            sb_idx0 = (e * nb_exp + cg / 128) * KB;
+            sb_idx1 = (e * nb_exp + (p.N + cg) / 128) * KB;
+          }
         } else {
           if (!p.a_sorted) {
             sa_idx = static_cast<long long>(t) * p.topk + slot;
             c.sa_step = static_cast<long long>(p.M) * p.topk;
           }
           const int n0 = n_tile * BN;
-          const long long nb_exp = p.N / 128;
-          sb_idx0 = (e * nb_exp + min(n0 + half * CH, p.N - 1) / 128) * KB;
-          sb_idx1 = (e * nb_exp + min(n0 + BN / 2 + half * CH, p.N - 1) / 128) * KB;
+          if constexpr (is_pt(MODE)) {
+            c.c0 = n0 + half * CH;
+            c.c1 = c.c0 + BN / 2;
+            sb_idx0 = static_cast<long long>(e) * p.N + c.c0;
+            sb_idx1 = sb_idx0 + BN / 2;
+          } else {
+            const long long nb_exp = p.N / 128;
+            sb_idx0 = (e * nb_exp + min(n0 + half * CH, p.N - 1) / 128) * KB;
+            sb_idx1 = (e * nb_exp + min(n0 + BN / 2 + half * CH, p.N - 1) / 128) * KB;
+          }
         }
       }
       c.sa = p.scale_a + sa_idx;
@@ -725,7 +747,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         int t, slot;
         c.row_ok = moe_row(m_blk, t, slot);
         if (c.row_ok && p.doweight) c.route_w = p.sorted_weights[m_blk * p.tile_m + r];
-        if constexpr (MODE == kMoe1) {
+        if constexpr (is_moe1(MODE)) {
           c.n0 = n_tile * (BN / 2);
           c.col0 = c.col1 = half * CH;
           c.out_row = p.out_sorted ? static_cast<size_t>(m_blk * p.tile_m + r) * p.N
@@ -751,7 +773,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     float ring_a[kRing], ring_b0[kRing], ring_b1[kRing];
     TilePos pos = walk.start();
     find_tile(pos, cur);
-    if (MODE != kDensePT && walk.valid(pos)) {
+    if (!is_pt(MODE) && walk.valid(pos)) {
 #pragma unroll
       for (int j = 0; j < kRing; ++j) {
         const int kb = j < KB ? j : 0;
@@ -787,7 +809,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       ScaleCtx nxt;
       float nring_a[kRing], nring_b0[kRing], nring_b1[kRing];
       TilePos npos = pos;
-      for (int kb0 = 0; MODE != kDensePT && kb0 < KB && alive; kb0 += kRing) {
+      for (int kb0 = 0; !is_pt(MODE) && kb0 < KB && alive; kb0 += kRing) {
         if (kb0 + kRing >= KB) {
           // last trip: the next tile's scale context and first scales are fetched now, so that their
           // latency is over when the store phase ends
@@ -868,10 +890,11 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
         }
       }
-      if constexpr (MODE == kDensePT) {
+      if constexpr (is_pt(MODE)) {
         // Per-token / per-channel scales: the tile's whole K range has been accumulated in TMEM
         // buffer pt_tiles % kAccBufs; read it once, scale by sa[row] * sb[column], hand it back.
         walk.advance(npos);
+        if constexpr (!is_dense(MODE)) find_tile(npos, nxt);
         const int buf = static_cast<int>(pt_tiles % kAccBufs);
         const bool got = mbar_wait(tfull_bar(buf), (pt_tiles / kAccBufs) & 1, abort_flag, p.err,
                                    kErrWaitTmemFull);
@@ -881,9 +904,31 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           break;
         }
         tc_fence_after();
-        const int row = pos.m_blk * BM + r;
-        const float sa = row < p.M ? __ldg(p.scale_a + row) : 0.f;
-        const int n0t = pos.n_tile * BN;
+        // this thread's row scale, and for each column group the address of its first channel's
+        // scale and that channel's index (channels at or beyond N are not read)
+        float sa;
+        const float *sbp0, *sbp1;
+        int cb0, cb1;
+        if constexpr (is_dense(MODE)) {
+          const int row = pos.m_blk * BM + r;
+          sa = row < p.M ? __ldg(p.scale_a + row) : 0.f;
+          cb0 = pos.n_tile * BN + half * CH;
+          cb1 = cb0 + BN / 2;
+          sbp0 = p.scale_b + cb0;
+          sbp1 = p.scale_b + cb1;
+        } else {
+          sa = __ldg(cur.sa);
+          cb0 = cur.c0;
+          cb1 = cur.c1;
+          sbp0 = cur.sb0;
+          sbp1 = cur.sb1;
+        }
+        if (!is_dense(MODE) && !cur.active) {
+          // a warp whose rows are all padding hands the buffer back unread
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(buf));
+        } else {
         const uint32_t t0 = tmem_base + lane_base + buf * BN + half * CH;
         auto taddr = [&](int q) { return t0 + (q >= NSUB ? BN / 2 : 0) + (q % NSUB) * LDW; };
         uint32_t va[LDW], vb[LDW];
@@ -894,13 +939,15 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           uint32_t* cv = (q & 1) ? vb : va;
           uint32_t* nv = (q & 1) ? va : vb;
           if (q + 1 < NQ) tmem_ld<LDW>(taddr(q + 1), nv);
-          const int col = (q >= NSUB ? BN / 2 : 0) + half * CH + (q % NSUB) * LDW;  // tile-relative
+          const int off = (q % NSUB) * LDW;   // first channel of this load inside its group
+          const float* sbp = (q >= NSUB ? sbp1 : sbp0) + off;
           float2* a = acc + (q >= NSUB ? CH / 2 : 0) + (q % NSUB) * (LDW / 2);
-          const bool in_n = n0t + col < p.N;   // N % 16 == 0: a load's columns are all in or all out
+          // N % 16 == 0: a load's channels are all in or all out
+          const bool in_n = (q >= NSUB ? cb1 : cb0) + off < p.N;
 #pragma unroll
           for (int c = 0; c < LDW / 2; ++c) {
-            const float s0 = in_n ? sa * __ldg(p.scale_b + n0t + col + 2 * c) : 0.f;
-            const float s1 = in_n ? sa * __ldg(p.scale_b + n0t + col + 2 * c + 1) : 0.f;
+            const float s0 = in_n ? sa * __ldg(sbp + 2 * c) : 0.f;
+            const float s1 = in_n ? sa * __ldg(sbp + 2 * c + 1) : 0.f;
             a[c] = make_float2(__uint_as_float(cv[2 * c]) * s0, __uint_as_float(cv[2 * c + 1]) * s1);
           }
           if (q + 1 < NQ) {
@@ -911,6 +958,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               if (lane == 0) mbar_arrive(tempty_bar(buf));
             }
           }
+        }
         }
       }
       if (!alive) break;
@@ -1046,7 +1094,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         if (tile_stored) {
           // nothing left to do for this tile
-        } else if constexpr (MODE == kMoe1) {
+        } else if constexpr (is_moe1(MODE)) {
 #pragma unroll
           for (int j = 0; j < CH; j += 8) {
             float y[8];
@@ -1126,7 +1174,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                  : "r"(addr)
                                  : "memory");
                     OutT* dst = out + off + n0 + col;
-                    if (MODE == kMoe2 && p.accumulate)
+                    if (is_moe2(MODE) && p.accumulate)
                       red8_packed(dst, q);
                     else
                       *reinterpret_cast<uint4*>(dst) = q;
@@ -1139,7 +1187,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       } else {
         // direct path (narrow tiles, f32 output): each thread stores its own row segments
         if (row_ok) {
-          if constexpr (MODE == kMoe1) {
+          if constexpr (is_moe1(MODE)) {
 #pragma unroll
             for (int j = 0; j < CH; j += 8) {
               if (n0 + col0 + j + 8 <= p.N) {
@@ -1159,7 +1207,7 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                   float y[8];
 #pragma unroll
                   for (int q = 0; q < 8; ++q) y[q] = accf[grp * CH + j + q] * route_w;
-                  if (MODE == kMoe2 && p.accumulate)
+                  if (is_moe2(MODE) && p.accumulate)
                     red8<OutT>(out + out_row + cb + j, y);
                   else
                     store8<OutT>(out + out_row + cb + j, y);
@@ -1171,7 +1219,9 @@ bs_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
 
       // rotate to the prefetched tile
-      if constexpr (MODE != kDensePT) {
+      if constexpr (is_pt(MODE)) {
+        if constexpr (!is_dense(MODE)) cur = nxt;
+      } else {
         cur = nxt;
 #pragma unroll
         for (int j = 0; j < kRing; ++j) {
@@ -1271,7 +1321,7 @@ static int launch_bn(int bn, const CUtensorMap& tmap_a, const CUtensorMap& tmap_
                      const GemmParams& p, int grid, cudaStream_t stream) {
   switch (bn) {
     case 32:
-      if constexpr (MODE == kMoe1) break;  // 16 gate + 16 up columns: not built
+      if constexpr (is_moe1(MODE)) break;  // 16 gate + 16 up columns: not built
       else return launch<32, MODE, OutT>(tmap_a, tmap_c, p, grid, stream);
     case 64: return launch<64, MODE, OutT>(tmap_a, tmap_c, p, grid, stream);
     case 128: return launch<128, MODE, OutT>(tmap_a, tmap_c, p, grid, stream);
@@ -1480,7 +1530,8 @@ static int moe_gemm1_impl(void* out, void* out_q, float* out_scale_t, const void
                           const int32_t* expert_ids, const float* sorted_weights,
                           const int32_t* num_valid_ids, int32_t T, int32_t I, int32_t H,
                           int32_t num_blocks, int32_t E, int32_t k, int32_t tile_m, int32_t doweight,
-                          int32_t out_dtype, const flyb200_gemm_cfg* cfg, void* stream) {
+                          int32_t out_dtype, const flyb200_gemm_cfg* cfg, void* stream,
+                          bool pertoken = false) {
   int rc = moe_common_checks(out_q ? out_q : out, x, w_repacked, scale_x, scale_w, sorted_ids, expert_ids,
                              sorted_weights, num_valid_ids, T, I, H, num_blocks, E, k, tile_m,
                              doweight);
@@ -1492,6 +1543,11 @@ static int moe_gemm1_impl(void* out, void* out_q, float* out_scale_t, const void
   if (sms <= 0) return FLYB200_ERR_CUDA;
   int bn = (cfg && cfg->block_n) ? cfg->block_n : pick_block_n(num_blocks, I, sms, true);
   if (bn < 64) return set_error(FLYB200_ERR_INVALID_ARGUMENT, "stage-1 block_n must be >= 64");
+  if (pertoken) {
+    if (cfg && cfg->block_n && cfg->block_n != 256)
+      return set_error(FLYB200_ERR_INVALID_ARGUMENT, "the per-token MoE kernels are built for block_n 256");
+    bn = 256;
+  }
   if (out_q) {
     if (cfg && cfg->block_n && cfg->block_n != 256)
       return set_error(FLYB200_ERR_INVALID_ARGUMENT, "fused re-quantisation needs block_n 256");
@@ -1522,6 +1578,10 @@ static int moe_gemm1_impl(void* out, void* out_q, float* out_scale_t, const void
   CUtensorMap tmap{};
   if ((rc = moe_sorted_layout(cfg, T, E, k, tile_m, H, x, &p, &tmap))) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (pertoken) {
+    if (out_dtype == FLYB200_BF16) return launch<256, kMoe1PT, __nv_bfloat16>(tmap, tmap, p, grid, st);
+    return launch<256, kMoe1PT, __half>(tmap, tmap, p, grid, st);
+  }
   if (out_dtype == FLYB200_BF16)
     return launch_bn<kMoe1, __nv_bfloat16>(bn, tmap, tmap, p, grid, st);
   return launch_bn<kMoe1, __half>(bn, tmap, tmap, p, grid, st);
@@ -1552,13 +1612,13 @@ extern "C" int flyb200_moe_gemm1_q8(void* out_q, float* out_scale_t, const void*
                         mid_dtype, cfg, stream);
 }
 
-extern "C" int flyb200_moe_gemm2(void* out, const void* a2, const void* w_repacked,
-                                 const float* scale_x, const float* scale_w,
-                                 const int32_t* sorted_ids, const int32_t* expert_ids,
-                                 const float* sorted_weights, const int32_t* num_valid_ids,
-                                 int32_t T, int32_t H, int32_t I, int32_t num_blocks, int32_t E,
-                                 int32_t k, int32_t tile_m, int32_t doweight, int32_t accumulate,
-                                 int32_t out_dtype, const flyb200_gemm_cfg* cfg, void* stream) {
+static int moe_gemm2_impl(void* out, const void* a2, const void* w_repacked,
+                          const float* scale_x, const float* scale_w,
+                          const int32_t* sorted_ids, const int32_t* expert_ids,
+                          const float* sorted_weights, const int32_t* num_valid_ids,
+                          int32_t T, int32_t H, int32_t I, int32_t num_blocks, int32_t E,
+                          int32_t k, int32_t tile_m, int32_t doweight, int32_t accumulate,
+                          int32_t out_dtype, const flyb200_gemm_cfg* cfg, void* stream, bool pertoken) {
   int rc = moe_common_checks(out, a2, w_repacked, scale_x, scale_w, sorted_ids, expert_ids,
                              sorted_weights, num_valid_ids, T, H, I, num_blocks, E, k, tile_m,
                              doweight);
@@ -1569,6 +1629,11 @@ extern "C" int flyb200_moe_gemm2(void* out, const void* a2, const void* w_repack
   const int sms = sm_count();
   if (sms <= 0) return FLYB200_ERR_CUDA;
   int bn = (cfg && cfg->block_n) ? cfg->block_n : pick_block_n(num_blocks, H, sms, false);
+  if (pertoken) {
+    if (cfg && cfg->block_n && cfg->block_n != 256)
+      return set_error(FLYB200_ERR_INVALID_ARGUMENT, "the per-token MoE kernels are built for block_n 256");
+    bn = 256;
+  }
   int grid = sms;
   if (cfg && cfg->max_ctas > 0 && cfg->max_ctas < grid) grid = cfg->max_ctas;
   const long tiles = static_cast<long>(num_blocks) * cdiv(H, bn);
@@ -1589,8 +1654,52 @@ extern "C" int flyb200_moe_gemm2(void* out, const void* a2, const void* w_repack
   if (p.out_sorted)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "stage 2 has no sorted output layout (cfg.path bit 1)");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (pertoken) {
+    if (out_dtype == FLYB200_BF16) return launch<256, kMoe2PT, __nv_bfloat16>(tmap, tmap, p, grid, st);
+    if (out_dtype == FLYB200_F16) return launch<256, kMoe2PT, __half>(tmap, tmap, p, grid, st);
+    return launch<256, kMoe2PT, float>(tmap, tmap, p, grid, st);
+  }
   if (out_dtype == FLYB200_BF16)
     return launch_bn<kMoe2, __nv_bfloat16>(bn, tmap, tmap, p, grid, st);
   if (out_dtype == FLYB200_F16) return launch_bn<kMoe2, __half>(bn, tmap, tmap, p, grid, st);
   return launch_bn<kMoe2, float>(bn, tmap, tmap, p, grid, st);
+}
+
+extern "C" int flyb200_moe_gemm2(void* out, const void* a2, const void* w_repacked,
+                                 const float* scale_x, const float* scale_w,
+                                 const int32_t* sorted_ids, const int32_t* expert_ids,
+                                 const float* sorted_weights, const int32_t* num_valid_ids,
+                                 int32_t T, int32_t H, int32_t I, int32_t num_blocks, int32_t E,
+                                 int32_t k, int32_t tile_m, int32_t doweight, int32_t accumulate,
+                                 int32_t out_dtype, const flyb200_gemm_cfg* cfg, void* stream) {
+  return moe_gemm2_impl(out, a2, w_repacked, scale_x, scale_w, sorted_ids, expert_ids, sorted_weights,
+                        num_valid_ids, T, H, I, num_blocks, E, k, tile_m, doweight, accumulate, out_dtype,
+                        cfg, stream, false);
+}
+
+// The per-token-scale siblings: scale_x [rows] (one per activation row: token for stage 1,
+// token*topk+slot -- or the sorted row with cfg.path bit 0 -- for stage 2), scale_w one per output
+// channel of every expert ([E*2I] / [E*H]). Everything else as in the block-scale entry points.
+extern "C" int flyb200_moe_gemm1_pertoken(void* out, const void* x, const void* w_repacked,
+                                          const float* scale_x, const float* scale_w,
+                                          const int32_t* sorted_ids, const int32_t* expert_ids,
+                                          const float* sorted_weights, const int32_t* num_valid_ids,
+                                          int32_t T, int32_t I, int32_t H, int32_t num_blocks, int32_t E,
+                                          int32_t k, int32_t tile_m, int32_t doweight, int32_t out_dtype,
+                                          const flyb200_gemm_cfg* cfg, void* stream) {
+  return moe_gemm1_impl(out, nullptr, nullptr, x, w_repacked, scale_x, scale_w, sorted_ids, expert_ids,
+                        sorted_weights, num_valid_ids, T, I, H, num_blocks, E, k, tile_m, doweight,
+                        out_dtype, cfg, stream, true);
+}
+
+extern "C" int flyb200_moe_gemm2_pertoken(void* out, const void* a2, const void* w_repacked,
+                                          const float* scale_x, const float* scale_w,
+                                          const int32_t* sorted_ids, const int32_t* expert_ids,
+                                          const float* sorted_weights, const int32_t* num_valid_ids,
+                                          int32_t T, int32_t H, int32_t I, int32_t num_blocks, int32_t E,
+                                          int32_t k, int32_t tile_m, int32_t doweight, int32_t accumulate,
+                                          int32_t out_dtype, const flyb200_gemm_cfg* cfg, void* stream) {
+  return moe_gemm2_impl(out, a2, w_repacked, scale_x, scale_w, sorted_ids, expert_ids, sorted_weights,
+                        num_valid_ids, T, H, I, num_blocks, E, k, tile_m, doweight, accumulate, out_dtype,
+                        cfg, stream, true);
 }

@@ -44,6 +44,37 @@ extern "C" int flyb200_moe_gemm2_reduce(void* out, const void* a2, const void* w
   return flyb200_moe_reduce(workspace, out, valid_mask, T, k, H, out_dtype, stream);
 }
 
+// The per-token-scale sibling (scale_x [T*k], scale_w [E*H]); `zero_fill` = 0 skips the clearing of
+// the per-route rows when the caller knows that every (token, slot) has a routing position
+// (zero_intermediate of the reference's wrapper, kernels/moe_gemm_2stage.py:2689-2780).
+extern "C" int flyb200_moe_gemm2_reduce_pertoken(void* out, const void* a2, const void* w_repacked,
+                                                 const float* scale_x, const float* scale_w,
+                                                 const int32_t* sorted_ids, const int32_t* expert_ids,
+                                                 const float* sorted_weights, const int32_t* num_valid_ids,
+                                                 const uint8_t* valid_mask, int32_t T, int32_t H, int32_t I,
+                                                 int32_t num_blocks, int32_t E, int32_t k, int32_t tile_m,
+                                                 int32_t doweight, int32_t out_dtype,
+                                                 const flyb200_gemm_cfg* cfg, void* workspace,
+                                                 size_t workspace_bytes, int32_t zero_fill, void* stream) {
+  if (out_dtype != FLYB200_BF16 && out_dtype != FLYB200_F16)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT,
+                     "moe_gemm2_reduce_pertoken: out_dtype must be BF16 or F16 (per-route rows are 16-bit)");
+  if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 16)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT,
+                     "moe_gemm2_reduce_pertoken: workspace must be non-NULL and 16-byte aligned");
+  const size_t need = flyb200_moe_gemm2_reduce_workspace_bytes(T, k, H, out_dtype);
+  if (workspace_bytes < need)
+    return set_error(FLYB200_ERR_WORKSPACE, "moe_gemm2_reduce_pertoken: workspace has %zu bytes, needs %zu",
+                     workspace_bytes, need);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (!valid_mask && zero_fill) FLYB200_CUDA_CHECK(cudaMemsetAsync(workspace, 0, need, st));
+  int rc = flyb200_moe_gemm2_pertoken(workspace, a2, w_repacked, scale_x, scale_w, sorted_ids, expert_ids,
+                                      sorted_weights, num_valid_ids, T, H, I, num_blocks, E, k, tile_m,
+                                      doweight, /*accumulate=*/0, out_dtype, cfg, stream);
+  if (rc) return rc;
+  return flyb200_moe_reduce(workspace, out, valid_mask, T, k, H, out_dtype, stream);
+}
+
 // ---------------------------------------------------------------------------------------------
 // The same operation for callers that have no way to hand over scratch memory.
 //

@@ -8,6 +8,11 @@ from .moe_blockscale_2stage import (  # noqa: F401
     compile_moe_blockscale_gemm2_ex,
     compile_moe_reduction,
 )
+from .moe_gemm_2stage import (  # noqa: F401
+    compile_moe_gemm1,
+    compile_moe_gemm2,
+    compile_moe_gemm2_ex,
+)
 from .int4_gemm import (  # noqa: F401
     compile_int4_weight_only_gemm,
     pack_int4_weight,

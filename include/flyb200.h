@@ -153,6 +153,39 @@ int flyb200_moe_gemm2(void* out, const void* a2, const void* w_repacked, const f
                       int32_t tile_m, int32_t doweight, int32_t accumulate, int32_t out_dtype,
                       const flyb200_gemm_cfg* cfg, void* stream);
 
+/* The two MoE stages with per-token activation scales and per-channel weight scales (fp8 operands):
+ * replace launch_moe_gemm1 (kernels/moe_gemm_2stage.py:1215-1262; factory :93-107) and launch_moe_gemm2
+ * (kernels/moe_gemm_2stage.py:2431-2478; factory :1267-1282) for in_dtype "fp8". Arguments as in
+ * flyb200_moe_gemm1 / flyb200_moe_gemm2 except the scales: scale_x one f32 per activation row ([T]
+ * for stage 1; [T*k], row t*k+s, for stage 2 -- or one per routing-order row with cfg.path bit 0),
+ * scale_w one f32 per output channel of every expert ([E*2I], gate channels then up channels per
+ * expert, for stage 1; [E*H] for stage 2). The whole K range of a tile is accumulated in tensor
+ * memory and scaled once. cfg.block_n must be 0 or 256. */
+int flyb200_moe_gemm1_pertoken(void* out, const void* x, const void* w_repacked, const float* scale_x,
+                               const float* scale_w, const int32_t* sorted_ids, const int32_t* expert_ids,
+                               const float* sorted_weights, const int32_t* num_valid_ids, int32_t T,
+                               int32_t I, int32_t H, int32_t num_blocks, int32_t E, int32_t k,
+                               int32_t tile_m, int32_t doweight, int32_t out_dtype,
+                               const flyb200_gemm_cfg* cfg, void* stream);
+int flyb200_moe_gemm2_pertoken(void* out, const void* a2, const void* w_repacked, const float* scale_x,
+                               const float* scale_w, const int32_t* sorted_ids, const int32_t* expert_ids,
+                               const float* sorted_weights, const int32_t* num_valid_ids, int32_t T,
+                               int32_t H, int32_t I, int32_t num_blocks, int32_t E, int32_t k,
+                               int32_t tile_m, int32_t doweight, int32_t accumulate, int32_t out_dtype,
+                               const flyb200_gemm_cfg* cfg, void* stream);
+/* Per-token stage 2 in reduce mode: per-route rows into `workspace` (cleared first when there is no
+ * mask and zero_fill != 0), then the top-k reduction: the wrapper of compile_moe_gemm2_ex(mode=
+ * "reduce") (kernels/moe_gemm_2stage.py:2689-2780). workspace as for flyb200_moe_gemm2_reduce. */
+int flyb200_moe_gemm2_reduce_pertoken(void* out, const void* a2, const void* w_repacked,
+                                      const float* scale_x, const float* scale_w,
+                                      const int32_t* sorted_ids, const int32_t* expert_ids,
+                                      const float* sorted_weights, const int32_t* num_valid_ids,
+                                      const uint8_t* valid_mask, int32_t T, int32_t H, int32_t I,
+                                      int32_t num_blocks, int32_t E, int32_t k, int32_t tile_m,
+                                      int32_t doweight, int32_t out_dtype, const flyb200_gemm_cfg* cfg,
+                                      void* workspace, size_t workspace_bytes, int32_t zero_fill,
+                                      void* stream);
+
 /* Y[t,d] = sum_s X[t,s,d] (fp32 accumulate, slot order 0..k-1), optional u8 mask [T,k].
  * Replaces the launcher of compile_moe_reduction (kernels/moe_blockscale_2stage.py:2446-2638). */
 int flyb200_moe_reduce(const void* x, void* y, const uint8_t* valid_mask, int32_t T, int32_t k,

@@ -144,6 +144,39 @@ def moe_case(ref):
             "fused": fused.numpy()}
 
 
+def moe_pertoken_case(ref):
+    """Per-token-scale MoE, both stages, with the reference test's recipe
+    (tests/kernels/test_moe_gemm.py:1236-1300: randn * 0.2 operands quantised by pertoken_quant, rand
+    scores, stage-1 output rounded to fp16 and re-quantised per route) and its torch_moe_gemm1 /
+    torch_moe_gemm2 (tests/kernels/test_ref.py)."""
+    T, H, I, E, k = 24, 256, 128, 4, 2
+    g = torch.Generator().manual_seed(11)
+    s = 0.2
+    x = torch.randn(T, H, generator=g) * s
+    w1 = torch.randn(E, 2 * I, H, generator=g) * s
+    w2 = torch.randn(E, H, I, generator=g) * (s / I ** 0.5)
+    score = torch.rand(T, E, generator=g)
+    vals, ids = torch.topk(score, k=k, dim=1)
+    tw = torch.softmax(vals, dim=1).float()
+    xq, xs = ref["pertoken_quant"](x, quant_dtype=FP8)
+    w1q, w1s = ref["pertoken_quant"](w1, quant_dtype=FP8)
+    w2q, w2s = ref["pertoken_quant"](w2, quant_dtype=FP8)
+    ids64 = ids.to(torch.int64)
+    out1 = ref["torch_moe_gemm1"](xq, w1q.view(E * 2 * I, H), xs, w1s.view(E * 2 * I, 1), ids64, tw,
+                                  inter_dim=I, doweight_stage1=False)
+    out1w = ref["torch_moe_gemm1"](xq, w1q.view(E * 2 * I, H), xs, w1s.view(E * 2 * I, 1), ids64, tw,
+                                   inter_dim=I, doweight_stage1=True)
+    a2q, a2s = ref["pertoken_quant"](out1.to(torch.float16).float(), quant_dtype=FP8)
+    out2 = ref["torch_moe_gemm2"](a2q, w2q, a2s, w2s, ids64, tw, model_dim=H, doweight_stage2=True)
+    out2n = ref["torch_moe_gemm2"](a2q, w2q, a2s, w2s, ids64, tw, model_dim=H, doweight_stage2=False)
+    return {"cfg": np.array([T, H, I, E, k], dtype=np.int32), "x_q": u8(xq), "x_scale": xs.reshape(-1).numpy(),
+            "topk_ids": ids.to(torch.int32).numpy(), "topk_w": tw.numpy(),
+            "w1_q": u8(w1q), "w1_scale": w1s.reshape(-1).numpy(), "w2_q": u8(w2q),
+            "w2_scale": w2s.reshape(-1).numpy(), "out1": out1.numpy(), "out1_weighted": out1w.numpy(),
+            "a2_q": u8(a2q), "a2_scale": a2s.reshape(-1).numpy(), "out2": out2.numpy(),
+            "out2_unweighted": out2n.numpy()}
+
+
 def quant_case(ref):
     g = torch.Generator().manual_seed(3)
     x = torch.randn(20, 128, generator=g) * 3
@@ -168,7 +201,8 @@ def main():
     np.savez_compressed(os.path.join(HERE, "moe.npz"), **moe_case(ref))
     np.savez_compressed(os.path.join(HERE, "quant.npz"), **quant_case(ref))
     np.savez_compressed(os.path.join(HERE, "pertoken.npz"), **pertoken_cases(ref))
-    for f in ("dense.npz", "sort.npz", "moe.npz", "quant.npz", "pertoken.npz"):
+    np.savez_compressed(os.path.join(HERE, "moe_pertoken.npz"), **moe_pertoken_case(ref))
+    for f in ("dense.npz", "sort.npz", "moe.npz", "quant.npz", "pertoken.npz", "moe_pertoken.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
 
 

@@ -1,0 +1,254 @@
+"""Per-token-scale FP8 MoE (compile_moe_gemm1 / compile_moe_gemm2 / compile_moe_gemm2_ex) on the GPU,
+against the golden vectors made with the reference's torch_moe_gemm1 / torch_moe_gemm2 and against
+the CPU oracle on larger seeded cases."""
+import pytest
+import torch
+
+from oracle import blockscale_ref as O
+from tests.helpers import MAX_REL, MAX_REL_ATOMIC16, assert_close_to_oracle, fp8_from_u8, load_golden
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TDT = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
+
+
+def _golden():
+    g = load_golden("moe_pertoken.npz")
+    cfg = tuple(int(v) for v in g["cfg"])
+    t = {n: torch.from_numpy(g[n]) for n in ("x_scale", "topk_ids", "topk_w", "w1_scale", "w2_scale", "out1",
+                                             "out1_weighted", "a2_scale", "out2", "out2_unweighted")}
+    t.update(x_q=fp8_from_u8(g["x_q"]), w1_q=fp8_from_u8(g["w1_q"]), w2_q=fp8_from_u8(g["w2_q"]),
+             a2_q=fp8_from_u8(g["a2_q"]))
+    return cfg, t
+
+
+def _routing(ids, tw, E, H, tile_m):
+    from flydsl_b200.utils import build_routing_buffers
+
+    sid, sw, seid, nv, _, blocks = build_routing_buffers(topk_ids=ids.to(DEV), topk_weights=tw.to(DEV), experts=E,
+                                                         model_dim=H, tile_m=tile_m, moe_sort_mode="torch")
+    return sid, sw, seid, nv, blocks
+
+
+def _stage1(t, cfg, tile_m, doweight, out_dtype="f16"):
+    from flydsl_b200.kernels import compile_moe_gemm1
+    from flydsl_b200.utils import shuffle_weight
+
+    T, H, I, E, k = cfg
+    sid, sw, seid, nv, blocks = _routing(t["topk_ids"], t["topk_w"], E, H, tile_m)
+    fn = compile_moe_gemm1(model_dim=H, inter_dim=I, experts=E, topk=k, tile_m=tile_m, tile_n=256, tile_k=128,
+                           doweight_stage1=doweight, in_dtype="fp8", out_dtype=out_dtype)
+    out1 = torch.zeros(T, k, I, dtype=TDT[out_dtype], device=DEV)
+    fn(out1.view(-1), t["x_q"].to(DEV).view(-1), shuffle_weight(t["w1_q"].to(DEV)).view(-1),
+       t["x_scale"].to(DEV).view(-1), t["w1_scale"].to(DEV).view(-1), sid, seid, sw, nv, T, I, H, blocks,
+       torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    return out1
+
+
+def _stage2(t, cfg, tile_m, doweight, out_dtype, accumulate):
+    from flydsl_b200.kernels import compile_moe_gemm2, compile_moe_reduction
+    from flydsl_b200.utils import shuffle_weight
+
+    T, H, I, E, k = cfg
+    sid, sw, seid, nv, blocks = _routing(t["topk_ids"], t["topk_w"], E, H, tile_m)
+    fn = compile_moe_gemm2(model_dim=H, inter_dim=I, experts=E, topk=k, tile_m=tile_m, tile_n=256, tile_k=128,
+                           doweight_stage2=doweight, in_dtype="fp8", out_dtype=out_dtype, accumulate=accumulate)
+    args = (t["a2_q"].to(DEV).view(-1), shuffle_weight(t["w2_q"].to(DEV)).view(-1), t["a2_scale"].to(DEV).view(-1),
+            t["w2_scale"].to(DEV).view(-1), sid, seid, sw, nv, T, H, I, blocks, torch.cuda.current_stream())
+    if accumulate:
+        out = torch.zeros(T, H, dtype=TDT[out_dtype], device=DEV)
+        fn(out.view(-1), *args)
+    else:
+        routes = torch.zeros(T * k, H, dtype=TDT[out_dtype], device=DEV)
+        fn(routes.view(-1), *args)
+        out = torch.empty(T, H, dtype=TDT[out_dtype], device=DEV)
+        compile_moe_reduction(topk=k, model_dim=H, dtype_str=out_dtype)(routes.view(T, k, H), out, None, T, None)
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("tile_m", [16, 32, 64, 128])
+@pytest.mark.parametrize("doweight", [False, True])
+def test_stage1_vs_golden(tile_m, doweight):
+    cfg, t = _golden()
+    out1 = _stage1(t, cfg, tile_m, doweight)
+    assert_close_to_oracle(out1, t["out1_weighted" if doweight else "out1"], f"stage1 tile_m={tile_m} w={doweight}")
+
+
+@pytest.mark.parametrize("out_dtype,accumulate", [("f16", True), ("bf16", True), ("f32", True), ("f16", False),
+                                                  ("bf16", False)])
+@pytest.mark.parametrize("tile_m", [16, 128])
+def test_stage2_vs_golden(out_dtype, accumulate, tile_m):
+    cfg, t = _golden()
+    out = _stage2(t, cfg, tile_m, True, out_dtype, accumulate)
+    budget = MAX_REL_ATOMIC16 if (accumulate and out_dtype != "f32") else MAX_REL
+    assert_close_to_oracle(out, t["out2"], f"stage2 {out_dtype} acc={accumulate} tile_m={tile_m}", max_rel=budget)
+
+
+def test_stage2_unweighted_vs_golden():
+    cfg, t = _golden()
+    out = _stage2(t, cfg, 32, False, "f32", True)
+    assert_close_to_oracle(out, t["out2_unweighted"], "stage2 without route weights")
+
+
+def _seeded_case(T, H, I, E, k, seed, hot=0):
+    g = torch.Generator().manual_seed(seed)
+    s = 0.2
+    x = torch.randn(T, H, generator=g) * s
+    w1 = torch.randn(E, 2 * I, H, generator=g) * s
+    w2 = torch.randn(E, H, I, generator=g) * (s / I ** 0.5)
+    score = torch.rand(T, E, generator=g)
+    if hot:
+        score[:, :hot] += 1.0
+    vals, ids = torch.topk(score, k=k, dim=1)
+    tw = torch.softmax(vals, dim=1).float()
+    xq, xs = O.pertoken_quant(x)
+    w1q, w1s = O.pertoken_quant(w1)
+    w2q, w2s = O.pertoken_quant(w2)
+    return dict(x_q=xq, x_scale=xs.reshape(-1), w1_q=w1q, w1_scale=w1s.reshape(-1), w2_q=w2q,
+                w2_scale=w2s.reshape(-1), topk_ids=ids.to(torch.int32), topk_w=tw)
+
+
+# the reference's small and medium rows (tests/kernels/test_moe_gemm.py test_moe_gemm_2stage grid:
+# model_dim / inter_dim multiples of 256, 8-16 experts, top-2/4) plus ragged token counts and a case
+# with many row blocks per expert and empty experts
+@pytest.mark.parametrize("T,H,I,E,k,tile_m,hot", [(64, 1024, 256, 4, 2, 32, 0), (129, 1024, 256, 8, 2, 64, 0),
+                                                  (333, 512, 384, 16, 4, 128, 0), (1, 256, 128, 8, 2, 16, 0),
+                                                  (700, 256, 128, 8, 2, 128, 2)])
+def test_two_stage_chain_vs_oracle(T, H, I, E, k, tile_m, hot):
+    """gemm1 -> fp16 -> per-route re-quantisation (the reference's host-side pertoken_quant) -> gemm2
+    in reduce mode, each stage against the oracle on the tensors the GPU chain itself produced."""
+    from flydsl_b200.kernels import MoeGemm2Mode, compile_moe_gemm2_ex
+    from flydsl_b200.utils import pertoken_quant, shuffle_weight
+
+    cfg = (T, H, I, E, k)
+    t = _seeded_case(T, H, I, E, k, seed=T + E, hot=hot)
+    out1 = _stage1(t, cfg, tile_m, False)
+    ids64 = t["topk_ids"].to(torch.int64)
+    want1 = O.torch_moe_gemm1_pertoken_ref(t["x_q"], t["w1_q"], t["x_scale"], t["w1_scale"], ids64, t["topk_w"], I)
+    assert_close_to_oracle(out1, want1, f"stage1 {cfg}")
+
+    a2q, a2s = pertoken_quant(out1.float())          # [T, k, I] fp8, [T, k, 1]
+    sid, sw, seid, nv, blocks = _routing(t["topk_ids"], t["topk_w"], E, H, tile_m)
+    exe = compile_moe_gemm2_ex(model_dim=H, inter_dim=I, experts=E, topk=k, tile_m=tile_m, tile_n=256, tile_k=128,
+                               doweight_stage2=True, in_dtype="fp8", out_dtype="bf16", mode=MoeGemm2Mode.REDUCE)
+    assert exe.mode == MoeGemm2Mode.REDUCE
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+    exe(out, a2q.view(-1), shuffle_weight(t["w2_q"].to(DEV)).view(-1), a2s.view(-1), t["w2_scale"].to(DEV), sid, seid,
+        sw, nv, T, H, I, blocks)
+    torch.cuda.synchronize()
+    want2 = O.torch_moe_gemm2_pertoken_ref(a2q.cpu(), t["w2_q"], a2s.cpu(), t["w2_scale"], ids64, t["topk_w"], H)
+    assert_close_to_oracle(out, want2, f"stage2 reduce {cfg}")
+
+
+def test_gemm2_ex_modes_and_valid_mask():
+    from flydsl_b200.kernels import MoeGemm2Mode, compile_moe_gemm2_ex
+    from flydsl_b200.utils import shuffle_weight
+
+    cfg, t = _golden()
+    T, H, I, E, k = cfg
+    sid, sw, seid, nv, blocks = _routing(t["topk_ids"], t["topk_w"], E, H, 32)
+    args = (t["a2_q"].to(DEV), shuffle_weight(t["w2_q"].to(DEV)), t["a2_scale"].to(DEV), t["w2_scale"].to(DEV), sid,
+            seid, sw, nv, T, H, I, blocks)
+    common = dict(model_dim=H, inter_dim=I, experts=E, topk=k, tile_m=32, tile_n=256, tile_k=128,
+                  doweight_stage2=True, in_dtype="fp8", out_dtype="f16")
+    atomic = compile_moe_gemm2_ex(mode=MoeGemm2Mode.ATOMIC, **common)
+    out = torch.zeros(T, H, dtype=torch.float16, device=DEV)
+    atomic(out, *args)
+    torch.cuda.synchronize()
+    assert_close_to_oracle(out, t["out2"], "gemm2_ex atomic", max_rel=MAX_REL_ATOMIC16)
+
+    # masked reduce: slot 1 of every odd token is dropped from the sum
+    mask = torch.ones(T, k, dtype=torch.uint8, device=DEV)
+    mask[1::2, 1] = 0
+    masked = compile_moe_gemm2_ex(mode=MoeGemm2Mode.REDUCE, valid_mask=mask, **common)
+    out_m = torch.empty(T, H, dtype=torch.float16, device=DEV)
+    masked(out_m, *args, valid_mask=mask)
+    torch.cuda.synchronize()
+    routes = O.torch_moe_gemm2_pertoken_ref(t["a2_q"].view(T, k, I), t["w2_q"], t["a2_scale"], t["w2_scale"],
+                                            t["topk_ids"].to(torch.int64), t["topk_w"], H, per_route=True)
+    want = (routes * mask.cpu().view(T, k, 1).float()).sum(1)
+    assert_close_to_oracle(out_m, want, "gemm2_ex reduce with valid_mask")
+
+    # zero_intermediate=False is allowed when every (token, slot) has a routing position
+    nz = compile_moe_gemm2_ex(mode=MoeGemm2Mode.REDUCE, zero_intermediate=False, **common)
+    out_nz = torch.empty(T, H, dtype=torch.float16, device=DEV)
+    nz(out_nz, *args)
+    torch.cuda.synchronize()
+    assert_close_to_oracle(out_nz, t["out2"], "gemm2_ex reduce without zero fill")
+
+
+def test_factories_validate_like_the_reference():
+    from flydsl_b200.kernels import compile_moe_gemm1, compile_moe_gemm2, compile_moe_gemm2_ex
+
+    ok = dict(model_dim=256, inter_dim=128, experts=4, topk=2, tile_m=32, tile_n=128, tile_k=128)
+    with pytest.raises(ValueError, match="in_dtype must be one of"):
+        compile_moe_gemm1(doweight_stage1=False, in_dtype="fp4", **ok)
+    with pytest.raises(NotImplementedError):
+        compile_moe_gemm1(doweight_stage1=False, in_dtype="int8", **ok)
+    with pytest.raises(NotImplementedError):
+        compile_moe_gemm2(doweight_stage2=True, in_dtype="int4_bf16", group_size=32, **ok)
+    with pytest.raises(ValueError, match="out_dtype must be"):
+        compile_moe_gemm2(doweight_stage2=True, out_dtype="i8", **ok)
+    with pytest.raises(ValueError, match="accumulate=False"):
+        compile_moe_gemm2(doweight_stage2=True, out_dtype="f32", accumulate=False, **ok)
+    with pytest.raises(ValueError, match="tile_k_bytes"):
+        compile_moe_gemm1(doweight_stage1=False, **{**ok, "tile_k": 96})
+    with pytest.raises(ValueError, match="mode must be"):
+        compile_moe_gemm2_ex(doweight_stage2=True, mode="sum", **ok)
+    fn = compile_moe_gemm1(doweight_stage1=False, **ok)
+    assert fn is compile_moe_gemm1(doweight_stage1=False, **ok)   # cached like the reference's factories
+    z = torch.zeros(8, dtype=torch.float32, device=DEV)
+    with pytest.raises(ValueError, match="built for"):
+        fn(z, z, z, z, z, z, z, z, z, 4, 256, 256, 1)
+
+
+@pytest.mark.parametrize("tile_m", [16, 128])
+def test_routing_order_layouts_give_the_same_bits_as_the_gathered_layouts(tile_m):
+    """a_sorted / out_sorted (rows fetched by TMA, staged tiles written by the store warps) against
+    the reference layouts (rows gathered, [tokens, topk, ...] outputs): same tiles, same arithmetic."""
+    from flydsl_b200.kernels import compile_moe_gemm1, compile_moe_gemm2
+    from flydsl_b200.utils import pertoken_quant, shuffle_weight
+
+    T, H, I, E, k = cfg = (200, 512, 256, 8, 2)
+    t = _seeded_case(T, H, I, E, k, seed=77, hot=1)
+    sid, sw, seid, nv, blocks = _routing(t["topk_ids"], t["topk_w"], E, H, tile_m)
+    rows = T * k + E * tile_m - k
+    tok, slot = (sid[:rows] & 0xFFFFFF).long(), (sid[:rows] >> 24).long()
+    valid = tok < T
+    x_sorted = torch.zeros(rows, H, dtype=torch.uint8, device=DEV)
+    x_sorted[valid] = t["x_q"].to(DEV).view(torch.uint8)[tok[valid]]
+    xs_sorted = torch.ones(rows, dtype=torch.float32, device=DEV)
+    xs_sorted[valid] = t["x_scale"].to(DEV)[tok[valid]]
+    common = dict(model_dim=H, inter_dim=I, experts=E, topk=k, tile_m=tile_m, tile_n=256, tile_k=128)
+    w1 = shuffle_weight(t["w1_q"].to(DEV))
+    w2 = shuffle_weight(t["w2_q"].to(DEV))
+
+    want1 = _stage1(t, cfg, tile_m, True)
+    g1 = compile_moe_gemm1(doweight_stage1=True, a_sorted=True, out_sorted=True, **common)
+    out1_sorted = torch.zeros(rows, I, dtype=torch.float16, device=DEV)
+    g1(out1_sorted, x_sorted.view(torch.float8_e4m3fn), w1, xs_sorted, t["w1_scale"].to(DEV), sid, seid, sw, nv, T, I,
+       H, blocks)
+    torch.cuda.synchronize()
+    got1 = torch.zeros_like(want1)
+    got1[tok[valid], slot[valid]] = out1_sorted[valid]
+    assert torch.equal(got1, want1)
+
+    a2q, a2s = pertoken_quant(want1.float())                       # [T, k, I], [T, k, 1]
+    a2_sorted = torch.zeros(rows, I, dtype=torch.uint8, device=DEV)
+    a2_sorted[valid] = a2q.view(torch.uint8)[tok[valid], slot[valid]]
+    a2s_sorted = torch.ones(rows, dtype=torch.float32, device=DEV)
+    a2s_sorted[valid] = a2s[tok[valid], slot[valid], 0]
+    outs = []
+    for a_sorted, x2, s2 in ((False, a2q, a2s), (True, a2_sorted.view(torch.float8_e4m3fn), a2s_sorted)):
+        g2 = compile_moe_gemm2(doweight_stage2=False, out_dtype="bf16", accumulate=False, a_sorted=a_sorted, **common)
+        routes = torch.zeros(T * k, H, dtype=torch.bfloat16, device=DEV)
+        g2(routes, x2, w2, s2, t["w2_scale"].to(DEV), sid, seid, sw, nv, T, H, I, blocks)
+        torch.cuda.synchronize()
+        outs.append(routes)
+    assert torch.equal(outs[0], outs[1])
+    want2 = O.torch_moe_gemm2_pertoken_ref(a2q.cpu(), t["w2_q"], a2s.cpu(), t["w2_scale"],
+                                           t["topk_ids"].to(torch.int64), t["topk_w"], H, doweight_stage2=False,
+                                           per_route=True)
+    assert_close_to_oracle(outs[1].view(T, k, H), want2, "stage2 routes, routing-order input")

@@ -31,6 +31,25 @@ def test_pertoken_oracle_matches_golden(tag):
     assert torch.equal(c, torch.from_numpy(g[f"{tag}_c_f32"]))
 
 
+def test_pertoken_moe_oracle_matches_golden():
+    g = load_golden("moe_pertoken.npz")
+    T, H, I, E, k = (int(v) for v in g["cfg"])
+    ids = torch.from_numpy(g["topk_ids"]).to(torch.int64)
+    tw = torch.from_numpy(g["topk_w"])
+    xq, w1q, w2q, a2q = (fp8_from_u8(g[n]) for n in ("x_q", "w1_q", "w2_q", "a2_q"))
+    xs, w1s, w2s, a2s = (torch.from_numpy(g[n]) for n in ("x_scale", "w1_scale", "w2_scale", "a2_scale"))
+    for doweight, key in ((False, "out1"), (True, "out1_weighted")):
+        out1 = O.torch_moe_gemm1_pertoken_ref(xq, w1q, xs, w1s, ids, tw, I, doweight_stage1=doweight)
+        torch.testing.assert_close(out1, torch.from_numpy(g[key]), rtol=1e-6, atol=1e-6)
+    # the chain of the reference test: fp16 rounding, then per-route re-quantisation (bit-exact)
+    q, s = O.pertoken_quant(torch.from_numpy(g["out1"]).to(torch.float16).float())
+    assert np.array_equal(q.view(torch.uint8).numpy(), g["a2_q"])
+    assert np.array_equal(s.reshape(-1).numpy(), g["a2_scale"])
+    for doweight, key in ((True, "out2"), (False, "out2_unweighted")):
+        out2 = O.torch_moe_gemm2_pertoken_ref(a2q, w2q, a2s, w2s, ids, tw, H, doweight_stage2=doweight)
+        torch.testing.assert_close(out2, torch.from_numpy(g[key]), rtol=1e-6, atol=1e-6)
+
+
 def test_quantisers_match_golden():
     g = load_golden("quant.npz")
     q, s = O.pertoken_quant(torch.from_numpy(g["x"]))
