@@ -20,7 +20,8 @@ from its own weight shard, no collective (strong scaling). Rank 0 prints ONE JSO
   cpu_baseline  the CPU oracle (torch dequantise-then-matmul, oracle/blockscale_ref.py) timed on the
              host cores on the same workload
   sweep/moe/int4/pertoken  extra measurements (dense M-sweep of the three (N,K) pairs; the
-             256-expert top-8 MoE layer; the int4 weight-only decode GEMM; the per-token-scale
+             256-expert top-8 MoE layer and, as the last entry of `moe`, the two stages of its
+             per-token-scale sibling; the int4 weight-only decode GEMM; the per-token-scale
              FP8 GEMM) so the whole scope is measured in one run; skipped with --no-extras
 
   check      outside every timed region the result of the headline GEMM (each rank: its column shard)
@@ -944,6 +945,12 @@ def run_probe(args):
             if i >= args.warmup:
                 times.append(e0.elapsed_time(e1))
         print(json.dumps({"probe": "moe", "experts": E, "tokens": T, "ms": statistics.median(times)}))
+    elif args.probe == "moe_pertoken":
+        # the per-token-scale stages on 32 experts / 512 tokens (routing-order layouts), for ncu
+        H, I, E, topk, T = 7168, 2048, 32, 8, 512
+        w1, _, w2, _ = make_moe_gpu(0, H, I, E, topk, dev, seed=0)
+        r = moe_pertoken_stages(w1, w2, H, I, E, topk, dev, load_peaks(), T=T, tile_m=128)
+        print(json.dumps({"probe": "moe_pertoken", "experts": E, **r}))
     elif args.probe == "int4":
         from flydsl_b200.kernels import compile_int4_weight_only_gemm, pack_int4_weight
 
@@ -1006,7 +1013,7 @@ def run_probe(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--probe", default=None, choices=["moe", "decode", "int4", "pertoken"], help="small profiling run (see run_probe)")
+    ap.add_argument("--probe", default=None, choices=["moe", "moe_pertoken", "decode", "int4", "pertoken"], help="small profiling run (see run_probe)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
