@@ -574,6 +574,13 @@ def moe_pertoken_stages(w1, w2, H, I, E, topk, dev, peaks, T=4096, tile_m=128):
         return statistics.median(ts)
 
     ms1, ms2 = timed(stage1), timed(stage2)
+    # the whole layer as flydsl_b200.moe.PertokenMoE chains it (sort, permute, stage 1, whole-row
+    # re-quantisation, stage 2, reduce)
+    from flydsl_b200.moe import PertokenMoE
+
+    layer = PertokenMoE(w1, w1_cs, w2, w2_cs, topk=topk, tile_m=tile_m)
+    out_layer = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    ms_layer = timed(lambda: layer.forward(x_q, x_s, ids, tw, out=out_layer))
     # back to [T, topk, ...] for the checker
     out1 = torch.zeros(T, topk, I, dtype=torch.float16, device=dev)
     out1[pos_tok[valid], pos_slot[valid]] = out1_sorted[valid]
@@ -602,10 +609,14 @@ def moe_pertoken_stages(w1, w2, H, I, E, topk, dev, peaks, T=4096, tile_m=128):
     ref2 = O.torch_moe_gemm2_pertoken_ref(a2_q[sel.to(dev)].cpu(), torch.stack(q2s), a2_s[sel.to(dev)].cpu(), s2,
                                           local, tw_sel, H)
     mr2, cs2 = parity(out[sel.to(dev)], ref2)
+    mr3, cs3 = parity(out_layer[sel.to(dev)], ref2)   # the layer re-quantises the same fp16 stage-1 rows
+    mr2, cs2 = max(mr2, mr3), min(cs2, cs3)
     ok = bool(max(mr1, mr2) <= MAX_REL and min(cs1, cs2) >= MIN_COS)
     fl1, fl2 = 2.0 * T * topk * 2 * I * H, 2.0 * T * topk * I * H
     return {"tokens": T, "tile_m": tile_m, "scales": "per token / per output channel",
             "layout": "routing-order activations (a_sorted / out_sorted extensions)",
+            "layer_ms": round(ms_layer, 4), "layer_tokens_per_s": round(T / (ms_layer * 1e-3), 1),
+            "layer_launches_per_step": layer.launches_per_step,
             "stage1_ms": round(ms1, 4), "stage2_reduce_ms": round(ms2, 4),
             "stage1_tflops": round(fl1 / (ms1 * 1e-3) / 1e12, 1), "stage2_tflops": round(fl2 / (ms2 * 1e-3) / 1e12, 1),
             "stage1_weight_gbs": round(E * 2 * I * H / (ms1 * 1e-3) / 1e9, 1),
@@ -951,6 +962,24 @@ def run_probe(args):
         w1, _, w2, _ = make_moe_gpu(0, H, I, E, topk, dev, seed=0)
         r = moe_pertoken_stages(w1, w2, H, I, E, topk, dev, load_peaks(), T=T, tile_m=128)
         print(json.dumps({"probe": "moe_pertoken", "experts": E, **r}))
+    elif args.probe == "quant":
+        # the 1x128 quantiser on the stage-1 output of the 256-expert layer: 48 768 x 2 048 f16
+        from flydsl_b200.utils import quant_1x128
+
+        rows, cols = 48768, 2048
+        x = torch.randn(rows, cols, device=dev, dtype=torch.float16)
+        times = []
+        for i in range(args.warmup + args.steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            quant_1x128(x)
+            e1.record()
+            e1.synchronize()
+            if i >= args.warmup:
+                times.append(e0.elapsed_time(e1))
+        us = statistics.median(times) * 1e3
+        print(json.dumps({"probe": "quant", "rows": rows, "cols": cols, "us": us,
+                          "gbs": rows * cols * 3.03125 / us / 1e3}))
     elif args.probe == "int4":
         from flydsl_b200.kernels import compile_int4_weight_only_gemm, pack_int4_weight
 
@@ -1013,7 +1042,7 @@ def run_probe(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--probe", default=None, choices=["moe", "moe_pertoken", "decode", "int4", "pertoken"], help="small profiling run (see run_probe)")
+    ap.add_argument("--probe", default=None, choices=["moe", "moe_pertoken", "quant", "decode", "int4", "pertoken"], help="small profiling run (see run_probe)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)

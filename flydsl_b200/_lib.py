@@ -67,6 +67,9 @@ SIGNATURES = {
     "flyb200_quant_1x128": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32,
                                     c_void_p]),
     "flyb200_moe_gather_rows": (c_int, [c_void_p] * 6 + [c_int32] * 5 + [c_void_p]),
+    "flyb200_moe_gather_rows_pertoken": (c_int, [c_void_p] * 6 + [c_int32] * 5 + [c_void_p]),
+    "flyb200_quant_pertoken": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32,
+                                       c_void_p]),
     "flyb200_quant_1x128_devrows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32,
                                             c_void_p]),
     "flyb200_ep_plan_pack": (c_int, [c_void_p] * 4 + [c_int32] * 5 + [c_void_p] * 5),

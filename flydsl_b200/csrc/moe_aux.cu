@@ -314,9 +314,9 @@ __global__ void __launch_bounds__(256)
 moe_gather_rows_kernel(const uint4* __restrict__ x, const float* __restrict__ scale_t,
                        const int* __restrict__ sorted_ids, const int* __restrict__ num_valid,
                        uint4* __restrict__ x_out, float* __restrict__ scale_out_t, int rows_in,
-                       int K, int topk, int rows_out, int by_slot) {
+                       int K, int topk, int rows_out, int by_slot, int nscale) {
+  // nscale: scale rows per activation row (K/128 for 1x128 groups, 1 for per-token scales)
   const int chunks = K / 16;               // 16-byte chunks per row
-  const int nscale = K / 128;
   const int valid = min(num_valid[0], rows_out);
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
@@ -377,7 +377,128 @@ extern "C" int flyb200_moe_gather_rows(const void* x, const float* scale_t, cons
   if (sms <= 0) return FLYB200_ERR_CUDA;
   moe_gather_rows_kernel<<<sms * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), scale_t, sorted_ids, num_valid_ids, static_cast<uint4*>(x_out),
-      scale_out_t, rows_in, K, topk, rows_out, by_slot ? 1 : 0);
+      scale_out_t, rows_in, K, topk, rows_out, by_slot ? 1 : 0, K / 128);
+  FLYB200_CUDA_CHECK(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+// The same permutation for activations with ONE scale per row (the per-token-scale MoE): scale
+// [rows_in] -> scale_out [rows_out].
+extern "C" int flyb200_moe_gather_rows_pertoken(const void* x, const float* scale, const int32_t* sorted_ids,
+                                                const int32_t* num_valid_ids, void* x_out, float* scale_out,
+                                                int32_t rows_in, int32_t K, int32_t topk, int32_t rows_out,
+                                                int32_t by_slot, void* stream) {
+  if (!x || !scale || !sorted_ids || !num_valid_ids || !x_out || !scale_out)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "moe_gather_rows_pertoken: NULL buffer");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(x_out)) % 16)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "moe_gather_rows_pertoken: x and x_out must be 16-byte aligned");
+  if (rows_in < 1 || rows_out < 1 || K < 16 || K % 16 || topk < 1)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "moe_gather_rows_pertoken: bad sizes");
+  const int sms = sm_count();
+  if (sms <= 0) return FLYB200_ERR_CUDA;
+  moe_gather_rows_kernel<<<sms * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), scale, sorted_ids, num_valid_ids, static_cast<uint4*>(x_out), scale_out,
+      rows_in, K, topk, rows_out, by_slot ? 1 : 0, 1);
+  FLYB200_CUDA_CHECK(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Whole-row quantiser (pertoken_quant of the reference, tests/utils.py:29-73, on 16-bit rows): one
+// scale per row, scale = amax/448 (0 -> 1), q = x/scale; NaN -> 0, +-Inf -> +-448 first. One warp per
+// row, two passes over the row (the second finds it in L1/L2). Used between the stages of the
+// per-token-scale MoE, where the reference test calls the torch function on the host side.
+namespace flyb200 {
+template <typename T>
+__global__ void __launch_bounds__(256)
+quant_pertoken_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale,
+                      const int* __restrict__ num_rows_dev, int64_t rows_alloc, int cols) {
+  const int64_t rows = num_rows_dev ? min(static_cast<int64_t>(num_rows_dev[0]), rows_alloc) : rows_alloc;
+  const int lane = threadIdx.x & 31;
+  const int chunks = cols / 8;   // 16-byte chunks of 8 values
+  const int64_t warp0 = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  auto clean = [](float v) -> float {
+    if (v != v) return 0.f;
+    if (isinf(v)) return v > 0 ? 448.f : -448.f;
+    return v;
+  };
+  for (int64_t row = warp0; row < rows; row += nwarps) {
+    const uint4* xrow = reinterpret_cast<const uint4*>(x + row * cols);
+    float amax = 0.f;
+    for (int c0 = lane; c0 < chunks; c0 += 128) {
+      uint4 raw[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + 32 * u;
+        raw[u] = c < chunks ? xrow[c] : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const T* e = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(clean(to_f32<T>(e[j]))));
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    float sc = __fdiv_rn(amax, 448.f);
+    if (sc == 0.f) sc = 1.f;
+    // Quotients from one reciprocal: q0 = v*rc, q = fma(fma(-sc, q0, v), rc, q0) is the IEEE quotient
+    // v/sc when rc is the correctly rounded reciprocal, the mantissa of sc is not all ones and
+    // nothing is subnormal (Markstein); the other rows take the true division. The sign of v is put
+    // back for the one case the correction step loses it (-0 / sc = -0).
+    const bool true_div = ((__float_as_uint(sc) & 0x7fffffu) == 0x7fffffu) || amax < 1e-20f;
+    const float rc = __frcp_rn(sc);
+    uint2* qrow = reinterpret_cast<uint2*>(q + row * cols);
+    for (int c = lane; c < chunks; c += 32) {
+      const uint4 raw = xrow[c];
+      const T* e = reinterpret_cast<const T*>(&raw);
+      float qv[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float v = clean(to_f32<T>(e[j]));
+        if (true_div) {
+          qv[j] = __fdiv_rn(v, sc);
+        } else {
+          const float q0 = v * rc;
+          const float qc = __fmaf_rn(__fmaf_rn(-sc, q0, v), rc, q0);
+          qv[j] = __uint_as_float(__float_as_uint(qc) | (__float_as_uint(v) & 0x80000000u));
+        }
+      }
+      const uint32_t lo = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qv[0], qv[1]), __NV_SATFINITE, __NV_E4M3)) |
+                          (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qv[2], qv[3]), __NV_SATFINITE, __NV_E4M3)) << 16);
+      const uint32_t hi = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qv[4], qv[5]), __NV_SATFINITE, __NV_E4M3)) |
+                          (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qv[6], qv[7]), __NV_SATFINITE, __NV_E4M3)) << 16);
+      qrow[c] = make_uint2(lo, hi);
+    }
+    if (lane == 0) scale[row] = sc;
+  }
+}
+}  // namespace flyb200
+
+extern "C" int flyb200_quant_pertoken(const void* x, void* q, float* scale, const int32_t* num_rows_dev,
+                                      int64_t rows, int32_t cols, int32_t in_dtype, void* stream) {
+  if (!x || !q || !scale) return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant_pertoken: NULL buffer");
+  if ((reinterpret_cast<uintptr_t>(x) % 16) || (reinterpret_cast<uintptr_t>(q) % 8))
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant_pertoken: x must be 16-byte, q 8-byte aligned");
+  if (rows < 0 || cols < 8 || cols % 8)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant_pertoken: cols (%d) must be a multiple of 8", cols);
+  if (in_dtype != FLYB200_BF16 && in_dtype != FLYB200_F16)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "quant_pertoken: input must be BF16 or F16");
+  if (rows == 0) return FLYB200_OK;
+  const int sms = sm_count();
+  if (sms <= 0) return FLYB200_ERR_CUDA;
+  int64_t blocks = (rows + 7) / 8;
+  if (blocks > static_cast<int64_t>(sms) * 16) blocks = static_cast<int64_t>(sms) * 16;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  uint8_t* qo = static_cast<uint8_t*>(q);
+  if (in_dtype == FLYB200_BF16)
+    quant_pertoken_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(x), qo, scale, num_rows_dev, rows, cols);
+  else
+    quant_pertoken_kernel<__half><<<static_cast<int>(blocks), 256, 0, st>>>(static_cast<const __half*>(x), qo,
+                                                                            scale, num_rows_dev, rows, cols);
   FLYB200_CUDA_CHECK(cudaGetLastError());
   return FLYB200_OK;
 }

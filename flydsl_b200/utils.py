@@ -108,6 +108,27 @@ def quant_1x128(x: torch.Tensor, stream=None) -> Tuple[torch.Tensor, torch.Tenso
     return q, st
 
 
+def quant_pertoken(x: torch.Tensor, num_rows_dev: Optional[torch.Tensor] = None, out=None, scale_out=None,
+                   stream=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """CUDA whole-row quantiser, bit for bit ``pertoken_quant`` on f16/bf16 rows: ``x [rows, cols]``
+    -> (fp8 ``[rows, cols]``, scales f32 ``[rows]``). ``num_rows_dev`` (device int32) limits the work to
+    its first value's leading rows; the other rows of the outputs are left as they are."""
+    _require_cuda(x, "x")
+    if x.dim() != 2 or x.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("quant_pertoken expects f16/bf16 [rows, cols]")
+    rows, cols = x.shape
+    if out is None:
+        out = torch.empty((rows, cols), dtype=FP8_DTYPE, device=x.device)
+    if scale_out is None:
+        scale_out = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().flyb200_quant_pertoken(
+            x.data_ptr(), out.data_ptr(), scale_out.data_ptr(),
+            None if num_rows_dev is None else num_rows_dev.data_ptr(), rows, cols, _dtype_code(x.dtype),
+            _lib.stream_handle(stream)))
+    return out, scale_out
+
+
 def moe_sorting(topk_ids: torch.Tensor, topk_weights: torch.Tensor, *, num_experts: int,
                 block_size: int, expert_mask: Optional[torch.Tensor] = None,
                 num_local_tokens=None, stream=None, permute=None
@@ -206,17 +227,29 @@ def build_routing_buffers(*, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
 
 
 def moe_gather_rows(x, scale_t, sorted_ids, num_valid_ids, *, topk: int, by_slot: bool = False,
-                    out=None, scale_out=None, stream=None):
+                    out=None, scale_out=None, stream=None, per_token: bool = False):
     """Activations into routing order for the TMA-fed stage kernels (``a_sorted=True``).
 
     ``x`` fp8 ``[rows_in, K]`` and ``scale_t`` f32 ``[K/128, rows_in]``; row i of the result is the
     row of sorted position i (token ``t``, or route ``t*topk+slot`` with ``by_slot``), zero for
-    padding. Returns ``(x_sorted [len(sorted_ids), K], scale_sorted_t [K/128, len(sorted_ids)])``."""
+    padding. Returns ``(x_sorted [len(sorted_ids), K], scale_sorted_t [K/128, len(sorted_ids)])``.
+    ``per_token``: one scale per row instead (``scale_t [rows_in]`` -> ``[len(sorted_ids)]``)."""
     _require_cuda(x, "x")
     rows_in, K = x.shape
     rows_out = sorted_ids.numel()
     if out is None:
         out = torch.empty((rows_out, K), dtype=x.dtype, device=x.device)
+    if per_token:
+        if scale_t.numel() != rows_in:
+            raise ValueError(f"per_token gather needs one scale per row ({rows_in}), got {scale_t.numel()}")
+        if scale_out is None:
+            scale_out = torch.empty((rows_out,), dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.load().flyb200_moe_gather_rows_pertoken(
+                x.data_ptr(), scale_t.data_ptr(), sorted_ids.data_ptr(), num_valid_ids.data_ptr(),
+                out.data_ptr(), scale_out.data_ptr(), rows_in, K, int(topk), rows_out, int(bool(by_slot)),
+                _lib.stream_handle(stream)))
+        return out, scale_out
     if scale_out is None:
         scale_out = torch.empty((K // 128, rows_out), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):

@@ -249,6 +249,21 @@ int flyb200_moe_gather_rows(const void* x, const float* scale_t, const int32_t* 
                             const int32_t* num_valid_ids, void* x_out, float* scale_out_t,
                             int32_t rows_in, int32_t K, int32_t topk, int32_t rows_out,
                             int32_t by_slot, void* stream);
+/* The same permutation for the per-token-scale MoE: ONE scale per row, scale [rows_in] ->
+ * scale_out [rows_out] (K a multiple of 16). */
+int flyb200_moe_gather_rows_pertoken(const void* x, const float* scale, const int32_t* sorted_ids,
+                                     const int32_t* num_valid_ids, void* x_out, float* scale_out,
+                                     int32_t rows_in, int32_t K, int32_t topk, int32_t rows_out,
+                                     int32_t by_slot, void* stream);
+
+/* Whole-row quantiser, bit for bit the reference's pertoken_quant (tests/utils.py:29-73) on 16-bit
+ * rows: scale[r] = amax(|x[r, :]|)/448 (0 -> 1; NaN -> 0 and +-Inf -> +-448 first), q = x/scale as
+ * fp8 e4m3. It is what the reference test runs on the host between the stages of the per-token-scale
+ * MoE (tests/kernels/test_moe_gemm.py:1296-1300). x [rows, cols] in_dtype (F16|BF16), cols % 8 == 0;
+ * num_rows_dev (may be NULL): device int32 holding the number of leading rows to process, at most
+ * `rows` (the padded route count of the sorter). */
+int flyb200_quant_pertoken(const void* x, void* q, float* scale, const int32_t* num_rows_dev,
+                           int64_t rows, int32_t cols, int32_t in_dtype, void* stream);
 
 /* flyb200_quant_1x128 over the first num_rows_dev[0] rows only (row count known on the device, e.g.
  * the sorter's padded route count); scale_t is [cols/128, rows_alloc]. Input BF16|F16. */

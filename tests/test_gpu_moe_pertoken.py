@@ -252,3 +252,78 @@ def test_routing_order_layouts_give_the_same_bits_as_the_gathered_layouts(tile_m
                                            t["topk_ids"].to(torch.int64), t["topk_w"], H, doweight_stage2=False,
                                            per_route=True)
     assert_close_to_oracle(outs[1].view(T, k, H), want2, "stage2 routes, routing-order input")
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+def test_quant_pertoken_is_bit_exact_with_the_torch_quantiser(dt):
+    from flydsl_b200.utils import quant_pertoken
+
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(300, 2048, generator=g) * 3).to(dt)
+    x[3] = 0.0                               # all-zero row -> scale 1
+    x[5, 7] = float("inf")
+    x[6, 9] = float("nan")
+    x[7, 11] = float("-inf")
+    x[8] *= 1e-4                             # small values
+    x[9, :64] = -0.0
+    x[10] = x[10].abs().clamp(max=7.0)
+    x[10, 0] = 7.0                           # amax = 7 * 2^0: a power-of-two scale, exact ties
+    x[11] *= 1e-30 if dt == torch.bfloat16 else 1e-3
+    want_q, want_s = O.pertoken_quant(x.float())
+    q, s = quant_pertoken(x.to(DEV))
+    torch.cuda.synchronize()
+    assert torch.equal(s.cpu(), want_s.reshape(-1))
+    assert torch.equal(q.cpu().view(torch.uint8), want_q.view(torch.uint8))
+
+    # a device-side row count: rows beyond it are left untouched; odd widths
+    x2 = (torch.randn(50, 520, generator=g)).to(dt).to(DEV)
+    n = torch.tensor([17], dtype=torch.int32, device=DEV)
+    q2 = torch.full((50, 520), 0x7F, dtype=torch.uint8, device=DEV).view(torch.float8_e4m3fn)
+    s2 = torch.full((50,), -1.0, dtype=torch.float32, device=DEV)
+    quant_pertoken(x2, n, out=q2, scale_out=s2)
+    torch.cuda.synchronize()
+    wq, ws = O.pertoken_quant(x2.cpu().float())
+    assert torch.equal(q2.cpu().view(torch.uint8)[:17], wq.view(torch.uint8)[:17])
+    assert torch.equal(s2.cpu()[:17], ws.reshape(-1)[:17])
+    assert bool((q2.cpu().view(torch.uint8)[17:] == 0x7F).all()) and bool((s2.cpu()[17:] == -1.0).all())
+
+
+def test_gather_rows_with_one_scale_per_row():
+    from flydsl_b200.utils import moe_gather_rows
+
+    T, H, E, k, tile_m = 77, 256, 8, 2, 16
+    t = _seeded_case(T, H, 128, E, k, seed=9)
+    sid, sw, seid, nv, blocks = _routing(t["topk_ids"], t["topk_w"], E, H, tile_m)
+    xs, ss = moe_gather_rows(t["x_q"].to(DEV), t["x_scale"].to(DEV), sid, nv, topk=k, per_token=True)
+    torch.cuda.synchronize()
+    valid_rows = int(nv[0])
+    tok = (sid[:valid_rows] & 0xFFFFFF).long().cpu()
+    ok = tok < T
+    want = torch.zeros(valid_rows, H, dtype=torch.uint8)
+    want[ok] = t["x_q"].view(torch.uint8)[tok[ok]]
+    want_s = torch.zeros(valid_rows)
+    want_s[ok] = t["x_scale"][tok[ok]]
+    assert torch.equal(xs.cpu().view(torch.uint8)[:valid_rows], want)
+    assert torch.equal(ss.cpu()[:valid_rows], want_s)
+
+
+@pytest.mark.parametrize("T,H,I,E,k,tile_m,hot", [(64, 1024, 256, 4, 2, 32, 0), (333, 512, 384, 16, 4, 128, 0),
+                                                  (1, 256, 128, 8, 2, 16, 0), (700, 256, 128, 8, 2, 128, 2),
+                                                  (512, 7168, 2048, 8, 4, 128, 0)])
+def test_layer_vs_oracle(T, H, I, E, k, tile_m, hot):
+    """PertokenMoE (sort, permute, stage 1, whole-row re-quantisation, stage 2, reduce: all kernels)
+    against the oracle's chain (stage 1 -> fp16 -> pertoken_quant -> stage 2)."""
+    from flydsl_b200.moe import PertokenMoE
+
+    t = _seeded_case(T, H, I, E, k, seed=3 * T + E, hot=hot)
+    layer = PertokenMoE.from_unpacked(t["w1_q"].to(DEV), t["w1_scale"].to(DEV), t["w2_q"].to(DEV),
+                                      t["w2_scale"].to(DEV), topk=k, tile_m=tile_m)
+    out = layer.forward(t["x_q"].to(DEV), t["x_scale"].to(DEV), t["topk_ids"].to(DEV), t["topk_w"].to(DEV))
+    out_again = layer.forward(t["x_q"].to(DEV), t["x_scale"].to(DEV), t["topk_ids"].to(DEV), t["topk_w"].to(DEV))
+    torch.cuda.synchronize()
+    assert torch.equal(out, out_again)        # fixed summation order: deterministic
+    ids64 = t["topk_ids"].to(torch.int64)
+    out1 = O.torch_moe_gemm1_pertoken_ref(t["x_q"], t["w1_q"], t["x_scale"], t["w1_scale"], ids64, t["topk_w"], I)
+    a2q, a2s = O.pertoken_quant(out1.to(torch.float16).float())
+    want = O.torch_moe_gemm2_pertoken_ref(a2q, t["w2_q"], a2s, t["w2_scale"], ids64, t["topk_w"], H)
+    assert_close_to_oracle(out, want, f"per-token layer {(T, H, I, E, k)}")
