@@ -1538,16 +1538,14 @@ static int moe_gemm1_impl(void* out, void* out_q, float* out_scale_t, const void
   if (rc) return rc;
   if (out_dtype != FLYB200_BF16 && out_dtype != FLYB200_F16)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "stage-1 out_dtype must be BF16 or F16");
+  if (pertoken && cfg && cfg->block_n && cfg->block_n != 256)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "the per-token MoE kernels are built for block_n 256");
   if (num_blocks == 0) return FLYB200_OK;
   const int sms = sm_count();
   if (sms <= 0) return FLYB200_ERR_CUDA;
   int bn = (cfg && cfg->block_n) ? cfg->block_n : pick_block_n(num_blocks, I, sms, true);
   if (bn < 64) return set_error(FLYB200_ERR_INVALID_ARGUMENT, "stage-1 block_n must be >= 64");
-  if (pertoken) {
-    if (cfg && cfg->block_n && cfg->block_n != 256)
-      return set_error(FLYB200_ERR_INVALID_ARGUMENT, "the per-token MoE kernels are built for block_n 256");
-    bn = 256;
-  }
+  if (pertoken) bn = 256;
   if (out_q) {
     if (cfg && cfg->block_n && cfg->block_n != 256)
       return set_error(FLYB200_ERR_INVALID_ARGUMENT, "fused re-quantisation needs block_n 256");
@@ -1625,15 +1623,13 @@ static int moe_gemm2_impl(void* out, const void* a2, const void* w_repacked,
   if (rc) return rc;
   if (out_dtype != FLYB200_BF16 && out_dtype != FLYB200_F16 && out_dtype != FLYB200_F32)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "stage-2 out_dtype must be BF16, F16 or F32");
+  if (pertoken && cfg && cfg->block_n && cfg->block_n != 256)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "the per-token MoE kernels are built for block_n 256");
   if (num_blocks == 0) return FLYB200_OK;
   const int sms = sm_count();
   if (sms <= 0) return FLYB200_ERR_CUDA;
   int bn = (cfg && cfg->block_n) ? cfg->block_n : pick_block_n(num_blocks, H, sms, false);
-  if (pertoken) {
-    if (cfg && cfg->block_n && cfg->block_n != 256)
-      return set_error(FLYB200_ERR_INVALID_ARGUMENT, "the per-token MoE kernels are built for block_n 256");
-    bn = 256;
-  }
+  if (pertoken) bn = 256;
   int grid = sms;
   if (cfg && cfg->max_ctas > 0 && cfg->max_ctas < grid) grid = cfg->max_ctas;
   const long tiles = static_cast<long>(num_blocks) * cdiv(H, bn);

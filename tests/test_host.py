@@ -134,3 +134,37 @@ def test_c_abi_refuses_bad_sizes_before_any_launch():
     # more routes per token than experts would overrun the reference-sized sort buffers
     assert lib.flyb200_moe_sort(p16, p16, 4, 9, 8, 16, None, -1, p16, p16, p16, p16, None) == inval
     assert b"k <= E" in lib.flyb200_last_error_string()
+    # the whole-row quantiser reads 16 bytes and writes 8 at a time
+    assert lib.flyb200_quant_pertoken(p16, p16 + 4, p16, None, 2, 128, _lib.F16, None) == inval
+    assert lib.flyb200_quant_pertoken(p16, p16, p16, None, 2, 132, _lib.F16, None) == inval
+    assert lib.flyb200_quant_pertoken(p16, p16, p16, None, 2, 128, _lib.F32, None) == inval
+    assert lib.flyb200_moe_gather_rows_pertoken(p16, p16, p16, p16, p16 + 8, p16, 4, 128, 2, 8, 0, None) == inval
+    assert lib.flyb200_moe_gather_rows_pertoken(p16, None, p16, p16, p16, p16, 4, 128, 2, 8, 0, None) == inval
+
+
+def test_pertoken_moe_entries_refuse_bad_arguments_before_any_launch():
+    from flydsl_b200 import _lib
+
+    lib = _lib.load()
+    buf = (ctypes.c_ubyte * 4096)()
+    p16 = (ctypes.addressof(buf) + 15) // 16 * 16
+    inval = _lib.ERR_INVALID_ARGUMENT
+    ptrs = [p16] * 9
+    # T, I/H, H/I, blocks, E, k, tile_m, doweight, out_dtype
+    ok1 = [4, 128, 256, 1, 4, 2, 16, 0, _lib.F16]
+    cfg = _lib.GemmCfg(128, 0, 0, 0)   # the per-token stages are built for 256-wide tiles only
+    assert lib.flyb200_moe_gemm1_pertoken(*ptrs, *ok1, ctypes.byref(cfg), None) == inval
+    assert b"block_n 256" in lib.flyb200_last_error_string()
+    bad_k = list(ok1); bad_k[5] = 9    # more routes per token than experts
+    assert lib.flyb200_moe_gemm1_pertoken(*ptrs, *bad_k, None, None) == inval
+    bad_dim = list(ok1); bad_dim[1] = 96
+    assert lib.flyb200_moe_gemm1_pertoken(*ptrs, *bad_dim, None, None) == inval
+    ok2 = [4, 256, 128, 1, 4, 2, 16, 1, 0, _lib.BF16]    # ..., doweight, accumulate, out_dtype
+    assert lib.flyb200_moe_gemm2_pertoken(*ptrs, *ok2, ctypes.byref(cfg), None) == inval
+    bad_tile = list(ok2); bad_tile[6] = 129
+    assert lib.flyb200_moe_gemm2_pertoken(*ptrs, *bad_tile, None, None) == inval
+    # reduce mode: the workspace must be there, aligned and large enough
+    red = [p16] * 10 + [4, 256, 128, 1, 4, 2, 16, 1, _lib.BF16]
+    assert lib.flyb200_moe_gemm2_reduce_pertoken(*red, None, None, 0, 1, None) == inval
+    assert lib.flyb200_moe_gemm2_reduce_pertoken(*red, None, p16, 16, 1, None) == _lib.ERR_WORKSPACE
+    assert lib.flyb200_moe_gemm2_reduce_pertoken(*red[:18], _lib.F32, None, p16, 1 << 20, 1, None) == inval
