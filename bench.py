@@ -654,7 +654,7 @@ def moe_layer_bench(rank, world, dev, peaks, quick=False):
             layer_t.forward(x_q, x_st, ids, tw, out=out)
         torch.cuda.synchronize()
         times = []
-        for _ in range(5 if T >= 1024 else 10):
+        for _ in range(20):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             layer_t.forward(x_q, x_st, ids, tw, out=out)
@@ -667,6 +667,7 @@ def moe_layer_bench(rank, world, dev, peaks, quick=False):
         wbytes = active * 3 * I * H
         abytes = T * H + T * topk * I * (2 + 2 + 1 + 1) + T * topk * H * 2 * 2 + T * H * 2
         res.append({"tokens": T, "hot_experts": hot, "tile_m": tile_m, "ms": round(ms, 4),
+                    "ms_min": round(min(times), 4), "timed_iterations": len(times),
                     "tokens_per_s": round(T / (ms * 1e-3), 1), "active_experts": active,
                     "weight_gb": round(wbytes / 1e9, 3),
                     "hbm_gbs_on_algorithmic_bytes": round((wbytes + abytes) / (ms * 1e-3) / 1e9, 1),
