@@ -1373,7 +1373,7 @@ static int check_ptr(const void* p, size_t align, const char* name) {
 // decode_gemm.cu
 int launch_decode_gemm(void* c, const void* a, const void* b_repacked, const float* scale_a_t,
                        const float* scale_b, int M, int N, int K, int out_dtype, int force_splits,
-                       cudaStream_t stream);
+                       cudaStream_t stream, bool pertoken);
 bool decode_path_pays_off(int M, int N, int K);
 
 }  // namespace flyb200
@@ -1405,7 +1405,7 @@ extern "C" int flyb200_blockscale_gemm(void* c, const void* a, const void* b_rep
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "the decode path takes M <= 64 (got %d)", M);
   if (path == 2 || (path == 0 && M <= 64 && !(cfg && cfg->block_n) && decode_path_pays_off(M, N, K)))
     return launch_decode_gemm(c, a, b_repacked, scale_a_t, scale_b, M, N, K, out_dtype,
-                              cfg ? cfg->split_k : 0, reinterpret_cast<cudaStream_t>(stream));
+                              cfg ? cfg->split_k : 0, reinterpret_cast<cudaStream_t>(stream), false);
 
   const int sms = sm_count();
   if (sms <= 0) return FLYB200_ERR_CUDA;
@@ -1453,6 +1453,16 @@ extern "C" int flyb200_pertoken_gemm(void* c, const void* a, const void* b_repac
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "out_dtype must be BF16 or F16");
   if (cfg && cfg->block_n && cfg->block_n != 256)
     return set_error(FLYB200_ERR_UNSUPPORTED, "the per-token-scale GEMM is built with 256-wide tiles only");
+  // Decode-size M: the swap-AB split-K kernel with the token's scale on every K block and the
+  // channel's scale applied once (cfg.path as for flyb200_blockscale_gemm).
+  const int path = cfg ? cfg->path : 0;
+  if (path < 0 || path > 2)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "cfg.path must be 0 (auto), 1 (tiled) or 2 (decode)");
+  if (path == 2 && M > 64)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "the decode path takes M <= 64 (got %d)", M);
+  if (path == 2 || (path == 0 && M <= 64 && !(cfg && cfg->block_n) && decode_path_pays_off(M, N, K)))
+    return launch_decode_gemm(c, a, b_repacked, scale_a, scale_b, M, N, K, out_dtype,
+                              cfg ? cfg->split_k : 0, reinterpret_cast<cudaStream_t>(stream), true);
   const int sms = sm_count();
   if (sms <= 0) return FLYB200_ERR_CUDA;
   const int m_blocks = cdiv(M, BM);

@@ -38,6 +38,7 @@ struct DecodeParams {
   int splits;              // cluster size along x
   int kbps;                // K blocks per split
   int stages;              // ring depth used (<= kDecMaxStages)
+  int pertoken;            // scales are per token [M] and per output channel [N] (no K dimension)
 };
 
 template <int NT>
@@ -208,10 +209,13 @@ bs_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecodePa
     // scales of this CTA's K range -> shared memory (sa: per token, sb: one per K block)
     for (int idx = et; idx < count * NT; idx += 128) {
       const int kbl = idx / NT, j = idx - kbl * NT;
-      sa_s[idx] = (j < p.M) ? __ldg(p.scale_a + static_cast<size_t>(kb_begin + kbl) * p.M + j) : 0.f;
+      const size_t src = p.pertoken ? static_cast<size_t>(j) : static_cast<size_t>(kb_begin + kbl) * p.M + j;
+      sa_s[idx] = (j < p.M) ? __ldg(p.scale_a + src) : 0.f;
     }
+    // per-token mode: the token's scale rides along every K block, the channel's scale is applied
+    // once after the K loop
     for (int kbl = et; kbl < count; kbl += 128)
-      sb_s[kbl] = __ldg(p.scale_b + static_cast<size_t>(n_tile) * KBt + kb_begin + kbl);
+      sb_s[kbl] = p.pertoken ? 1.f : __ldg(p.scale_b + static_cast<size_t>(n_tile) * KBt + kb_begin + kbl);
     asm volatile("bar.sync 1, 128;" ::: "memory");
 
     float acc[NT];
@@ -261,6 +265,12 @@ bs_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecodePa
     // of its last K block by now; the other warps arrive as soon as they have issued their work).
     // The send area is this CTA's own (only its finished MMAs read it), so it is written between
     // the arrival and the wait.
+    if (p.pertoken) {
+      const int n = n_tile * 128 + n_loc;
+      const float sbn = n < p.N ? __ldg(p.scale_b + n) : 0.f;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) acc[j] *= sbn;
+    }
     __syncwarp();
     cluster_arrive();
     float* send = reinterpret_cast<float*>(smem_al);
@@ -436,7 +446,7 @@ bool decode_path_pays_off(int M, int N, int K) {
 // Entry used by flyb200_blockscale_gemm for M <= 64.
 int launch_decode_gemm(void* c, const void* a, const void* b_repacked, const float* scale_a_t,
                        const float* scale_b, int M, int N, int K, int out_dtype, int force_splits,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, bool pertoken) {
   const int sms = sm_count();
   if (sms <= 0) return FLYB200_ERR_CUDA;
   const DecodePlan plan = plan_decode(M, N, K, sms, force_splits);
@@ -451,6 +461,7 @@ int launch_decode_gemm(void* c, const void* a, const void* b_repacked, const flo
   if (!p.err) return FLYB200_ERR_CUDA;
   p.M = M; p.N = N; p.K = K;
   p.splits = plan.splits; p.kbps = plan.kbps; p.stages = plan.stages;
+  p.pertoken = pertoken ? 1 : 0;
   CUtensorMap tmap;
   int rc = make_tensor_map_2d(&tmap, a, M, K, 1, plan.nt);
   if (rc) return rc;

@@ -21,11 +21,11 @@ _OUT = {"bf16": _lib.BF16, "fp16": _lib.F16}
 class PertokenGemmLauncher:
     """Callable returned by the factory. Holds only compile-time constants; buffers are the caller's."""
 
-    def __init__(self, N, K, out_dtype, name):
+    def __init__(self, N, K, out_dtype, name, path=0):
         self.N, self.K = int(N), int(K)
         self.out_dtype = out_dtype
         self._out_code = _OUT[out_dtype]
-        self._cfg = _lib.GemmCfg(0, 0, 0, 0)
+        self._cfg = _lib.GemmCfg(0, 0, int(path), 0)
         self._cfg_ref = ctypes.byref(self._cfg)
         self.__name__ = name
         self._fn = _lib.load().flyb200_pertoken_gemm
@@ -57,14 +57,19 @@ def compile_preshuffle_gemm_a8(
     use_cshuffle_epilog: bool = False,
     waves_per_eu: Optional[int] = None,
     use_async_copy: bool = False,
+    path: str = "auto",
 ):
     """Build a launcher for ``C = (A @ B^T) * scale_a * scale_b`` with FP8 (e4m3) operands.
 
     ``tile_m/tile_n/tile_k``, ``lds_stage``, ``use_cshuffle_epilog``, ``waves_per_eu`` and
     ``use_async_copy`` are accepted and validated like the reference does but do not pick the B200
     tile (128 x 256 x 128, whole K accumulated in tensor memory). M and N are run-time arguments of
-    the launcher, as in the reference.
+    the launcher, as in the reference. ``path`` (extension): ``"auto"`` sends M <= 64 to the swap-AB
+    split-K decode kernel when that pays off, ``"tiled"`` / ``"decode"`` force one of the two.
     """
+    paths = {"auto": 0, "tiled": 1, "decode": 2}
+    if path not in paths:
+        raise ValueError(f"path must be one of {tuple(paths)}, got {path!r}")
     if in_dtype not in ("fp8", "int8", "int4", "fp16", "bf16", "fp4"):
         raise ValueError(
             "in_dtype must be one of ('fp8','int8','int4','fp16','bf16','fp4'), " f"got {in_dtype!r}")
@@ -80,4 +85,4 @@ def compile_preshuffle_gemm_a8(
     if N and N % 16 != 0:
         raise ValueError(f"N ({N}) must be divisible by 16")
     name = f"pt_gemm_{out_dtype}_t{tile_m}x{tile_n}x{tile_k}"
-    return PertokenGemmLauncher(N, K, out_dtype, name)
+    return PertokenGemmLauncher(N, K, out_dtype, name, paths[path])

@@ -9,7 +9,7 @@ from tests.helpers import assert_close_to_oracle, fp8_from_u8, load_golden
 pytestmark = pytest.mark.gpu
 
 
-def _run(a_q, sa, b_q, sb, out_dtype="bf16", stream=None):
+def _run(a_q, sa, b_q, sb, out_dtype="bf16", stream=None, path="auto"):
     from flydsl_b200 import _lib
     from flydsl_b200.kernels import compile_preshuffle_gemm_a8
     from flydsl_b200.utils import shuffle_weight
@@ -18,7 +18,7 @@ def _run(a_q, sa, b_q, sb, out_dtype="bf16", stream=None):
     M, K = a_q.shape
     N = b_q.shape[0]
     fn = compile_preshuffle_gemm_a8(M=M, N=N, K=K, tile_m=64, tile_n=256, tile_k=128, in_dtype="fp8",
-                                    out_dtype=out_dtype)
+                                    out_dtype=out_dtype, path=path)
     tdt = torch.bfloat16 if out_dtype == "bf16" else torch.float16
     c = torch.zeros((M, N), dtype=tdt, device=dev)
     fn(c, a_q.to(dev), shuffle_weight(b_q.to(dev)), sa.to(dev).contiguous().view(-1),
@@ -57,6 +57,20 @@ def test_pertoken_reference_shapes(M, N, K, out_dtype):
     want = O.run_torch_pertoken(a_q, b_q, sa, sb)
     got = _run(a_q, sa, b_q, sb, out_dtype=out_dtype, stream=torch.cuda.current_stream())
     assert_close_to_oracle(got, want, f"per-token M={M} N={N} K={K} {out_dtype}")
+
+
+# Decode-size M on both kernels: the swap-AB split-K kernel (token scale on every K block, channel
+# scale once) and the tiled kernel give the same result within the parity bar.
+@pytest.mark.parametrize("M,N,K", [(1, 7168, 2048), (16, 4096, 7168), (32, 7168, 2048), (33, 1024, 2048),
+                                   (64, 24576, 1536), (7, 272, 256)])
+@pytest.mark.parametrize("path", ["decode", "tiled", "auto"])
+def test_pertoken_decode_sizes_on_both_kernels(M, N, K, path):
+    g = torch.Generator().manual_seed(M + K)
+    a_q, sa = O.pertoken_quant(torch.randn(M, K, generator=g))
+    b_q, sb = O.pertoken_quant(torch.randn(N, K, generator=g) * 0.05)
+    want = O.run_torch_pertoken(a_q, b_q, sa.view(-1), sb.view(-1))
+    got = _run(a_q, sa.view(-1), b_q, sb.view(-1), path=path)
+    assert_close_to_oracle(got, want, f"per-token {path} M={M} N={N} K={K}")
 
 
 def test_pertoken_signed_operands_and_many_tiles_per_cta():
