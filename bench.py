@@ -458,6 +458,33 @@ def pertoken_sweep(dev, peaks, quick=False):
                      "frac_fp8_peak": round(tf / (2 * peaks["bf16_tflops"]), 4), "copies": nset,
                      "check": {"max_rel": rel, "ok": bool(rel <= MAX_REL), "against": "fp32 torch on the GPU, 64 x 64 samples"}})
         del sets
+    # decode size: M = 32 on the split-K decode kernel, cold L2 via a CUDA graph over weight copies
+    for (M, N, K) in ([] if quick else [(32, 7168, 2048), (32, 4096, 7168)]):
+        byts = M * K + N * K + 2 * M * N
+        copies = max(2, min(24, -(-2 * L2_BYTES // byts)))
+        sets = []
+        for _ in range(copies):
+            a = torch.randn(M, K, generator=g, device=dev).to(torch.float8_e4m3fn)
+            b = (torch.randn(N, K, generator=g, device=dev) * 0.5).to(torch.float8_e4m3fn)
+            sets.append((a, shuffle_weight(b), torch.rand(M, generator=g, device=dev) + 0.5,
+                         torch.rand(N, generator=g, device=dev) + 0.5,
+                         torch.empty(M, N, dtype=torch.bfloat16, device=dev), b))
+        fn = compile_preshuffle_gemm_a8(M=M, N=N, K=K, tile_m=64, tile_n=256, tile_k=128, out_dtype="bf16")
+
+        def make_call(i):
+            a, b, sa, sb, c, _ = sets[i]
+            return lambda: fn(c, a, b, sa, sb, M, N, None)
+
+        us = time_graph_rotating(make_call, copies)
+        a, _, sa, sb, c, b_raw = sets[0]
+        ci = torch.linspace(0, N - 1, 64, device=dev).long()
+        want = (a.float() * sa[:, None]) @ (b_raw[ci].float() * sb[ci, None]).t()
+        rel = ((c[:, ci].float() - want).abs().max() / want.abs().max()).item()
+        gbs = byts / us / 1e3
+        rows.append({"M": M, "N": N, "K": K, "us": round(us, 2), "gbs": round(gbs, 1),
+                     "frac_hbm_peak": round(gbs / peaks["hbm_gbs"], 4), "copies": copies,
+                     "check": {"max_rel": rel, "ok": bool(rel <= MAX_REL), "against": "fp32 torch on the GPU, 32 x 64 samples"}})
+        del sets
     return rows
 
 
