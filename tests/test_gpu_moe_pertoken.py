@@ -327,3 +327,49 @@ def test_layer_vs_oracle(T, H, I, E, k, tile_m, hot):
     a2q, a2s = O.pertoken_quant(out1.to(torch.float16).float())
     want = O.torch_moe_gemm2_pertoken_ref(a2q, t["w2_q"], a2s, t["w2_scale"], ids64, t["topk_w"], H)
     assert_close_to_oracle(out, want, f"per-token layer {(T, H, I, E, k)}")
+
+
+@pytest.mark.parametrize("kind", ["pertoken", "blockscale"])
+def test_layers_replay_from_a_cuda_graph(kind):
+    """Both layer chains are launch-only after warm-up, so a step can be captured once and replayed
+    on new inputs written into the same buffers (the reference's tests do the same with their
+    testGraph switch, tests/test_common.py:79-91)."""
+    from flydsl_b200.moe import BlockscaleMoE, PertokenMoE
+
+    T, H, I, E, k, tile_m = 96, 512, 256, 8, 2, 32
+    if kind == "pertoken":
+        t = _seeded_case(T, H, I, E, k, seed=21)
+        layer = PertokenMoE.from_unpacked(t["w1_q"].to(DEV), t["w1_scale"].to(DEV), t["w2_q"].to(DEV),
+                                          t["w2_scale"].to(DEV), topk=k, tile_m=tile_m)
+        x_q, x_s = t["x_q"].to(DEV), t["x_scale"].to(DEV)
+        t2 = _seeded_case(T, H, I, E, k, seed=22)
+        x_q2, x_s2 = t2["x_q"].to(DEV), t2["x_scale"].to(DEV)
+    else:
+        m = O.make_moe_case(T, H, I, E, k, seed=21)
+        layer = BlockscaleMoE.from_unpacked(m["w1_q"].to(DEV), m["w1_scale"].to(DEV), m["w2_q"].to(DEV),
+                                            m["w2_scale"].to(DEV), topk=k, tile_m=tile_m)
+        t = {"topk_ids": m["topk_ids"], "topk_w": m["topk_weights"]}
+        x_q, x_s = m["x_q"].to(DEV), m["x_scale"].t().contiguous().to(DEV)
+        m2 = O.make_moe_case(T, H, I, E, k, seed=22)
+        t2 = {"topk_ids": m2["topk_ids"], "topk_w": m2["topk_weights"]}
+        x_q2, x_s2 = m2["x_q"].to(DEV), m2["x_scale"].t().contiguous().to(DEV)
+    ids, tw = t["topk_ids"].to(DEV), t["topk_w"].to(DEV)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(2):
+            layer.forward(x_q, x_s, ids, tw, out=out)      # warm-up: buffers, kernel attributes
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        layer.forward(x_q, x_s, ids, tw, out=out)
+    # new inputs and routing in the captured buffers
+    x_q.copy_(x_q2); x_s.copy_(x_s2); ids.copy_(t2["topk_ids"].to(DEV)); tw.copy_(t2["topk_w"].to(DEV))
+    graph.replay()
+    torch.cuda.synchronize()
+    got = out.clone()
+    want = layer.forward(x_q, x_s, ids, tw)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
