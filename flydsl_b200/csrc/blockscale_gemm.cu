@@ -60,6 +60,9 @@ struct GemmParams {
   int N;                   // dense: N; stage 1: inter_dim I; stage 2: model_dim H
   int K;
   int a_box_rows;          // dense: rows the A tensor-map box brings per stage
+  // Dense: 0, or the number of row blocks per group of the tile order (see TileWalker): set by the
+  // host when the activations alone are larger than half the L2.
+  int group_m;
   // MoE only
   const int* sorted_ids;
   const int* expert_ids;
@@ -176,6 +179,11 @@ template <int BN, int MODE>
 struct TileWalker {
   int num_m, num_n, total;
   int step_major, step_minor;  // gridDim.x split by the minor dimension's extent
+  // Dense with many row blocks: they are taken in groups of group_m; inside a group the order is the
+  // usual one (row blocks fastest, then column tiles), so a group's slice of A (group_m x 128 x K
+  // bytes) stays in L2 while all column tiles pass over it, instead of the whole of A streaming
+  // through L2 once per column tile. Positions are decoded with divisions then (once per tile).
+  int group_m;
   // tile -> (m block, n tile). Dense: consecutive CTAs share the weight tile and differ in rows
   // (minor = m). MoE: every row block has its own expert's weights, so that order shares nothing and
   // re-reads the whole routing-ordered activation tensor once per column tile (350 MB at 4096 tokens
@@ -184,9 +192,11 @@ struct TileWalker {
   // expert follows its first closely enough to find the expert's weights (29 MB) still in L2.
   static constexpr bool kRowBlockMajor = (!is_dense(MODE));
   __device__ __forceinline__ TileWalker(const GemmParams& p) {
+    group_m = 0;
     if constexpr (is_dense(MODE)) {
       num_m = (p.M + BM - 1) / BM;
       num_n = (p.N + BN - 1) / BN;
+      if (p.group_m > 0 && p.group_m < num_m) group_m = p.group_m;
     } else {
       int valid_rows = p.num_valid[0];
       int nb = (valid_rows + p.tile_m - 1) / p.tile_m;
@@ -201,9 +211,23 @@ struct TileWalker {
     step_major = minor > 0 ? g / minor : 0;
     step_minor = minor > 0 ? g - step_major * minor : 0;
   }
+  __device__ __forceinline__ void decode_grouped(TilePos& t) const {
+    const int per_group = group_m * num_n;
+    const int g = t.tile / per_group;
+    const int r = t.tile - g * per_group;
+    const int rows_here = min(group_m, num_m - g * group_m);   // the last group may be shorter
+    // tiles of the earlier groups are all full, so r indexes this group's own (rows_here x num_n) grid
+    t.n_tile = r / rows_here;
+    t.m_blk = g * group_m + (r - t.n_tile * rows_here);
+  }
   __device__ __forceinline__ TilePos start() const {
     TilePos t;
     t.tile = static_cast<int>(blockIdx.x);
+    if (is_dense(MODE) && group_m > 0) {
+      if (t.tile < total) decode_grouped(t);
+      else t.m_blk = t.n_tile = 0;
+      return t;
+    }
     const int minor = kRowBlockMajor ? num_n : num_m;
     const int hi = minor > 0 ? t.tile / minor : 0;
     const int lo = t.tile - hi * minor;
@@ -214,6 +238,10 @@ struct TileWalker {
   __device__ __forceinline__ bool valid(const TilePos& t) const { return t.tile < total; }
   __device__ __forceinline__ void advance(TilePos& t) const {
     t.tile += static_cast<int>(gridDim.x);
+    if (is_dense(MODE) && group_m > 0) {
+      if (t.tile < total) decode_grouped(t);
+      return;
+    }
     int& lo = kRowBlockMajor ? t.n_tile : t.m_blk;
     int& hi = kRowBlockMajor ? t.m_blk : t.n_tile;
     const int minor = kRowBlockMajor ? num_n : num_m;
@@ -1380,6 +1408,17 @@ bool decode_path_pays_off(int M, int N, int K);
 
 using namespace flyb200;
 
+// Row blocks per group of the dense tile order (TileWalker::group_m): groups whose slice of A is
+// about 24 MB (8..64 row blocks), used when there are at least two such groups. Measured on B200 at
+// M = 16384: (N, K) = (4096, 7168) 544 -> 439-449 us with groups of 8-32 (504 with 64), (7168, 2048)
+// 255 -> 240 us and (24576, 1536) 680 -> 625 us with 64; at M = 4096 (32 row blocks) smaller groups
+// are neutral or slower, and the rule leaves those shapes alone.
+static int dense_group_m(int M, int K) {
+  int gm = static_cast<int>((static_cast<size_t>(24) << 20) / (static_cast<size_t>(BM) * K));
+  gm = gm < 8 ? 8 : (gm > 64 ? 64 : gm);
+  return cdiv(M, BM) >= 2 * gm ? gm : 0;
+}
+
 extern "C" int flyb200_blockscale_gemm(void* c, const void* a, const void* b_repacked,
                                        const float* scale_a_t, const float* scale_b, int32_t M,
                                        int32_t N, int32_t K, int32_t out_dtype,
@@ -1425,6 +1464,7 @@ extern "C" int flyb200_blockscale_gemm(void* c, const void* a, const void* b_rep
   p.err = device_error_word();
   if (!p.err) return FLYB200_ERR_CUDA;
   p.M = M; p.N = N; p.K = K;
+  p.group_m = dense_group_m(M, K);
   // Small M: bring only as many rows as exist (rounded up to the 8-row swizzle atom).
   p.a_box_rows = M >= BM ? BM : ((M + 7) / 8) * 8;
 
@@ -1480,6 +1520,7 @@ extern "C" int flyb200_pertoken_gemm(void* c, const void* a, const void* b_repac
   p.err = device_error_word();
   if (!p.err) return FLYB200_ERR_CUDA;
   p.M = M; p.N = N; p.K = K;
+  p.group_m = dense_group_m(M, K);
   p.a_box_rows = M >= BM ? BM : ((M + 7) / 8) * 8;
   CUtensorMap tmap_a, tmap_c;
   if ((rc = make_tensor_map_2d(&tmap_a, a, M, K, 1, p.a_box_rows))) return rc;

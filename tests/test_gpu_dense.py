@@ -215,3 +215,13 @@ def test_autotuner_picks_a_valid_configuration(tmp_path):
        d["b_scale"].to(DEV), M, N, None)
     torch.cuda.synchronize()
     assert_close_to_oracle(c, ref, f"tuned {cfg}")
+
+
+@pytest.mark.parametrize("M,N,K,block_n", [(4500, 512, 12288, None), (4500, 512, 12288, 128), (7000, 768, 7168, 256)])
+def test_dense_grouped_tile_order_with_a_short_last_group(M, N, K, block_n):
+    """Shapes with enough row blocks for the grouped tile order (groups of 16 / 26 row blocks here),
+    M chosen so that the last group is shorter than the others and the last row block is partial."""
+    case = O.make_dense_case(M, N, K, seed=M)
+    ref = O.run_torch_blockscale(case["a_q"], case["b_q"], case["a_scale"], case["b_scale"], dtype=torch.float32)
+    c = _run_dense(case["a_q"], case["a_scale"], case["b_q"], case["b_scale"], block_n=block_n)
+    assert_close_to_oracle(c, ref, f"grouped order M={M} N={N} K={K} bn={block_n}")

@@ -73,6 +73,16 @@ def test_pertoken_decode_sizes_on_both_kernels(M, N, K, path):
     assert_close_to_oracle(got, want, f"per-token {path} M={M} N={N} K={K}")
 
 
+def test_pertoken_grouped_tile_order_with_a_short_last_group():
+    """Enough row blocks for the grouped tile order (groups of 26 at K = 7168), the last group short."""
+    g = torch.Generator().manual_seed(11)
+    M, N, K = 7000, 768, 7168
+    a_q, sa = O.pertoken_quant(torch.randn(M, K, generator=g))
+    b_q, sb = O.pertoken_quant(torch.randn(N, K, generator=g) * 0.05)
+    want = O.run_torch_pertoken(a_q, b_q, sa.view(-1), sb.view(-1))
+    assert_close_to_oracle(_run(a_q, sa.view(-1), b_q, sb.view(-1)), want, "per-token grouped order")
+
+
 def test_pertoken_signed_operands_and_many_tiles_per_cta():
     """Signed operands (the reference test only uses positive ones) on a shape with several tiles per
     CTA, so that both accumulator buffers and the store hand-off are exercised; twice for
