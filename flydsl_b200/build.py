@@ -23,7 +23,7 @@ LIB_PATH = os.path.join(LIB_DIR, "libflyb200.so")
 INCLUDE_DIR = os.path.join(os.path.dirname(PKG_DIR), "include")
 
 SOURCES = ["api.cu", "repack.cu", "blockscale_gemm.cu", "decode_gemm.cu", "moe_sort.cu", "moe_aux.cu",
-           "moe_pipeline.cu", "ep_pack.cu", "ep_peer.cu", "int4_gemm.cu", "int4_stream.cu"]
+           "moe_pipeline.cu", "ep_pack.cu", "ep_peer.cu", "int4_gemm.cu", "int4_stream.cu", "pt_pair_gemm.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

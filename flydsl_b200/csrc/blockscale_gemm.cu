@@ -1403,6 +1403,10 @@ int launch_decode_gemm(void* c, const void* a, const void* b_repacked, const flo
                        const float* scale_b, int M, int N, int K, int out_dtype, int force_splits,
                        cudaStream_t stream, bool pertoken);
 bool decode_path_pays_off(int M, int N, int K);
+// pt_pair_gemm.cu
+int launch_pertoken_pair_gemm(void* c, const void* a, const void* b_repacked, const float* scale_a,
+                              const float* scale_b, int M, int N, int K, int out_dtype, int max_ctas, int group_m,
+                              cudaStream_t stream);
 
 }  // namespace flyb200
 
@@ -1496,13 +1500,23 @@ extern "C" int flyb200_pertoken_gemm(void* c, const void* a, const void* b_repac
   // Decode-size M: the swap-AB split-K kernel with the token's scale on every K block and the
   // channel's scale applied once (cfg.path as for flyb200_blockscale_gemm).
   const int path = cfg ? cfg->path : 0;
-  if (path < 0 || path > 2)
-    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "cfg.path must be 0 (auto), 1 (tiled) or 2 (decode)");
+  if (path < 0 || path > 3)
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT,
+                     "cfg.path must be 0 (auto), 1 (tiled), 2 (decode) or 3 (CTA pairs)");
   if (path == 2 && M > 64)
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "the decode path takes M <= 64 (got %d)", M);
   if (path == 2 || (path == 0 && M <= 64 && !(cfg && cfg->block_n) && decode_path_pays_off(M, N, K)))
     return launch_decode_gemm(c, a, b_repacked, scale_a, scale_b, M, N, K, out_dtype,
                               cfg ? cfg->split_k : 0, reinterpret_cast<cudaStream_t>(stream), true);
+  // Large problems: the CTA-pair kernel (256 x 256 tiles over two SMs, 32 KB stages), measured faster
+  // than the single-CTA tiles on every benchmarked shape from M = 4096 up.
+  if (path == 3 && (M < 256 || N % 256))
+    return set_error(FLYB200_ERR_INVALID_ARGUMENT, "the CTA-pair path takes M >= 256 and N %% 256 == 0");
+  if (path == 3 || (path == 0 && M >= 2048 && N % 256 == 0 && !(cfg && cfg->block_n))) {
+    return launch_pertoken_pair_gemm(c, a, b_repacked, scale_a, scale_b, M, N, K, out_dtype,
+                                     cfg ? cfg->max_ctas : 0, dense_group_m(M, K),
+                                     reinterpret_cast<cudaStream_t>(stream));
+  }
   const int sms = sm_count();
   if (sms <= 0) return FLYB200_ERR_CUDA;
   const int m_blocks = cdiv(M, BM);

@@ -67,7 +67,7 @@ def compile_preshuffle_gemm_a8(
     the launcher, as in the reference. ``path`` (extension): ``"auto"`` sends M <= 64 to the swap-AB
     split-K decode kernel when that pays off, ``"tiled"`` / ``"decode"`` force one of the two.
     """
-    paths = {"auto": 0, "tiled": 1, "decode": 2}
+    paths = {"auto": 0, "tiled": 1, "decode": 2, "pair": 3}
     if path not in paths:
         raise ValueError(f"path must be one of {tuple(paths)}, got {path!r}")
     if in_dtype not in ("fp8", "int8", "int4", "fp16", "bf16", "fp4"):

@@ -83,6 +83,35 @@ def test_pertoken_grouped_tile_order_with_a_short_last_group():
     assert_close_to_oracle(_run(a_q, sa.view(-1), b_q, sb.view(-1)), want, "per-token grouped order")
 
 
+# The CTA-pair kernel (tcgen05.mma.cta_group::2, 256 x 256 tiles over two SMs): forced on shapes with
+# one tile, ragged M (a pair whose second CTA has few or no rows), many tiles per pair, the grouped
+# tile order, both output types; it must reproduce the single-CTA kernel bit for bit (same products,
+# same fp32 accumulation order inside the tensor core, same scaling) and match the oracle.
+@pytest.mark.parametrize("M,N,K,out_dtype", [(256, 256, 256, "bf16"), (300, 768, 384, "fp16"), (129 + 256, 512, 2048, "bf16"),
+                                             (2048, 6144, 1024, "bf16"), (7000, 768, 7168, "bf16")])
+def test_pertoken_cta_pair_kernel(M, N, K, out_dtype):
+    g = torch.Generator().manual_seed(M + K)
+    a_q, sa = O.pertoken_quant(torch.randn(M, K, generator=g))
+    b_q, sb = O.pertoken_quant(torch.randn(N, K, generator=g) * 0.05)
+    want = O.run_torch_pertoken(a_q, b_q, sa.view(-1), sb.view(-1))
+    pair = _run(a_q, sa.view(-1), b_q, sb.view(-1), out_dtype=out_dtype, path="pair")
+    tiled = _run(a_q, sa.view(-1), b_q, sb.view(-1), out_dtype=out_dtype, path="tiled")
+    assert_close_to_oracle(pair, want, f"per-token pair M={M} N={N} K={K}")
+    assert torch.equal(pair, tiled)
+    again = _run(a_q, sa.view(-1), b_q, sb.view(-1), out_dtype=out_dtype, path="pair")
+    assert torch.equal(pair, again)
+
+
+def test_pertoken_pair_path_argument_checks():
+    from flydsl_b200.kernels import compile_preshuffle_gemm_a8
+
+    dev = torch.device("cuda")
+    fn = compile_preshuffle_gemm_a8(M=128, N=320, K=256, tile_m=64, tile_n=256, tile_k=128, path="pair")
+    z = torch.zeros(128 * 320, dtype=torch.float32, device=dev)
+    with pytest.raises(ValueError, match="CTA-pair path"):
+        fn(z, z, z, z, z, 128, 320, None)
+
+
 def test_pertoken_signed_operands_and_many_tiles_per_cta():
     """Signed operands (the reference test only uses positive ones) on a shape with several tiles per
     CTA, so that both accumulator buffers and the store hand-off are exercised; twice for
