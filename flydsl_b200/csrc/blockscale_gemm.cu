@@ -1509,10 +1509,10 @@ extern "C" int flyb200_pertoken_gemm(void* c, const void* a, const void* b_repac
     return launch_decode_gemm(c, a, b_repacked, scale_a, scale_b, M, N, K, out_dtype,
                               cfg ? cfg->split_k : 0, reinterpret_cast<cudaStream_t>(stream), true);
   // Large problems: the CTA-pair kernel (256 x 256 tiles over two SMs, 32 KB stages), measured faster
-  // than the single-CTA tiles on every benchmarked shape from M = 4096 up.
+  // than the single-CTA tiles on every benchmarked shape from M = 1024 up (equal at 256-512).
   if (path == 3 && (M < 256 || N % 256))
     return set_error(FLYB200_ERR_INVALID_ARGUMENT, "the CTA-pair path takes M >= 256 and N %% 256 == 0");
-  if (path == 3 || (path == 0 && M >= 2048 && N % 256 == 0 && !(cfg && cfg->block_n))) {
+  if (path == 3 || (path == 0 && M >= 1024 && N % 256 == 0 && !(cfg && cfg->block_n))) {
     return launch_pertoken_pair_gemm(c, a, b_repacked, scale_a, scale_b, M, N, K, out_dtype,
                                      cfg ? cfg->max_ctas : 0, dense_group_m(M, K),
                                      reinterpret_cast<cudaStream_t>(stream));

@@ -80,7 +80,7 @@ int flyb200_blockscale_gemm(void* c, const void* a, const void* b_repacked, cons
  * run_torch of tests/kernels/test_preshuffle_gemm.py:55-66. c [M,N] out_dtype (BF16|F16); a [M,K];
  * b_repacked [N,K] from flyb200_repack_weight_fp8; scale_a [M]; scale_b [N]. Any M >= 1;
  * N % 16 == 0; K % 128 == 0. cfg: max_ctas; path 0 = auto, 1 = single-CTA tiles, 2 = decode kernel,
- * 3 = CTA pairs (256 x 256 tiles over two SMs; M >= 256, N % 256 == 0; auto takes it from M = 2048);
+ * 3 = CTA pairs (256 x 256 tiles over two SMs; M >= 256, N % 256 == 0; auto takes it from M = 1024);
  * split_k as for flyb200_blockscale_gemm (M <= 64
  * goes to the swap-AB split-K decode kernel when that pays off: there the token's scale rides along
  * every K block and the channel's scale is applied once after the K loop). */
